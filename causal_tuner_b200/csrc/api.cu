@@ -1,0 +1,211 @@
+// extern "C" surface of libct_b200.so: argument checking, the mapping of each
+// reference operator onto GEMM segments, and the library state (error text,
+// launch counters, per-device error flag).
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace ct {
+
+namespace {
+thread_local char g_error_text[512] = "";
+std::atomic<int64_t> g_launches{0}, g_tc_launches{0};
+constexpr int kMaxDevices = 64;
+int* g_error_flags[kMaxDevices] = {};
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error_text, sizeof(g_error_text), fmt, args);
+  va_end(args);
+  return code;
+}
+
+void count_launch(bool tcgen05) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (tcgen05) g_tc_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+int check_launch(const char* what) {
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(CT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+  return CT_OK;
+}
+
+int* device_error_flag() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!g_error_flags[dev]) {
+    int* flag = nullptr;
+    if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(flag, 0, sizeof(int)) != cudaSuccess) return nullptr;
+    g_error_flags[dev] = flag;
+  }
+  return g_error_flags[dev];
+}
+
+namespace {
+
+bool known_dtype(int d) { return d == CT_F32 || d == CT_BF16 || d == CT_F16; }
+
+Segment segment(const void* a, int64_t a_rs, int64_t a_cs, const void* b, int64_t b_rs, int64_t b_cs, int64_t k) {
+  Segment s;
+  s.a = a; s.a_rs = a_rs; s.a_cs = a_cs;
+  s.b = b; s.b_rs = b_rs; s.b_cs = b_cs;
+  s.k = k;
+  return s;
+}
+
+GemmArgs blank(int64_t M, int64_t N, int in_dtype, void* out, int64_t ldo, int out_dtype) {
+  GemmArgs g;
+  g.M = M; g.N = N; g.nseg = 0; g.in_dtype = in_dtype;
+  g.out = out; g.ldo = ldo; g.out_dtype = out_dtype;
+  g.beta = 0; g.bias = nullptr; g.residual = nullptr; g.ld_res = 0; g.split_k = 1;
+  return g;
+}
+
+// Contraction slices for the token-contracted LoRA gradients. A function of the
+// shapes alone (148 is the B200 SM count), so a given problem is always summed in
+// the same order.
+int gradient_splits(int64_t rows, int64_t cols, int64_t T) {
+  const int64_t tiles = ((rows + 127) / 128) * ((cols + 255) / 256);
+  const int64_t k_blocks = (T + 63) / 64;
+  int64_t splits = tiles > 0 ? 148 / tiles : 1;
+  if (splits > 16) splits = 16;
+  if (splits > k_blocks / 8) splits = k_blocks / 8;  // keep at least 8 k-blocks per slice
+  if (splits < 1) splits = 1;
+  return static_cast<int>(splits);
+}
+
+// out[rows, cols] (fp32) (+)= A^T . B over T rows; A is [T, rows], B is [T, cols].
+int token_contraction(const void* a, int64_t lda, const void* b, int64_t ldb, float* out, int64_t rows, int64_t cols,
+                      int64_t T, int add, int dtype, void* workspace, int path, cudaStream_t stream) {
+  GemmArgs g = blank(rows, cols, dtype, out, cols, CT_F32);
+  g.nseg = 1;
+  g.seg[0] = segment(a, 1, lda, b, ldb, 1, T);
+  g.beta = add;
+  const bool tc = path != CT_PATH_SIMT && gemm_tcgen05_supported(g);
+  const int splits = tc ? gradient_splits(rows, cols, T) : 1;
+  if (splits <= 1) return gemm_dispatch(g, path, stream);
+  if (!workspace) return fail(CT_ERR_ARG, "parameter gradients: workspace is null but %d slices are needed", splits);
+  g.out = workspace;
+  g.beta = 0;
+  g.split_k = splits;
+  int rc = gemm_tcgen05(g, stream);
+  if (rc != CT_OK) return rc;
+  return reduce_partials(static_cast<const float*>(workspace), splits, rows, cols, cols, out, cols, add, stream);
+}
+
+}  // namespace
+}  // namespace ct
+
+using namespace ct;
+
+extern "C" int ct_abi_version(void) { return 1; }
+extern "C" int64_t ct_launch_count(void) { return g_launches.load(); }
+extern "C" int64_t ct_tcgen05_launch_count(void) { return g_tc_launches.load(); }
+extern "C" const char* ct_last_error(void) { return g_error_text; }
+
+extern "C" int ct_check_device(void* stream) {
+  cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(CT_ERR_CUDA, "ct_check_device: %s", cudaGetErrorString(err));
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(CT_ERR_CUDA, "ct_check_device: no current device");
+  if (!g_error_flags[dev]) return CT_OK;
+  int value = 0;
+  err = cudaMemcpy(&value, g_error_flags[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return fail(CT_ERR_CUDA, "ct_check_device: %s", cudaGetErrorString(err));
+  if (value == 0) return CT_OK;
+  cudaMemset(g_error_flags[dev], 0, sizeof(int));
+  static const char* roles[] = {"", "TMA producer waiting for a free stage", "MMA issuer waiting for a free accumulator",
+                                "MMA issuer waiting for a filled stage", "epilogue waiting for a finished accumulator"};
+  return fail(CT_ERR_DEVICE, "a tcgen05 GEMM CTA gave up on a bounded wait: %s", value >= 1 && value <= 4 ? roles[value] : "?");
+}
+
+extern "C" int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                         int64_t ldc, int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype, int add, int path,
+                         void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(CT_ERR_ARG, "ct_matmul: negative size");
+  if (M == 0 || N == 0) return CT_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(CT_ERR_ARG, "ct_matmul: null pointer");
+  if (!known_dtype(in_dtype) || !known_dtype(out_dtype)) return fail(CT_ERR_ARG, "ct_matmul: dtype");
+  GemmArgs g = blank(M, N, in_dtype, C, ldc, out_dtype);
+  g.nseg = 1;
+  g.seg[0] = segment(A, a_rs, a_cs, B, b_rs, b_cs, K);
+  g.beta = add;
+  return gemm_dispatch(g, path, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* a, const void* b,
+                                 const void* bias, const void* residual, int64_t ld_res, void* out, int64_t ld_out,
+                                 void* xa, int64_t ld_xa, int64_t T, int64_t K, int64_t N, int64_t r, int dtype,
+                                 int path, void* stream) {
+  if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_forward_linear: negative size");
+  if (T == 0 || N == 0) return CT_OK;
+  if (!out || (K > 0 && (!x || !w)) || (r > 0 && (!a || !b || !xa))) return fail(CT_ERR_ARG, "ct_forward_linear: null pointer");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_forward_linear: dtype %d", dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (r > 0) {
+    GemmArgs low = blank(T, r, dtype, xa, ld_xa, dtype);
+    low.nseg = 1;
+    low.seg[0] = segment(x, ldx, 1, a, 1, K, K);
+    const int rc = gemm_dispatch(low, path, s);
+    if (rc != CT_OK) return rc;
+  }
+  GemmArgs g = blank(T, N, dtype, out, ld_out, dtype);
+  g.seg[g.nseg++] = segment(x, ldx, 1, w, 1, ldw, K);
+  if (r > 0) g.seg[g.nseg++] = segment(xa, ld_xa, 1, b, 1, r, r);
+  g.bias = bias;
+  g.residual = residual;
+  g.ld_res = ld_res;
+  return gemm_dispatch(g, path, s);
+}
+
+extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t ldw, const void* a,
+                                 const void* b, void* dx, int64_t ld_dx, void* low, int64_t ld_low, int64_t T,
+                                 int64_t K, int64_t N, int64_t r, int add, int dtype, int path, void* stream) {
+  if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_input_gradient: negative size");
+  if (T == 0) return CT_OK;
+  if ((N > 0 && !dy) || (r > 0 && (!b || !low)) || (w && (!dx || (r > 0 && !a))))
+    return fail(CT_ERR_ARG, "ct_input_gradient: null pointer");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_input_gradient: dtype %d", dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (r > 0) {
+    GemmArgs g = blank(T, r, dtype, low, ld_low, dtype);
+    g.nseg = 1;
+    g.seg[0] = segment(dy, ld_dy, 1, b, r, 1, N);
+    const int rc = gemm_dispatch(g, path, s);
+    if (rc != CT_OK) return rc;
+  }
+  if (!w || K == 0) return CT_OK;
+  GemmArgs g = blank(T, K, dtype, dx, ld_dx, dtype);
+  g.seg[g.nseg++] = segment(dy, ld_dy, 1, w, ldw, 1, N);
+  if (r > 0) g.seg[g.nseg++] = segment(low, ld_low, 1, a, K, 1, r);
+  g.beta = add;
+  return gemm_dispatch(g, path, s);
+}
+
+extern "C" int64_t ct_parameter_gradients_workspace(int64_t T, int64_t K, int64_t N, int64_t r, int dtype, int path) {
+  if (dtype != CT_BF16 || path == CT_PATH_SIMT || T <= 0 || r <= 0) return 0;
+  const int sa = gradient_splits(r, K, T), sb = gradient_splits(N, r, T);
+  const int64_t need_a = sa > 1 ? sa * r * K * 4 : 0, need_b = sb > 1 ? sb * N * r * 4 : 0;
+  return need_a > need_b ? need_a : need_b;
+}
+
+extern "C" int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy, int64_t ld_dy, const void* low,
+                                      int64_t ld_low, const void* xa, int64_t ld_xa, float* da, float* db, int64_t T,
+                                      int64_t K, int64_t N, int64_t r, int add, int dtype, void* workspace, int path,
+                                      void* stream) {
+  if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_parameter_gradients: negative size");
+  if (r == 0) return CT_OK;
+  if (!da || !db || (T > 0 && (!x || !dy || !low || !xa))) return fail(CT_ERR_ARG, "ct_parameter_gradients: null pointer");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_parameter_gradients: dtype %d", dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = token_contraction(low, ld_low, x, ldx, da, r, K, T, add, dtype, workspace, path, s);
+  if (rc != CT_OK) return rc;
+  return token_contraction(dy, ld_dy, xa, ld_xa, db, N, r, T, add, dtype, workspace, path, s);
+}

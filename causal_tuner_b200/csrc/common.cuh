@@ -1,0 +1,94 @@
+// Internal declarations shared by the kernels of libct_b200.so.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ct_b200.h"
+
+namespace ct {
+
+// ---- error text + launch accounting (api.cu) --------------------------------
+int fail(int code, const char* fmt, ...);
+void count_launch(bool tcgen05);
+int check_launch(const char* what);
+// Per-device int the kernels raise when a bounded wait gives up.
+int* device_error_flag();
+
+// ---- dtype helpers ------------------------------------------------------------
+__host__ __device__ inline int dtype_size(int dtype) { return dtype == CT_F32 ? 4 : 2; }
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+// Round an fp32 value to T and widen it back.
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
+
+__device__ __forceinline__ float load_as_float(const void* p, int64_t i, int dtype) {
+  if (dtype == CT_F32) return static_cast<const float*>(p)[i];
+  if (dtype == CT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__device__ __forceinline__ void store_from_float(void* p, int64_t i, int dtype, float v) {
+  if (dtype == CT_F32) static_cast<float*>(p)[i] = v;
+  else if (dtype == CT_BF16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+__device__ __forceinline__ float round_dtype(float v, int dtype) {
+  if (dtype == CT_F32) return v;
+  if (dtype == CT_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return __half2float(__float2half_rn(v));
+}
+
+// ---- GEMM description shared by the SIMT and tcgen05 kernels ------------------
+// D[M, N] = (beta ? D : 0) + sum over segments s of A_s[M, k_s] * B_s[k_s, N] + bias[N]
+// then (optionally)  D = round(D) + residual, rounded again.
+// Element (m, k) of A_s is at a[m * a_rs + k * a_cs]; element (k, n) of B_s at
+// b[k * b_rs + n * b_cs]. One stride of each pair is 1.
+constexpr int kMaxSegments = 4;
+
+struct Segment {
+  const void* a;
+  int64_t a_rs, a_cs;
+  const void* b;
+  int64_t b_rs, b_cs;
+  int64_t k;
+};
+
+struct GemmArgs {
+  int64_t M, N;
+  int nseg;
+  Segment seg[kMaxSegments];
+  int in_dtype;        // CT_BF16 / CT_F32 (SIMT only) for every A_s and B_s
+  void* out;
+  int64_t ldo;
+  int out_dtype;
+  int beta;            // 1: accumulate onto the existing `out`
+  const void* bias;    // [N] in in_dtype, or null
+  const void* residual;  // [M, N] in out_dtype, or null
+  int64_t ld_res;
+  int split_k;         // >1: slice s writes fp32 partials to out + s*M*ldo (tcgen05, 1 segment)
+};
+
+int gemm_simt(const GemmArgs& g, cudaStream_t stream);
+// Returns CT_ERR_UNSUPPORTED (without launching) when a TMA rule is not met.
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream);
+bool gemm_tcgen05_supported(const GemmArgs& g);
+int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream);
+
+// out[i] = (add ? out[i] : 0) + partial[0][i] + partial[1][i] + ... in that order.
+int reduce_partials(const float* partials, int slices, int64_t rows, int64_t cols, int64_t ld_partial,
+                    float* out, int64_t ld_out, int add, cudaStream_t stream);
+
+}  // namespace ct

@@ -1,0 +1,306 @@
+// HBM-bound elementwise kernels of the projection / MLP path: dtype casts of the
+// LoRA factors, the SwiGLU product and its in-place backward, adjacent-pair
+// RoPE, the residual add and the ordered reduction of split-contraction
+// partial sums. All are grid-stride loops over 16-byte vectors where the
+// buffers allow it.
+#include "common.cuh"
+
+namespace ct {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline unsigned grid_for(int64_t work_items) {
+  // Enough CTAs to fill 148 SMs eight times over, never more than the work.
+  int64_t blocks = (work_items + kThreads - 1) / kThreads;
+  const int64_t cap = 148 * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<unsigned>(blocks);
+}
+
+// ---- cast ---------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+cast_kernel(const void* src, int src_dtype, int64_t ld_src, void* dst, int dst_dtype, int64_t ld_dst,
+            int64_t rows, int64_t cols) {
+  const int64_t total = rows * cols;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t r = i / cols, c = i - r * cols;
+    store_from_float(dst, r * ld_dst + c, dst_dtype, load_as_float(src, r * ld_src + c, src_dtype));
+  }
+}
+
+// fp32 -> bf16, contiguous, 8 elements per thread per step.
+__global__ void __launch_bounds__(kThreads)
+cast_f32_bf16_vec_kernel(const float4* __restrict__ src, uint4* __restrict__ dst, int64_t groups) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < groups;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const float4 lo = __ldg(src + 2 * i), hi = __ldg(src + 2 * i + 1);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, lo.y), p1 = __floats2bfloat162_rn(lo.z, lo.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(hi.x, hi.y), p3 = __floats2bfloat162_rn(hi.z, hi.w);
+    dst[i] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                        *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+  }
+}
+
+// ---- SwiGLU ---------------------------------------------------------------------
+// One scalar element of kernels/mlp_cuda.py:10-25.
+template <typename T>
+__device__ __forceinline__ void swiglu_element(float g, float u, float grad, bool backward, bool reconstruct,
+                                               float& h, float& dg, float& du) {
+  const float sig = 1.0f / (1.0f + __expf(-g));
+  const float activated = round_to<T>(g * sig);
+  if (backward) {
+    const float product_grad = round_to<T>(grad * u);
+    dg = product_grad * (sig * (1.0f + g * (1.0f - sig)));
+    du = grad * activated;
+  }
+  if (reconstruct) h = activated * u;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+swiglu_kernel(const T* gate, const T* up, const T* grad, T* out, T* dg, T* du, int64_t n, int reconstruct) {
+  const bool backward = grad != nullptr;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const float g = to_float<T>(gate[i]), u = to_float<T>(up[i]);
+    const float gr = backward ? to_float<T>(grad[i]) : 0.0f;
+    float h = 0.f, a = 0.f, b = 0.f;
+    swiglu_element<T>(g, u, gr, backward, reconstruct != 0, h, a, b);
+    if (backward) {
+      dg[i] = from_float<T>(a);
+      du[i] = from_float<T>(b);
+    }
+    if (reconstruct) out[i] = from_float<T>(h);
+  }
+}
+
+// bf16, 8 elements (16 bytes) per thread per step; every buffer 16-byte aligned, n % 8 == 0.
+__global__ void __launch_bounds__(kThreads)
+swiglu_bf16_vec_kernel(const uint4* gate, const uint4* up, const uint4* grad, uint4* out, uint4* dg, uint4* du,
+                       int64_t groups, int reconstruct) {
+  const bool backward = grad != nullptr;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < groups;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const uint4 gv = gate[i], uv = up[i];
+    uint4 rv = make_uint4(0, 0, 0, 0);
+    if (backward) rv = grad[i];
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t hw[4], aw[4], bw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[j]));
+      const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[j]));
+      const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+      float h0 = 0.f, h1 = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+      swiglu_element<__nv_bfloat16>(g.x, u.x, r.x, backward, reconstruct != 0, h0, a0, b0);
+      swiglu_element<__nv_bfloat16>(g.y, u.y, r.y, backward, reconstruct != 0, h1, a1, b1);
+      __nv_bfloat162 hp = __floats2bfloat162_rn(h0, h1), ap = __floats2bfloat162_rn(a0, a1),
+                     bp = __floats2bfloat162_rn(b0, b1);
+      hw[j] = *reinterpret_cast<uint32_t*>(&hp);
+      aw[j] = *reinterpret_cast<uint32_t*>(&ap);
+      bw[j] = *reinterpret_cast<uint32_t*>(&bp);
+    }
+    if (backward) {
+      dg[i] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+      du[i] = make_uint4(bw[0], bw[1], bw[2], bw[3]);
+    }
+    if (reconstruct) out[i] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+  }
+}
+
+// ---- RoPE -----------------------------------------------------------------------
+// One thread per (row, head, pair). kernels/core_cuda.py:134-164.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rope_kernel(const T* x, const T* cosine, const T* sine, T* y, int64_t rows, int heads, int head_dim, int half,
+            int inverse) {
+  const int pairs_per_head = head_dim / 2;
+  const int64_t total = rows * heads * pairs_per_head;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int channel = static_cast<int>(i % pairs_per_head);
+    const int64_t token = i / (static_cast<int64_t>(heads) * pairs_per_head);
+    const T even_raw = x[2 * i], odd_raw = x[2 * i + 1];
+    if (channel < half) {
+      const float even = to_float<T>(even_raw), odd = to_float<T>(odd_raw);
+      const float c = to_float<T>(cosine[token * half + channel]);
+      float s = to_float<T>(sine[token * half + channel]);
+      if (inverse) s = -s;
+      const float ec = round_to<T>(__fmul_rn(even, c)), os = round_to<T>(__fmul_rn(odd, s));
+      const float oc = round_to<T>(__fmul_rn(odd, c)), es = round_to<T>(__fmul_rn(even, s));
+      y[2 * i] = from_float<T>(__fsub_rn(ec, os));
+      y[2 * i + 1] = from_float<T>(__fadd_rn(oc, es));
+    } else {
+      y[2 * i] = even_raw;
+      y[2 * i + 1] = odd_raw;
+    }
+  }
+}
+
+// ---- residual add -----------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads) add_kernel(T* y, const T* r, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * kThreads)
+    y[i] = from_float<T>(__fadd_rn(to_float<T>(y[i]), to_float<T>(r[i])));
+}
+
+__global__ void __launch_bounds__(kThreads) add_bf16_vec_kernel(uint4* y, const uint4* r, int64_t groups) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < groups;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const uint4 a = y[i], b = __ldg(r + i);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[j]));
+      const float2 q = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[j]));
+      __nv_bfloat162 o = __floats2bfloat162_rn(__fadd_rn(p.x, q.x), __fadd_rn(p.y, q.y));
+      ow[j] = *reinterpret_cast<uint32_t*>(&o);
+    }
+    y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
+// ---- ordered reduction of split-contraction partial sums ---------------------------
+__global__ void __launch_bounds__(kThreads)
+reduce_partials_kernel(const float* __restrict__ partials, int slices, int64_t rows, int64_t cols,
+                       int64_t ld_partial, float* out, int64_t ld_out, int add) {
+  const int64_t total = rows * cols;
+  const int64_t slice_stride = rows * ld_partial;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t r = i / cols, c = i - r * cols;
+    float acc = add ? out[r * ld_out + c] : 0.0f;
+    const float* p = partials + r * ld_partial + c;
+    for (int s = 0; s < slices; ++s) acc = __fadd_rn(acc, p[s * slice_stride]);
+    out[r * ld_out + c] = acc;
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+int reduce_partials(const float* partials, int slices, int64_t rows, int64_t cols, int64_t ld_partial, float* out,
+                    int64_t ld_out, int add, cudaStream_t stream) {
+  if (rows * cols == 0) return CT_OK;
+  reduce_partials_kernel<<<grid_for(rows * cols), kThreads, 0, stream>>>(partials, slices, rows, cols, ld_partial, out,
+                                                                        ld_out, add);
+  count_launch(false);
+  return check_launch("reduce_partials");
+}
+
+}  // namespace ct
+
+using namespace ct;
+
+extern "C" int ct_cast(const void* src, int src_dtype, int64_t ld_src, void* dst, int dst_dtype, int64_t ld_dst,
+                       int64_t rows, int64_t cols, void* stream) {
+  if (rows < 0 || cols < 0) return fail(CT_ERR_ARG, "ct_cast: negative size");
+  if (rows * cols == 0) return CT_OK;
+  if (!src || !dst) return fail(CT_ERR_ARG, "ct_cast: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * cols;
+  if (src_dtype == CT_F32 && dst_dtype == CT_BF16 && ld_src == cols && ld_dst == cols && total % 8 == 0 &&
+      aligned16(src) && aligned16(dst)) {
+    cast_f32_bf16_vec_kernel<<<grid_for(total / 8), kThreads, 0, s>>>(static_cast<const float4*>(src),
+                                                                     static_cast<uint4*>(dst), total / 8);
+  } else {
+    cast_kernel<<<grid_for(total), kThreads, 0, s>>>(src, src_dtype, ld_src, dst, dst_dtype, ld_dst, rows, cols);
+  }
+  count_launch(false);
+  return check_launch("ct_cast");
+}
+
+extern "C" int ct_swiglu(const void* gate, const void* up, const void* grad, void* out, void* dg, void* du, int64_t n,
+                         int dtype, int reconstruct, void* stream) {
+  if (n < 0) return fail(CT_ERR_ARG, "ct_swiglu: negative size");
+  if (n == 0) return CT_OK;
+  if (!gate || !up || (reconstruct && !out) || (grad && (!dg || !du))) return fail(CT_ERR_ARG, "ct_swiglu: null pointer");
+  if (!grad && !reconstruct) return fail(CT_ERR_ARG, "ct_swiglu: nothing to compute");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == CT_BF16) {
+    const bool vec = n % 8 == 0 && aligned16(gate) && aligned16(up) && (!grad || aligned16(grad)) &&
+                     (!reconstruct || aligned16(out)) && (!grad || (aligned16(dg) && aligned16(du)));
+    if (vec)
+      swiglu_bf16_vec_kernel<<<grid_for(n / 8), kThreads, 0, s>>>(
+          static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<const uint4*>(grad),
+          static_cast<uint4*>(out), static_cast<uint4*>(dg), static_cast<uint4*>(du), n / 8, reconstruct);
+    else
+      swiglu_kernel<__nv_bfloat16><<<grid_for(n), kThreads, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+          static_cast<const __nv_bfloat16*>(grad), static_cast<__nv_bfloat16*>(out),
+          static_cast<__nv_bfloat16*>(dg), static_cast<__nv_bfloat16*>(du), n, reconstruct);
+  } else if (dtype == CT_F32) {
+    swiglu_kernel<float><<<grid_for(n), kThreads, 0, s>>>(static_cast<const float*>(gate), static_cast<const float*>(up),
+                                                          static_cast<const float*>(grad), static_cast<float*>(out),
+                                                          static_cast<float*>(dg), static_cast<float*>(du), n,
+                                                          reconstruct);
+  } else if (dtype == CT_F16) {
+    swiglu_kernel<__half><<<grid_for(n), kThreads, 0, s>>>(static_cast<const __half*>(gate),
+                                                           static_cast<const __half*>(up),
+                                                           static_cast<const __half*>(grad), static_cast<__half*>(out),
+                                                           static_cast<__half*>(dg), static_cast<__half*>(du), n,
+                                                           reconstruct);
+  } else {
+    return fail(CT_ERR_ARG, "ct_swiglu: dtype %d", dtype);
+  }
+  count_launch(false);
+  return check_launch("ct_swiglu");
+}
+
+extern "C" int ct_rope(const void* x, const void* cosine, const void* sine, void* y, int64_t rows, int heads,
+                       int head_dim, int half, int inverse, int dtype, void* stream) {
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || (head_dim & 1) || half < 0 || 2 * half > head_dim)
+    return fail(CT_ERR_ARG, "ct_rope: rows=%lld heads=%d head_dim=%d half=%d", (long long)rows, heads, head_dim, half);
+  if (rows == 0) return CT_OK;
+  if (!x || !y || (half && (!cosine || !sine))) return fail(CT_ERR_ARG, "ct_rope: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * heads * (head_dim / 2);
+  if (dtype == CT_BF16)
+    rope_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cosine),
+        static_cast<const __nv_bfloat16*>(sine), static_cast<__nv_bfloat16*>(y), rows, heads, head_dim, half, inverse);
+  else if (dtype == CT_F32)
+    rope_kernel<float><<<grid_for(total), kThreads, 0, s>>>(static_cast<const float*>(x),
+                                                            static_cast<const float*>(cosine),
+                                                            static_cast<const float*>(sine), static_cast<float*>(y),
+                                                            rows, heads, head_dim, half, inverse);
+  else if (dtype == CT_F16)
+    rope_kernel<__half><<<grid_for(total), kThreads, 0, s>>>(static_cast<const __half*>(x),
+                                                             static_cast<const __half*>(cosine),
+                                                             static_cast<const __half*>(sine), static_cast<__half*>(y),
+                                                             rows, heads, head_dim, half, inverse);
+  else
+    return fail(CT_ERR_ARG, "ct_rope: dtype %d", dtype);
+  count_launch(false);
+  return check_launch("ct_rope");
+}
+
+extern "C" int ct_add_inplace(void* y, const void* r, int64_t n, int dtype, void* stream) {
+  if (n < 0) return fail(CT_ERR_ARG, "ct_add_inplace: negative size");
+  if (n == 0) return CT_OK;
+  if (!y || !r) return fail(CT_ERR_ARG, "ct_add_inplace: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == CT_BF16) {
+    if (n % 8 == 0 && aligned16(y) && aligned16(r))
+      add_bf16_vec_kernel<<<grid_for(n / 8), kThreads, 0, s>>>(static_cast<uint4*>(y), static_cast<const uint4*>(r),
+                                                               n / 8);
+    else
+      add_kernel<__nv_bfloat16><<<grid_for(n), kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(y),
+                                                                 static_cast<const __nv_bfloat16*>(r), n);
+  } else if (dtype == CT_F32) {
+    add_kernel<float><<<grid_for(n), kThreads, 0, s>>>(static_cast<float*>(y), static_cast<const float*>(r), n);
+  } else if (dtype == CT_F16) {
+    add_kernel<__half><<<grid_for(n), kThreads, 0, s>>>(static_cast<__half*>(y), static_cast<const __half*>(r), n);
+  } else {
+    return fail(CT_ERR_ARG, "ct_add_inplace: dtype %d", dtype);
+  }
+  count_launch(false);
+  return check_launch("ct_add_inplace");
+}

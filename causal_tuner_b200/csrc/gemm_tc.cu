@@ -1,0 +1,595 @@
+// bf16 matrix product on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+//   D[M, N] = (beta ? D : 0) + sum_s A_s[M, k_s] . B_s[k_s, N] + bias, optional residual
+//
+// Persistent kernel, one CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: one lane streams 128x64 A tiles and 256x64 B tiles
+//               (bf16, 128-byte swizzle) into a 4-stage shared-memory ring;
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=256, K=16) from
+//               shared-memory descriptors into one of two fp32 accumulators in
+//               TMEM (2 x 256 columns), releasing ring stages with tcgen05.commit;
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp owns the 32
+//               TMEM lanes of its lane quarter), add bias / previous value /
+//               residual, round, and store 64-byte row segments to global memory
+//               while the MMA warp already works on the next tile in the other
+//               accumulator.
+// The contraction may be a concatenation of up to four (A_s, B_s) segments, each
+// with its own pair of tensor maps: the LoRA term x.A^T.B^T rides in the same
+// accumulator as the base product as [x | xa] . [W | B]^T, and dX sums
+// dY.W + low.A the same way. Each operand may be K-major (contraction index
+// contiguous) or MN-major (row/column index contiguous); MN-major tiles arrive as
+// 64x64 TMA boxes and are described to the tensor core with the MN-major
+// canonical layout, so W[N, K] serves both the forward and the dX product and
+// the token-contracted dA/dB products need no transposed copies.
+// A contraction can also be split into `splits` slices whose fp32 partial tiles
+// go to separate planes (summed afterwards in a fixed order).
+//
+// Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA
+// raises the device error flag, stops issuing work, frees its TMEM and exits.
+// No TMA load in this file uses cluster multicast.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace ct {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
+constexpr uint32_t B_TILE_BYTES = BN * BK * 2;  // 32 KB
+constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr uint32_t MN_BOX_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
+constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulators
+constexpr int GROUP_M = 16;                     // tile rasterisation: 16 row tiles share a sweep over columns
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+struct TcSegment {
+  CUtensorMap a, b;
+  int k_blocks;
+  int a_mn, b_mn;
+};
+
+struct TcParams {
+  TcSegment seg[kMaxSegments];
+  int nseg;
+  int k_blocks_total;
+  int splits;
+  int m_tiles, n_tiles;
+  int64_t M, N;
+  void* out;
+  int64_t ldo;
+  int64_t split_stride;  // elements between partial planes
+  int out_f32;
+  int beta;
+  int vec_store;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int64_t ld_res;
+  int* error_flag;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait. Returns false after kWaitLimitNs, having raised the error flag
+// with `code` (which names the waiting role).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(error_flag, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+// Offsets are in bytes; the hardware fields hold them divided by 16.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  uint64_t d = static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256.
+__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+         (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+struct TileCoord {
+  int m, n, split;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, const TcParams& p) {
+  const int per_split = p.m_tiles * p.n_tiles;
+  TileCoord c;
+  c.split = tile / per_split;
+  const int rem = tile - c.split * per_split;
+  const int per_group = GROUP_M * p.n_tiles;
+  const int group = rem / per_group;
+  const int first_m = group * GROUP_M;
+  const int group_rows = min(GROUP_M, p.m_tiles - first_m);
+  const int in_group = rem - group * per_group;
+  c.m = first_m + in_group % group_rows;
+  c.n = in_group / group_rows;
+  return c;
+}
+
+// k-block range [begin, end) of one split over the concatenated contraction.
+__device__ __forceinline__ void split_range(const TcParams& p, int split, int& begin, int& end) {
+  const int base = p.k_blocks_total / p.splits, extra = p.k_blocks_total % p.splits;
+  begin = split * base + min(split, extra);
+  end = begin + base + (split < extra ? 1 : 0);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars: [0, STAGES) full, [STAGES, 2*STAGES) empty, then tmem_full[2], tmem_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, p);
+        int kb_begin, kb_end;
+        split_range(p, tc.split, kb_begin, kb_end);
+        int seg = 0, seg_first = 0;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          while (kb >= seg_first + p.seg[seg].k_blocks) {
+            seg_first += p.seg[seg].k_blocks;
+            ++seg;
+          }
+          const int k0 = (kb - seg_first) * BK;
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.error_flag, 1)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          const TcSegment& sg = p.seg[seg];
+          if (!sg.a_mn) {
+            tma_load_2d(a_dst, &sg.a, full_bar(stage), k0, tc.m * BM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(a_dst + j * MN_BOX_BYTES, &sg.a, full_bar(stage), tc.m * BM + j * 64, k0);
+          }
+          if (!sg.b_mn) {
+            tma_load_2d(b_dst, &sg.b, full_bar(stage), k0, tc.n * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * MN_BOX_BYTES, &sg.b, full_bar(stage), tc.n * BN + j * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++local_tile) {
+        const TileCoord tc = tile_coord(tile, p);
+        int kb_begin, kb_end;
+        split_range(p, tc.split, kb_begin, kb_end);
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.error_flag, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        int seg = 0, seg_first = 0;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          while (kb >= seg_first + p.seg[seg].k_blocks) {
+            seg_first += p.seg[seg].k_blocks;
+            ++seg;
+          }
+          const TcSegment& sg = p.seg[seg];
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.error_flag, 3)) {
+            alive = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * STAGE_BYTES, b_src = a_src + A_TILE_BYTES;
+          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn);
+          // K-major: 8-row groups 1024 B apart, 32 B per 16-element k step inside the swizzle atom.
+          // MN-major: 64-wide column groups one box (8 KB) apart, 8-k groups 1024 B apart,
+          //           16 k rows (2 KB) per k step.
+          const uint64_t a_desc = sg.a_mn ? smem_desc(a_src, MN_BOX_BYTES, 1024) : smem_desc(a_src, 16, 1024);
+          const uint64_t b_desc = sg.b_mn ? smem_desc(b_src, MN_BOX_BYTES, 1024) : smem_desc(b_src, 16, 1024);
+          const uint64_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
+          const uint64_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j)
+            umma_bf16(tmem_d, a_desc + a_step * j, b_desc + b_step * j, idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (alive) umma_commit(tmem_full_bar(acc));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    int local_tile = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+      const TileCoord tc = tile_coord(tile, p);
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.error_flag, 4) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int64_t row = static_cast<int64_t>(tc.m) * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      char* out_plane = static_cast<char*>(p.out) +
+                        static_cast<int64_t>(tc.split) * p.split_stride * (p.out_f32 ? 4 : 2);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t raw[32];
+        tmem_load_32(taddr + c * 32, raw);
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        const bool full = col0 + 32 <= p.N;
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (p.out_f32) {
+          float* dst = reinterpret_cast<float*>(out_plane) + row * p.ldo + col0;
+          if (full && p.vec_store) {
+            float4* d4 = reinterpret_cast<float4*>(dst);
+            if (p.beta) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 o = d4[q];
+                v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = p.beta ? dst[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_plane) + row * p.ldo + col0;
+          const __nv_bfloat16* res = p.residual ? p.residual + row * p.ld_res + col0 : nullptr;
+          if (full && p.vec_store) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+            if (p.beta) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 o = d4[q];
+                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                  v[8 * q + 2 * j] += f.x;
+                  v[8 * q + 2 * j + 1] += f.y;
+                }
+              }
+            }
+            if (res) {
+              const uint4* r4 = reinterpret_cast<const uint4*>(res);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 o = __ldg(r4 + q);
+                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                  v[8 * q + 2 * j] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j])), f.x);
+                  v[8 * q + 2 * j + 1] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j + 1])), f.y);
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              d4[q] = make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
+                                 pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+              float x = v[j];
+              if (p.beta) x += __bfloat162float(dst[j]);
+              if (res) x = __fadd_rn(__bfloat162float(__float2bfloat16_rn(x)), __bfloat162float(res[j]));
+              dst[j] = __float2bfloat16_rn(x);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------
+constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }();
+  return fn;
+}
+
+// Tensor map over a bf16 matrix whose contiguous dimension has `inner` elements and
+// whose rows are `ld` elements apart; tiles are `box_rows` rows of 64 elements.
+int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_rows) {
+  auto fn = encode_fn();
+  if (!fn) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
+  return CT_OK;
+}
+
+bool operand_ok(const void* ptr, int64_t rs, int64_t cs) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return false;
+  const int64_t ld = (cs == 1) ? rs : cs;
+  if (rs != 1 && cs != 1) return false;
+  return ld % 8 == 0 && ld > 0;
+}
+
+int sm_count() {
+  static int count = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return n;
+  }();
+  return count;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supported(const GemmArgs& g) {
+  if (g.in_dtype != CT_BF16) return false;
+  if (g.out_dtype != CT_BF16 && g.out_dtype != CT_F32) return false;
+  if (g.M <= 0 || g.N <= 0 || g.nseg < 1 || g.nseg > kMaxSegments) return false;
+  if (g.M > (1LL << 31) - BM || g.N > (1LL << 31) - BN) return false;
+  int64_t k_blocks = 0;
+  for (int s = 0; s < g.nseg; ++s) {
+    const Segment& sg = g.seg[s];
+    if (sg.k <= 0 || sg.k > (1LL << 31) - BK) return false;
+    if (!operand_ok(sg.a, sg.a_rs, sg.a_cs) || !operand_ok(sg.b, sg.b_cs, sg.b_rs)) return false;
+    // A dimension of extent 1 makes "which stride is 1" ambiguous; leave those to the SIMT kernel.
+    if (sg.a_rs == 1 && sg.a_cs == 1) return false;
+    if (sg.b_rs == 1 && sg.b_cs == 1) return false;
+    k_blocks += (sg.k + BK - 1) / BK;
+  }
+  if (g.residual && (g.out_dtype != CT_BF16 || g.beta)) return false;
+  const int splits = g.split_k > 1 ? g.split_k : 1;
+  if (splits > 1 && (g.out_dtype != CT_F32 || g.beta || g.bias || g.residual)) return false;
+  if (k_blocks < splits) return false;
+  const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * splits;
+  return tiles < (1LL << 30);
+}
+
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
+  if (!gemm_tcgen05_supported(g)) return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05: operands break a TMA rule");
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(CT_ERR_CUDA, "gemm_tcgen05: no current device");
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kSmemBytes)) != cudaSuccess)
+      return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", kSmemBytes,
+                  cudaGetErrorString(cudaGetLastError()));
+    configured[device] = true;
+  }
+  TcParams p;
+  p.nseg = g.nseg;
+  p.k_blocks_total = 0;
+  for (int s = 0; s < g.nseg; ++s) {
+    const Segment& sg = g.seg[s];
+    TcSegment& t = p.seg[s];
+    t.k_blocks = static_cast<int>((sg.k + BK - 1) / BK);
+    p.k_blocks_total += t.k_blocks;
+    t.a_mn = sg.a_cs == 1 ? 0 : 1;
+    t.b_mn = sg.b_rs == 1 ? 0 : 1;
+    int rc;
+    // K-major: contiguous index is k, rows are m (or n). MN-major: contiguous index is m (or n), rows are k.
+    rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM);
+    if (rc != CT_OK) return rc;
+    rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK) : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, BN);
+    if (rc != CT_OK) return rc;
+  }
+  p.splits = g.split_k > 1 ? g.split_k : 1;
+  p.m_tiles = static_cast<int>((g.M + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
+  p.M = g.M;
+  p.N = g.N;
+  p.out = g.out;
+  p.ldo = g.ldo;
+  p.split_stride = g.M * g.ldo;
+  p.out_f32 = g.out_dtype == CT_F32;
+  p.beta = g.beta;
+  const int vec = p.out_f32 ? 4 : 8;
+  p.vec_store = (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && g.ldo % vec == 0 &&
+                (!g.residual || ((reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 && g.ld_res % 8 == 0));
+  p.bias = static_cast<const __nv_bfloat16*>(g.bias);
+  p.residual = static_cast<const __nv_bfloat16*>(g.residual);
+  p.ld_res = g.ld_res;
+  p.error_flag = device_error_flag();
+  if (!p.error_flag) return fail(CT_ERR_CUDA, "gemm_tcgen05: no device error flag");
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.splits;
+  int sms = sm_count();
+  if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot read the SM count");
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  count_launch(true);
+  return check_launch("gemm_tcgen05");
+}
+
+int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {
+  if (g.M == 0 || g.N == 0) return CT_OK;
+  if (path == CT_PATH_SIMT) return gemm_simt(g, stream);
+  if (path == CT_PATH_TCGEN05) return gemm_tcgen05(g, stream);
+  if (path != CT_PATH_AUTO) return fail(CT_ERR_ARG, "unknown path %d", path);
+  return gemm_tcgen05_supported(g) ? gemm_tcgen05(g, stream) : gemm_simt(g, stream);
+}
+
+}  // namespace ct

@@ -1,0 +1,323 @@
+"""Frozen-base projection with NF4 decode and rank-r LoRA, forward and analytic backward.
+
+Drop-in for the reference's kernels/linear.py: the same module-level names with the same
+arguments, ownership rules and error behaviour, so callers and tests written against the
+reference work unchanged. The arithmetic runs in libct_b200.so:
+
+* ``forward_linear``      -> ct_forward_linear   (xa = x.A^T, then ONE tcgen05 GEMM over the
+                             concatenated contraction [x | xa].[W | B]^T with bias and
+                             residual in the epilogue)
+* ``input_gradient``      -> ct_input_gradient   (low = dy.B, then ONE GEMM [dy | low].[W ; A])
+* ``parameter_gradients`` -> ct_parameter_gradients (token-contracted fp32 dA / dB, fixed
+                             summation order)
+* ``accumulate``          -> ct_matmul
+* ``materialize``         -> ct_nf4_decode / ct_cast
+
+Differences from the reference that callers can observe: outputs are rounded to the compute
+dtype once per GEMM (the reference rounds after the base product and again after the
+low-rank update), and `tile` only bounds workspaces - tile 0 runs all rows in one launch.
+"""
+
+import torch
+
+from .. import _lib
+from . import core_cuda
+
+
+# ---- tensor plumbing --------------------------------------------------------------------
+
+def cast(tensor, dtype):
+    """`tensor.to(dtype)` through ct_cast; returns the tensor itself when the dtype already matches."""
+    if tensor is None or tensor.dtype == dtype:
+        return tensor
+    _lib.require_cuda(tensor)
+    source = tensor.contiguous()
+    output = torch.empty(source.shape, device=source.device, dtype=dtype)
+    count = source.numel()
+    if count:
+        with _lib.on_device(source):
+            _lib.check(_lib.load().ct_cast(source.data_ptr(), _lib.code_of(source.dtype), count, output.data_ptr(),
+                                          _lib.code_of(dtype), count, 1, count, _lib.stream_of(source)))
+    return output
+
+
+def _leading(tensor):
+    """Leading dimension (elements between rows) of a 2-D tensor whose rows are contiguous."""
+    return tensor.stride(0) if tensor.shape[0] > 1 else max(tensor.shape[1], 1)
+
+
+def _readable(tensor):
+    if tensor.dim() != 2:
+        raise ValueError("expected a matrix")
+    if tensor.shape[1] > 1 and tensor.stride(1) != 1 or (tensor.shape[0] > 1 and tensor.stride(0) < tensor.shape[1]):
+        tensor = tensor.contiguous()
+    return tensor
+
+
+def _writable(tensor, name):
+    if tensor.dim() != 2 or (tensor.shape[1] > 1 and tensor.stride(1) != 1):
+        raise ValueError(f"{name} must be a matrix with contiguous rows")
+    return tensor
+
+
+def _strides(tensor):
+    """Element strides (row, column) with a unit stride wherever the extent is 1."""
+    rs = tensor.stride(0) if tensor.shape[0] > 1 else None
+    cs = tensor.stride(1) if tensor.shape[1] > 1 else None
+    if rs is None and cs is None:
+        return 1, 1
+    if rs is None:
+        return (tensor.shape[1] * cs if cs != 1 else tensor.shape[1]), cs
+    if cs is None:
+        return rs, (1 if rs != 1 else tensor.shape[0])
+    return rs, cs
+
+
+def matmul(left, right, *, out, add=False):
+    """out[m, n] = (add ? out : 0) + left[m, k] @ right[k, n]; any strides, fp32 accumulation."""
+    _lib.require_cuda(left, right, out)
+    _writable(out, "out")
+    if right.dtype != left.dtype:
+        right = cast(right, left.dtype)
+    (a_rs, a_cs), (b_rs, b_cs) = _strides(left), _strides(right)
+    if a_rs != 1 and a_cs != 1:
+        left = left.contiguous()
+        a_rs, a_cs = _strides(left)
+    if b_rs != 1 and b_cs != 1:
+        right = right.contiguous()
+        b_rs, b_cs = _strides(right)
+    m, k = left.shape
+    n = right.shape[1]
+    if right.shape[0] != k or out.shape != (m, n):
+        raise ValueError("matmul shape mismatch")
+    with _lib.on_device(out):
+        _lib.check(_lib.load().ct_matmul(left.data_ptr(), a_rs, a_cs, right.data_ptr(), b_rs, b_cs, out.data_ptr(),
+                                        _leading(out), m, n, k, _lib.code_of(left.dtype), _lib.code_of(out.dtype),
+                                        int(bool(add)), _lib.gemm_path, _lib.stream_of(out)))
+    return out
+
+
+# ---- the reference's primitives -----------------------------------------------------------
+
+def materialize(weight, state, dtype):
+    """Dense `dtype` copy of a base weight: NF4 decode when `state` is given, else a cast.
+
+    Mirrors kernels/linear.py:6-13. Without bitsandbytes there is exactly one quantised
+    format: contiguous uint8 NF4 on a CUDA device; anything else is an error, not a fallback.
+    """
+    if state is not None:
+        if weight.is_cuda and weight.dtype == torch.uint8 and weight.is_contiguous() and state.quant_type == "nf4":
+            from .nf4_cuda import dequantize_nf4
+            return dequantize_nf4(weight, state, dtype)
+        raise RuntimeError("only contiguous uint8 NF4 weights on a CUDA device can be decoded")
+    return cast(weight, dtype)
+
+
+def accumulate(output, left, right, *, add=True):
+    """output (+)= left @ right with fp32 accumulation (kernels/linear.py:16-24). With add=False the
+    previous contents of `output` are never read."""
+    matmul(left, right, out=output, add=add)
+
+
+def forward_linear(x, weight, a, b, *, out, xa, bias=None, residual=None):
+    """out = x @ weight.T + bias + (x @ a.T) @ b.T [+ residual]; also leaves xa = x @ a.T.
+
+    kernels/linear.py:27-33. `residual`, when given, is added to the rounded output and the sum
+    rounded again - the result of the reference's separate in-place add (kernels/linear.py:90-91).
+    """
+    _lib.require_cuda(x, weight, out)
+    x, weight = _readable(x), _readable(weight)
+    _writable(out, "out")
+    rows, inner = x.shape
+    outer = weight.shape[0]
+    rank = a.shape[0] if a is not None else 0
+    if rank:
+        a, b = a.contiguous(), b.contiguous()
+        _writable(xa, "xa")
+    if residual is not None:
+        residual = _readable(residual)
+    with _lib.on_device(x):
+        _lib.check(_lib.load().ct_forward_linear(
+            x.data_ptr(), _leading(x), weight.data_ptr(), _leading(weight), _lib.pointer(a if rank else None),
+            _lib.pointer(b if rank else None), _lib.pointer(bias), _lib.pointer(residual),
+            _leading(residual) if residual is not None else 0, out.data_ptr(), _leading(out),
+            _lib.pointer(xa if rank else None), _leading(xa) if rank else 0, rows, inner, outer, rank,
+            _lib.code_of(x.dtype), _lib.gemm_path, _lib.stream_of(x)))
+
+
+def input_gradient(dy, weight, a, b, dx, low, *, add=False):
+    """low = dy @ b; dx = (add ? dx : 0) + dy @ weight + low @ a (kernels/linear.py:36-39)."""
+    _lib.require_cuda(dy, weight, dx, low)
+    dy, weight = _readable(dy), _readable(weight)
+    _writable(dx, "dx")
+    _writable(low, "low")
+    a, b = a.contiguous(), b.contiguous()
+    rows, outer = dy.shape
+    inner, rank = weight.shape[1], a.shape[0]
+    with _lib.on_device(dy):
+        _lib.check(_lib.load().ct_input_gradient(
+            dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), b.data_ptr(),
+            dx.data_ptr(), _leading(dx), low.data_ptr(), _leading(low), rows, inner, outer, rank, int(bool(add)),
+            _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
+
+
+def parameter_gradients(x, dy, da, db, low, xa, *, add):
+    """da (+)= low.T @ x and db (+)= dy.T @ xa in fp32 (kernels/linear.py:42-44), summed in a fixed order."""
+    _lib.require_cuda(x, dy, da, db, low, xa)
+    if da.dtype != torch.float32 or db.dtype != torch.float32 or not (da.is_contiguous() and db.is_contiguous()):
+        # Adapters kept in a 16-bit training dtype: accumulate in fp32 and round once.
+        da32 = da.float() if add else torch.empty(da.shape, device=da.device, dtype=torch.float32)
+        db32 = db.float() if add else torch.empty(db.shape, device=db.device, dtype=torch.float32)
+        parameter_gradients(x, dy, da32, db32, low, xa, add=add)
+        da.copy_(da32)
+        db.copy_(db32)
+        return
+    x, dy, low, xa = _readable(x), _readable(dy), _readable(low), _readable(xa)
+    rows, inner = x.shape
+    outer, rank = dy.shape[1], low.shape[1]
+    library = _lib.load()
+    code = _lib.code_of(x.dtype)
+    need = library.ct_parameter_gradients_workspace(rows, inner, outer, rank, code, _lib.gemm_path)
+    workspace = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
+    with _lib.on_device(x):
+        _lib.check(library.ct_parameter_gradients(
+            x.data_ptr(), _leading(x), dy.data_ptr(), _leading(dy), low.data_ptr(), _leading(low), xa.data_ptr(),
+            _leading(xa), da.data_ptr(), db.data_ptr(), rows, inner, outer, rank, int(bool(add)), code,
+            _lib.pointer(workspace), _lib.gemm_path, _lib.stream_of(x)))
+
+
+def projection_parameters(module):
+    """((weight, A, B, bias), quant_state or None) of a `Projection` (kernels/linear.py:47-50)."""
+    weight = module.weight if module.quantized is None else module.quantized.weight
+    state = None if module.quantized is None else weight.quant_state
+    return (weight, module.lora_A, module.lora_B, module.bias), state
+
+
+def can_fuse(module, x):
+    """True when the fused operator applies: CUDA input, an adapter, frozen base weight and bias,
+    trainable A and B (kernels/linear.py:53-56)."""
+    return bool(x.is_cuda and module.rank and not (module.bias is not None and module.bias.requires_grad)
+                and (module.weight is None or not module.weight.requires_grad)
+                and module.lora_A.requires_grad and module.lora_B.requires_grad)
+
+
+class _LoRAGroup(torch.autograd.Function):
+    """One to three projections that share their input (q/k/v, or a single o/gate/up/down).
+
+    Saves only the input, the rotary table and the parameters (kernels/linear.py:62). The
+    backward pass decodes a base weight again only if the input gradient is wanted, rotates
+    upstream q/k gradients back into a private buffer, sums the input gradients of the group
+    and returns fp32 adapter gradients.
+    """
+
+    @staticmethod
+    def forward(ctx, x, dtype, tile, states, cosine, sine, head_dim, residual, *parameters):
+        _lib.require_cuda(x)
+        ctx.save_for_backward(x, cosine, sine, *parameters)
+        ctx.dtype, ctx.states, ctx.head_dim = dtype, states, head_dim
+        flat = cast(x.reshape(-1, x.shape[-1]), dtype)
+        rows = flat.shape[0]
+        ctx.tile = tile
+        step = max(1, min(tile, rows) if tile else rows)
+        widest = max(parameters[4 * i + 1].shape[0] for i in range(len(states)))
+        workspace = torch.empty((min(step, rows), widest), device=x.device, dtype=dtype)
+        fuse_residual = residual is not None and not head_dim
+        shortcut = residual.reshape(rows, residual.shape[-1]) if fuse_residual else None
+        outputs = []
+        for index, state in enumerate(states):
+            weight, a, b, bias = parameters[4 * index:4 * index + 4]
+            matrix = materialize(weight, state, dtype)
+            a16, b16, bias16 = cast(a, dtype), cast(b, dtype), cast(bias, dtype)
+            out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
+            for start in range(0, rows, step):
+                stop = min(start + step, rows)
+                forward_linear(flat[start:stop], matrix, a16, b16, bias=bias16, out=out[start:stop],
+                               xa=workspace[:stop - start, :a.shape[0]],
+                               residual=shortcut[start:stop] if fuse_residual and index == 0 else None)
+            outputs.append(out.reshape(*x.shape[:-1], matrix.shape[0]))
+            del matrix, a16, b16
+        if head_dim:
+            core_cuda.rotate_owned_qk(outputs[0], outputs[1], cosine, sine, head_dim)
+        if residual is not None and not fuse_residual:
+            _add_inplace(outputs[0], residual)
+        return tuple(outputs)
+
+    @staticmethod
+    def backward(ctx, *grad_outputs):
+        x, cosine, sine, *parameters = ctx.saved_tensors
+        dtype, states = ctx.dtype, ctx.states
+        flat = cast(x.reshape(-1, x.shape[-1]), dtype)
+        rows = flat.shape[0]
+        want_dx = ctx.needs_input_grad[0]
+        dx = torch.empty_like(flat) if want_dx else None
+        step = max(1, min(ctx.tile, rows) if ctx.tile else rows)
+        if ctx.head_dim:
+            cosine, sine = (value.reshape(-1, value.shape[-1]) for value in (cosine, sine))
+        widest = max(parameters[4 * i + 1].shape[0] for i in range(len(states)))
+        workspace = torch.empty((2, min(step, rows), widest), device=x.device, dtype=dtype)
+        rotary = None
+        if ctx.head_dim:
+            width = max(parameters[4 * i + 2].shape[0] for i in range(min(2, len(states))))
+            rotary = torch.empty(min(step, rows) * width, device=x.device, dtype=dtype)
+        results = []
+        for index, (state, grad) in enumerate(zip(states, grad_outputs)):
+            weight, a, b, _ = parameters[4 * index:4 * index + 4]
+            matrix = materialize(weight, state, dtype) if want_dx else None
+            a16, b16 = cast(a, dtype), cast(b, dtype)
+            dy = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
+            make = torch.empty_like if rows else torch.zeros_like
+            da, db = make(a), make(b)
+            rotate = bool(ctx.head_dim) and index < 2
+            for start in range(0, rows, step):
+                stop = min(start + step, rows)
+                signal = dy[start:stop]
+                if rotate:
+                    target = rotary[:signal.numel()].view_as(signal)
+                    signal = core_cuda.inverse_rope_tile(signal, cosine[start:stop], sine[start:stop], ctx.head_dim,
+                                                         target)
+                low = workspace[0, :stop - start, :a.shape[0]]
+                xa = workspace[1, :stop - start, :a.shape[0]]
+                if want_dx:
+                    input_gradient(signal, matrix, a16, b16, dx[start:stop], low, add=index > 0)
+                else:
+                    matmul(signal, b16, out=low)
+                matmul(flat[start:stop], a16.T, out=xa)
+                parameter_gradients(flat[start:stop], signal, da, db, low, xa, add=start > 0)
+            results.extend((None, da, db, None))
+            del matrix, a16, b16, dy
+        residual_grad = grad_outputs[0] if ctx.needs_input_grad[7] else None
+        dx_out = None if dx is None else cast(dx.reshape(x.shape), x.dtype)
+        return (dx_out, None, None, None, None, None, None, residual_grad, *results)
+
+
+def _add_inplace(target, other):
+    other = other.contiguous()
+    with _lib.on_device(target):
+        _lib.check(_lib.load().ct_add_inplace(target.data_ptr(), other.data_ptr(), target.numel(),
+                                             _lib.code_of(target.dtype), _lib.stream_of(target)))
+    return target
+
+
+def project_group(modules, x, tile=0, *, rotary=None, residual=None):
+    """Apply one to three LoRA projections to the same input (kernels/linear.py:133-148).
+
+    rotary = (cosine[..., half], sine[..., half], head_dim) rotates outputs 0 and 1 in place
+    before they become visible; `residual` is fused only for a single projection whose output
+    matches it in shape and dtype, otherwise it is added outside the operator.
+    """
+    if residual is not None:
+        if len(modules) != 1:
+            raise ValueError("Residual fusion requires one output projection")
+        shape = (*x.shape[:-1], len(modules[0].lora_B))
+        if residual.shape != shape or residual.dtype != modules[0].compute_dtype:
+            return (project_group(modules, x, tile, rotary=rotary)[0] + residual,)
+    parameters, states = [], []
+    for module in modules:
+        values, state = projection_parameters(module)
+        parameters.extend(values)
+        states.append(state)
+    cosine, sine, head_dim = (None, None, 0) if rotary is None else rotary
+    if rotary is not None:
+        cosine, sine = cosine.contiguous(), sine.contiguous()
+    return _LoRAGroup.apply(x, modules[0].compute_dtype, tile, tuple(states), cosine, sine, head_dim, residual,
+                            *parameters)

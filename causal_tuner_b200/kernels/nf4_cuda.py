@@ -1,0 +1,40 @@
+"""NF4 decode in one launch (drop-in for the reference's kernels/nf4_cuda.py)."""
+
+import torch
+
+from .. import _lib
+
+
+def dequantize_nf4(weight, state, dtype):
+    """Decode packed NF4 `weight` (uint8, two codes per byte) into a dense `dtype` tensor of `state.shape`.
+
+    Same contract as the reference's ``dequantize_nf4`` (kernels/nf4_cuda.py:32-43): plain or
+    nested (8-bit) absmax statistics, the fp32 product rounded to ``state.dtype`` and then to
+    ``dtype``, bit-exact with the reference decode.
+    """
+    _lib.require_cuda(weight)
+    if weight.dtype != torch.uint8 or not weight.is_contiguous():
+        raise ValueError("packed NF4 weights must be a contiguous uint8 tensor")
+    output = torch.empty(state.shape, device=weight.device, dtype=dtype)
+    nested = bool(state.nested)
+    auxiliary = state.state2 if nested else None
+    code = state.code if state.code.dtype == torch.float32 else state.code.float()
+    absmax = state.absmax
+    if nested:
+        if absmax.dtype != torch.uint8:
+            raise ValueError("nested NF4 statistics must be uint8")
+        code2 = auxiliary.code if auxiliary.code.dtype == torch.float32 else auxiliary.code.float()
+        absmax2 = auxiliary.absmax if auxiliary.absmax.dtype == torch.float32 else auxiliary.absmax.float()
+        offset = state.offset if state.offset.dtype == torch.float32 else state.offset.float()
+        extras = (code2.contiguous(), absmax2.contiguous(), offset.contiguous())
+    else:
+        if absmax.dtype != torch.float32:
+            absmax = absmax.float()
+        extras = (None, None, None)
+    absmax, code = absmax.contiguous(), code.contiguous()
+    with _lib.on_device(weight):
+        _lib.check(_lib.load().ct_nf4_decode(
+            weight.data_ptr(), absmax.data_ptr(), code.data_ptr(), *(_lib.pointer(t) for t in extras),
+            output.data_ptr(), output.numel(), int(state.blocksize), int(auxiliary.blocksize) if nested else 0,
+            int(nested), _lib.code_of(state.dtype), _lib.code_of(dtype), _lib.stream_of(weight)))
+    return output

@@ -1,0 +1,174 @@
+/*
+ * C ABI of libct_b200.so: the B200 (sm_100a) kernels behind causal-tuner's
+ * fused projection / SwiGLU-MLP operator layer.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the
+ *     current CUDA device unless a comment says otherwise;
+ *   - the caller owns every buffer (inputs, outputs and workspaces);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     kernels are enqueued on it and the call returns without synchronising;
+ *   - the return value is CT_OK (0) or a negative CT_ERR_* code; nothing is
+ *     thrown across the boundary;
+ *   - matrices are row-major with an explicit leading dimension in ELEMENTS;
+ *   - `dtype` arguments take the CT_F32 / CT_BF16 / CT_F16 codes below;
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point returns CT_ERR_CUDA.
+ *
+ * Each declaration cites the reference function (path inside the
+ * causal-tuner project : line) whose arithmetic it replaces.
+ */
+#ifndef CT_B200_H
+#define CT_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define CT_API __attribute__((visibility("default")))
+#else
+#define CT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { CT_F32 = 0, CT_BF16 = 1, CT_F16 = 2 };
+
+enum {
+  CT_OK = 0,
+  CT_ERR_ARG = -1,          /* null pointer, negative size, unknown dtype */
+  CT_ERR_UNSUPPORTED = -2,  /* shape/alignment the requested path cannot take */
+  CT_ERR_CUDA = -3,         /* a CUDA runtime/driver call failed */
+  CT_ERR_DEVICE = -4        /* a kernel reported a bounded-wait timeout */
+};
+
+/* GEMM path selection. AUTO picks the tcgen05 kernel when every operand meets
+ * the TMA rules (bf16, 16-byte aligned base, leading dimension a multiple of
+ * 8 elements) and falls back to the shape-generic SIMT kernel otherwise. Both
+ * run on the GPU. */
+enum { CT_PATH_AUTO = 0, CT_PATH_SIMT = 1, CT_PATH_TCGEN05 = 2 };
+
+/* ---- library state ------------------------------------------------------ */
+
+/* ABI version of this header. */
+CT_API int ct_abi_version(void);
+/* Kernels launched by this library in this process so far (all devices). */
+CT_API int64_t ct_launch_count(void);
+/* Kernels among those that were the tcgen05 GEMM. */
+CT_API int64_t ct_tcgen05_launch_count(void);
+/* Synchronises `stream`, then returns CT_OK, or CT_ERR_DEVICE when a kernel on
+ * the current device gave up on a bounded wait since the last call (the flag is
+ * cleared), or CT_ERR_CUDA with the sticky CUDA error. */
+CT_API int ct_check_device(void* stream);
+/* Text of the most recent CT_ERR_* on the calling thread (static storage). */
+CT_API const char* ct_last_error(void);
+
+/* ---- NF4 decode ---------------------------------------------------------
+ * Replaces kernels/nf4_cuda.py:32-43 (dequantize_nf4) and its Triton kernel
+ * kernels/nf4_cuda.py:9-29.
+ *   out[blocksize*g + 2j]   = code[packed[..] >> 4] * s_g
+ *   out[blocksize*g + 2j+1] = code[packed[..] & 15] * s_g
+ * s_g = absmax[g] (fp32) when nested == 0, else
+ * s_g = code2[absmax_u8[g]] * absmax2[g / blocksize2] + offset[0], the multiply
+ * and the add rounded separately. The fp32 product is rounded to `state_dtype`
+ * and then to `out_dtype`. `n` elements, (n+1)/2 packed bytes. `blocksize`
+ * must be even. When nested != 0 `absmax` points at uint8 values. */
+CT_API int ct_nf4_decode(const uint8_t* packed, const void* absmax, const float* code,
+                  const float* code2, const float* absmax2, const float* offset,
+                  void* out, int64_t n, int blocksize, int blocksize2, int nested,
+                  int state_dtype, int out_dtype, void* stream);
+
+/* ---- dtype cast ---------------------------------------------------------
+ * Replaces the per-call `a.to(dtype)`, `b.to(dtype)`, `bias.to(dtype)` casts of
+ * kernels/linear.py:70-71 and kernels/mlp_cuda.py:62. src[rows, cols] (ld_src)
+ * -> dst[rows, cols] (ld_dst), round-to-nearest-even. */
+CT_API int ct_cast(const void* src, int src_dtype, int64_t ld_src, void* dst, int dst_dtype,
+            int64_t ld_dst, int64_t rows, int64_t cols, void* stream);
+
+/* ---- generic matrix product --------------------------------------------
+ * Replaces kernels/linear.py:16-24 (accumulate) and the bare torch.mm calls at
+ * kernels/linear.py:83,124,125 and kernels/mlp_cuda.py:134,139.
+ *   C[m, n] = (add ? C[m, n] : 0) + sum_k A(m, k) * B(k, n)
+ * A(m, k) = A[m * a_rs + k * a_cs], B(k, n) = B[k * b_rs + n * b_cs] (element
+ * strides, one of each pair must be 1). fp32 accumulation; `in_dtype` is the
+ * type of A and B, `out_dtype` that of C. With add == 0, C is never read. */
+CT_API int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs,
+              int64_t b_cs, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+              int in_dtype, int out_dtype, int add, int path, void* stream);
+
+/* ---- fused projection forward --------------------------------------------
+ * Replaces kernels/linear.py:27-33 (forward_linear) plus the in-place residual
+ * add of kernels/linear.py:90-91.
+ *   xa  = round(x @ a^T)                                   [T, r]
+ *   out = round(round(x @ w^T + xa @ b^T + bias) + residual)   [T, N]
+ * x[T,K] (ldx), w[N,K] dense (ldw), a[r,K], b[N,r] contiguous, bias[N] or NULL,
+ * residual[T,N] (ld_res) or NULL; all of `dtype` (CT_BF16 or CT_F32). The
+ * low-rank term enters the same accumulator as the base product (one GEMM over
+ * the concatenated contraction [x | xa] . [w | b]^T), so `out` is rounded once
+ * where the reference rounds after the base product and again after the
+ * low-rank update. r may be 0 (a, b, xa ignored). */
+CT_API int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      const void* a, const void* b, const void* bias,
+                      const void* residual, int64_t ld_res, void* out, int64_t ld_out,
+                      void* xa, int64_t ld_xa, int64_t T, int64_t K, int64_t N,
+                      int64_t r, int dtype, int path, void* stream);
+
+/* ---- fused input gradient ---------------------------------------------------
+ * Replaces kernels/linear.py:36-39 (input_gradient).
+ *   low = round(dy @ b)                                        [T, r]
+ *   dx  = round((add ? dx : 0) + dy @ w + low @ a)             [T, K]
+ * dy[T,N] (ld_dy), w[N,K] (ldw), a[r,K], b[N,r] contiguous. `w` may be NULL:
+ * then only `low` is written (kernels/linear.py:124). */
+CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t ldw,
+                      const void* a, const void* b, void* dx, int64_t ld_dx,
+                      void* low, int64_t ld_low, int64_t T, int64_t K, int64_t N,
+                      int64_t r, int add, int dtype, int path, void* stream);
+
+/* ---- LoRA parameter gradients ----------------------------------------------
+ * Replaces kernels/linear.py:42-44 (parameter_gradients).
+ *   da[r, K] = (add ? da : 0) + low^T @ x     fp32
+ *   db[N, r] = (add ? db : 0) + dy^T  @ xa    fp32
+ * Deterministic: the contraction over T is split into a fixed number of
+ * slices whose fp32 partial sums are added in slice order (no atomics).
+ * `workspace` must hold ct_parameter_gradients_workspace(...) bytes (may be
+ * NULL when that is 0). */
+CT_API int64_t ct_parameter_gradients_workspace(int64_t T, int64_t K, int64_t N, int64_t r,
+                                         int dtype, int path);
+CT_API int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy, int64_t ld_dy,
+                           const void* low, int64_t ld_low, const void* xa,
+                           int64_t ld_xa, float* da, float* db, int64_t T, int64_t K,
+                           int64_t N, int64_t r, int add, int dtype, void* workspace,
+                           int path, void* stream);
+
+/* ---- SwiGLU activation ------------------------------------------------------
+ * Replaces kernels/mlp_cuda.py:10-35 (_activation / activation) and the
+ * separate-output backward of kernels/mlp_cuda.py:45-51.
+ * forward (grad == NULL):  out = round_d(g * sigmoid(g)) * u
+ * backward (grad != NULL): dg = round_d(grad * u) * sigmoid(g) * (1 + g * (1 - sigmoid(g)))
+ *                          du = grad * round_d(g * sigmoid(g))
+ *   and, when `reconstruct`, h = round_d(g * sigmoid(g)) * u is written to `out`.
+ * round_d rounds to `dtype`. `dg`/`du`/`out` may alias `gate`/`up`/`grad`
+ * element for element (the in-place use of kernels/mlp_cuda.py:133). */
+CT_API int ct_swiglu(const void* gate, const void* up, const void* grad, void* out, void* dg,
+              void* du, int64_t n, int dtype, int reconstruct, void* stream);
+
+/* ---- adjacent-pair partial RoPE ---------------------------------------------
+ * Replaces kernels/core_cuda.py:146-164 (_rope: forward, or inverse into a
+ * private tile, kernels/core_cuda.py:203-208) and kernels/core_cuda.py:167-199
+ * (in-place rotation of freshly produced q and k). x[rows, heads*head_dim],
+ * cos/sin[rows, half]; pairs (2c, 2c+1), c < half, of every head rotate; each
+ * product is rounded to `dtype` before the add (kernels/core_cuda.py:134-142).
+ * y may alias x. */
+CT_API int ct_rope(const void* x, const void* cosine, const void* sine, void* y, int64_t rows,
+            int heads, int head_dim, int half, int inverse, int dtype, void* stream);
+
+/* ---- elementwise add ---------------------------------------------------------
+ * Replaces `outputs[0].add_(residual)` (kernels/linear.py:90-91) and
+ * `output.add_(residual)` (kernels/mlp_cuda.py:79-80): y = round(y + r). */
+CT_API int ct_add_inplace(void* y, const void* r, int64_t n, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CT_B200_H */
