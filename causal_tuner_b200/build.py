@@ -17,7 +17,7 @@ LIBRARY = os.path.join(ROOT, "libct_b200.so")
 STAMP = os.path.join(ROOT, "libct_b200.so.stamp")
 SOURCES = ("api.cu", "nf4.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tc.cu")
 FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")
 
 
 def _nvcc():
@@ -54,7 +54,7 @@ def build(force=False, verbose=False):
     objects = []
     build_dir = os.path.join(ROOT, "build")
     os.makedirs(build_dir, exist_ok=True)
-    flags = [f for f in FLAGS if f != "--use_fast_math=false"]
+    flags = list(FLAGS)
     processes = []
     for source in SOURCES:
         obj = os.path.join(build_dir, source.replace(".cu", ".o"))

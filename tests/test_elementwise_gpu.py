@@ -1,0 +1,107 @@
+"""SwiGLU, RoPE, casts and the residual add against the CPU oracle and reference fixtures."""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from causal_tuner_b200.kernels import core_cuda, linear, mlp_cuda
+from oracle import ops
+from conftest import GOLDEN
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
+
+ROPE_FILES = sorted(os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "rope_*.npz")))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_extreme_inputs_and_tail_tiles(dtype):
+    gate = torch.linspace(-30, 30, 7 * 13569, device="cuda", dtype=dtype).reshape(7, -1).requires_grad_(True)
+    up = torch.randn_like(gate, requires_grad=True)
+    actual = mlp_cuda.silu_multiply(gate, up)
+    signal = torch.randn_like(actual.T).contiguous().T
+    original_signal = signal.clone()
+    expected = ops.swiglu(gate.detach().cpu(), up.detach().cpu())
+    tolerance = dict(rtol=.02, atol=.002) if dtype == torch.bfloat16 else dict(rtol=3e-5, atol=3e-6)
+    torch.testing.assert_close(actual.detach().cpu(), expected, **tolerance)
+    gradients = torch.autograd.grad(actual, (gate, up), signal, retain_graph=True)
+    oracle = ops.swiglu_backward(gate.detach().cpu(), up.detach().cpu(), signal.cpu())
+    for result, reference in zip(gradients, oracle):
+        torch.testing.assert_close(result.cpu(), reference, **tolerance)
+    for repeat, first in zip(torch.autograd.grad(actual, (gate, up), signal), gradients):
+        assert torch.equal(repeat, first)
+    assert torch.equal(signal, original_signal)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_activation_in_place_backward_rewrites_all_three_buffers(dtype):
+    gate = torch.randn(33, 257, device="cuda", dtype=dtype)
+    up, grad = torch.randn_like(gate), torch.randn_like(gate)
+    saved = (gate.clone(), up.clone(), grad.clone())
+    hidden_forward = mlp_cuda.activation(gate.clone(), up.clone())
+    returned = mlp_cuda.activation(gate, up, grad)
+    assert returned.data_ptr() == grad.data_ptr()
+    assert torch.equal(grad, hidden_forward)  # the gradient buffer now holds the forward product
+    dg, du = ops.swiglu_backward(*(t.cpu() for t in saved))
+    tolerance = dict(rtol=.02, atol=.002) if dtype == torch.bfloat16 else dict(rtol=3e-5, atol=3e-6)
+    torch.testing.assert_close(gate.cpu(), dg, **tolerance)
+    torch.testing.assert_close(up.cpu(), du, **tolerance)
+    # forward into a caller-provided buffer, including gate itself
+    target = torch.empty_like(gate)
+    assert mlp_cuda.activation(saved[0], saved[1], out=target) is target
+    alias = saved[0].clone()
+    mlp_cuda.activation(alias, saved[1], out=alias)
+    assert torch.equal(alias, target) and torch.equal(target, hidden_forward)
+
+
+@pytest.mark.parametrize("name", ROPE_FILES)
+def test_rope_fixture_bit_exact(golden, name):
+    g = golden(name)
+    dtype = torch.bfloat16 if int(g["bf16"]) else torch.float32
+    x, c, s, dy = (torch.from_numpy(g[k]).to(dtype).cuda() for k in ("x", "cosine", "sine", "dy"))
+    x.requires_grad_(True)
+    y = core_cuda.PartialRoPE.apply(x, c, s)
+    tolerance = 0 if dtype == torch.bfloat16 else 2e-6
+    torch.testing.assert_close(y.float().cpu(), torch.from_numpy(g["y"]), rtol=tolerance, atol=tolerance)
+    dx, = torch.autograd.grad(y, x, dy)
+    torch.testing.assert_close(dx.float().cpu(), torch.from_numpy(g["dx"]), rtol=tolerance, atol=tolerance)
+    heads, head_dim = x.shape[-2], x.shape[-1]
+    rotary = c.shape[-1] * 2
+    assert torch.equal(y[..., rotary:], x[..., rotary:])
+    # owned in-place rotation of a (query, key) pair equals the out-of-place one
+    query = x.detach().reshape(14, heads * head_dim).clone()
+    key = x.detach()[..., 0, :].reshape(14, head_dim).clone()
+    core_cuda.rotate_owned_qk(query, key, c, s, head_dim)
+    assert torch.equal(query, y.detach().reshape(14, -1))
+    assert torch.equal(key, y.detach()[..., 0, :].reshape(14, head_dim))
+    # inverse into a private tile leaves the source untouched
+    source = dy.reshape(14, -1).clone()
+    keep = source.clone()
+    tile = torch.empty_like(source)
+    assert core_cuda.inverse_rope_tile(source, c.reshape(14, -1), s.reshape(14, -1), head_dim, tile) is tile
+    assert torch.equal(source, keep) and torch.equal(tile, dx.reshape(14, -1))
+
+
+def test_rope_many_rows_and_heads_bit_exact_bf16():
+    rows, heads, head_dim, rotary = 4099, 32, 128, 64
+    x = torch.randn(rows, heads, head_dim, device="cuda", dtype=torch.bfloat16)
+    angles = torch.randn(rows, rotary // 2, device="cuda") * 1000
+    c, s = angles.cos().bfloat16(), angles.sin().bfloat16()
+    expected = ops.rotate(x.cpu(), c.cpu(), s.cpu())
+    assert torch.equal(core_cuda.PartialRoPE.apply(x, c, s).cpu(), expected)
+
+
+@pytest.mark.parametrize("shape", [(5, 7), (256, 4096), (3, 8)])
+def test_cast_and_residual_add(shape):
+    source = torch.randn(*shape, device="cuda")
+    assert torch.equal(linear.cast(source, torch.bfloat16), source.bfloat16())
+    assert linear.cast(source, torch.float32) is source
+    strided = torch.randn(shape[1], shape[0], device="cuda").T
+    assert torch.equal(linear.cast(strided, torch.bfloat16), strided.bfloat16())
+    for dtype in (torch.bfloat16, torch.float32):
+        y, r = torch.randn(*shape, device="cuda", dtype=dtype), torch.randn(*shape, device="cuda", dtype=dtype)
+        expected = y + r
+        linear._add_inplace(y, r)
+        assert torch.equal(y, expected)

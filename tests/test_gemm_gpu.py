@@ -1,0 +1,173 @@
+"""ct_matmul / fused GEMM entry points against a plain PyTorch fp32 product of the same operands,
+on both GPU paths (tcgen05 and the shape-generic SIMT kernel), for every operand orientation."""
+
+import pytest
+import torch
+
+from causal_tuner_b200 import _lib
+from causal_tuner_b200.kernels import linear
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
+
+PATHS = {"simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}
+
+
+@pytest.fixture(params=list(PATHS))
+def path(request, monkeypatch):
+    monkeypatch.setattr(_lib, "gemm_path", PATHS[request.param])
+    return request.param
+
+
+def relative(actual, expected):
+    actual, expected = actual.float(), expected.float()
+    return ((actual - expected).norm() / expected.norm().clamp_min(1e-20)).item()
+
+
+def operand(rows, cols, major, dtype=torch.bfloat16):
+    """A [rows, cols] matrix whose storage is row-major ("K") or column-major ("MN")."""
+    if major == "K":
+        return torch.randn(rows, cols, device="cuda").to(dtype)
+    return torch.randn(cols, rows, device="cuda").to(dtype).T
+
+
+# (M, N, K): one exact tile; ragged in every dimension; more tiles than SMs; a long contraction
+SHAPES = [(128, 256, 64), (304, 520, 200), (2048, 4096, 128), (96, 72, 2048), (1, 8, 8)]
+
+
+@pytest.mark.parametrize("a_major,b_major", [("K", "K"), ("K", "MN"), ("MN", "K"), ("MN", "MN")])
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_matmul_orientations(path, shape, a_major, b_major, out_dtype):
+    m, n, k = shape
+    if path == "tcgen05" and min(m, n, k) < 8:
+        pytest.skip("degenerate extents go to the SIMT kernel")
+    left = operand(m, k, a_major)             # A(m, k): "K" = k contiguous
+    right = operand(n, k, b_major).T          # B(k, n): "K" = k contiguous
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+    linear.matmul(left, right, out=out)
+    expected = left.float() @ right.float()
+    assert torch.isfinite(out).all()
+    assert relative(out, expected) < (4e-3 if out_dtype == torch.bfloat16 else 2e-6)
+    if out_dtype == torch.float32:
+        linear.matmul(left, right, out=out, add=True)
+        assert relative(out, 2 * expected) < 2e-6
+
+
+def test_matmul_exact_on_small_integers(path):
+    # Integer-valued operands: every product and partial sum is exact in fp32, so any layout
+    # mistake shows up as a nonzero difference.
+    m, n, k = 256, 512, 192
+    left = torch.randint(-3, 4, (m, k), device="cuda").bfloat16()
+    right = torch.randint(-3, 4, (k, n), device="cuda").bfloat16()
+    out = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    linear.matmul(left, right, out=out)
+    assert torch.equal(out, left.float() @ right.float())
+    linear.matmul(left.T.contiguous().T, right.T.contiguous().T, out=out)
+    assert torch.equal(out, left.float() @ right.float())
+
+
+@pytest.mark.parametrize("rows,inner,outer,rank", [(300, 256, 520, 16), (37, 32, 24, 8), (1024, 512, 768, 256)])
+@pytest.mark.parametrize("with_bias,with_residual", [(False, False), (True, True)])
+def test_forward_linear_concatenated_contraction(path, rows, inner, outer, rank, with_bias, with_residual):
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(outer, inner, device="cuda") * .05).bfloat16()
+    a = (torch.randn(rank, inner, device="cuda") * .05).bfloat16()
+    b = (torch.randn(outer, rank, device="cuda") * .05).bfloat16()
+    bias = torch.randn(outer, device="cuda").bfloat16() if with_bias else None
+    residual = torch.randn(rows, outer, device="cuda").bfloat16() if with_residual else None
+    out = torch.full((rows, outer), float("nan"), device="cuda", dtype=torch.bfloat16)
+    xa = torch.full((rows, rank), float("nan"), device="cuda", dtype=torch.bfloat16)
+    linear.forward_linear(x, w, a, b, out=out, xa=xa, bias=bias, residual=residual)
+    expected_xa = (x.float() @ a.float().T).bfloat16()
+    assert relative(xa, expected_xa) < 4e-3
+    expected = x.float() @ w.float().T + xa.float() @ b.float().T
+    if bias is not None:
+        expected = expected + bias.float()
+    expected = expected.bfloat16()
+    if residual is not None:
+        expected = (expected.float() + residual.float()).bfloat16()
+    assert relative(out, expected) < 4e-3
+    # the residual add must equal a separate rounded add of the unfused output
+    if residual is not None:
+        plain = torch.empty_like(out)
+        linear.forward_linear(x, w, a, b, out=plain, xa=xa, bias=bias)
+        assert torch.equal(out, (plain.float() + residual.float()).bfloat16())
+
+
+@pytest.mark.parametrize("rows,inner,outer,rank", [(300, 256, 520, 16), (1024, 512, 768, 256)])
+def test_input_gradient_and_parameter_gradients(path, rows, inner, outer, rank):
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    dy = torch.randn(rows, outer, device="cuda").bfloat16()
+    w = (torch.randn(outer, inner, device="cuda") * .05).bfloat16()
+    a = (torch.randn(rank, inner, device="cuda") * .05).bfloat16()
+    b = (torch.randn(outer, rank, device="cuda") * .05).bfloat16()
+    dx = torch.full((rows, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+    low = torch.full((rows, rank), float("nan"), device="cuda", dtype=torch.bfloat16)
+    linear.input_gradient(dy, w, a, b, dx, low)
+    expected_low = (dy.float() @ b.float()).bfloat16()
+    assert relative(low, expected_low) < 4e-3
+    expected_dx = dy.float() @ w.float() + low.float() @ a.float()
+    assert relative(dx, expected_dx) < 4e-3
+    before = dx.clone()
+    linear.input_gradient(dy, w, a, b, dx, low, add=True)
+    assert relative(dx, before.float() + expected_dx) < 6e-3
+    xa = (x.float() @ a.float().T).bfloat16()
+    da = torch.full((rank, inner), float("nan"), device="cuda")
+    db = torch.full((outer, rank), float("nan"), device="cuda")
+    linear.parameter_gradients(x, dy, da, db, low, xa, add=False)
+    expected_da, expected_db = low.float().T @ x.float(), dy.float().T @ xa.float()
+    assert relative(da, expected_da) < 1e-5 and relative(db, expected_db) < 1e-5
+    first = (da.clone(), db.clone())
+    linear.parameter_gradients(x, dy, da, db, low, xa, add=False)
+    assert torch.equal(da, first[0]) and torch.equal(db, first[1])  # fixed summation order
+    linear.parameter_gradients(x, dy, da, db, low, xa, add=True)
+    assert relative(da, 2 * expected_da) < 1e-5 and relative(db, 2 * expected_db) < 1e-5
+
+
+def test_split_contraction_matches_single_pass_and_is_repeatable(monkeypatch):
+    # rank-16 adapter over 4096 tokens: dA has a single output tile, so the token contraction is
+    # cut into 8 slices that are summed in slice order.
+    monkeypatch.setattr(_lib, "gemm_path", _lib.PATH_TCGEN05)
+    rows, inner, outer, rank = 4096, 256, 512, 16
+    assert _lib.load().ct_parameter_gradients_workspace(rows, inner, outer, rank, _lib.BF16, _lib.PATH_TCGEN05) > 0
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    dy = torch.randn(rows, outer, device="cuda").bfloat16()
+    low = torch.randn(rows, rank, device="cuda").bfloat16()
+    xa = torch.randn(rows, rank, device="cuda").bfloat16()
+    da, db = torch.empty(rank, inner, device="cuda"), torch.empty(outer, rank, device="cuda")
+    linear.parameter_gradients(x, dy, da, db, low, xa, add=False)
+    assert relative(da, low.float().T @ x.float()) < 1e-5
+    assert relative(db, dy.float().T @ xa.float()) < 1e-5
+    again = (torch.empty_like(da), torch.empty_like(db))
+    linear.parameter_gradients(x, dy, *again, low, xa, add=False)
+    assert torch.equal(da, again[0]) and torch.equal(db, again[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_accumulate_first_write_ignores_uninitialised_storage(dtype):
+    left = torch.randn(19, 37, device="cuda", dtype=dtype)
+    right = torch.randn(37, 23, device="cuda", dtype=dtype)
+    output = torch.full((19, 23), float("nan"), device="cuda")
+    expected = left.float() @ right.float()
+    linear.accumulate(output, left, right, add=False)
+    torch.testing.assert_close(output, expected, rtol=1e-5, atol=1e-5)
+    linear.accumulate(output, left, right, add=True)
+    torch.testing.assert_close(output, expected * 2, rtol=1e-5, atol=1e-5)
+
+
+def test_fp32_operands_use_the_simt_kernel():
+    before = _lib.tcgen05_launch_count()
+    left, right = torch.randn(130, 70, device="cuda"), torch.randn(70, 90, device="cuda")
+    out = torch.empty(130, 90, device="cuda")
+    linear.matmul(left, right, out=out)
+    torch.testing.assert_close(out, left @ right, rtol=1e-5, atol=1e-5)
+    assert _lib.tcgen05_launch_count() == before
+
+
+def test_auto_path_picks_tcgen05_for_aligned_bf16():
+    before = _lib.tcgen05_launch_count()
+    left, right = torch.randn(256, 128, device="cuda").bfloat16(), torch.randn(128, 512, device="cuda").bfloat16()
+    out = torch.empty(256, 512, device="cuda", dtype=torch.bfloat16)
+    linear.matmul(left, right, out=out)
+    assert _lib.tcgen05_launch_count() == before + 1
+    assert relative(out, left.float() @ right.float()) < 4e-3

@@ -1,0 +1,111 @@
+"""Host-side logic of the operator layer that needs no GPU: fusion predicate, argument
+guards, cache accounting, quantiser round trips and module surface."""
+
+import inspect
+
+import numpy as np
+import pytest
+import torch
+
+from causal_tuner_b200.kernels import core_cuda, linear, mlp_cuda, nf4_cuda
+from causal_tuner_b200.modeling.lora import Projection
+from causal_tuner_b200.modeling.model import MLP, Runtime
+from causal_tuner_b200.quant import quantize_nf4, NF4_LEVELS
+from oracle import nf4 as oracle_nf4
+
+
+class TinyConfig:
+    hidden_size, intermediate_size = 32, 68
+
+
+def test_operator_surface_matches_the_reference_signatures():
+    expected = {
+        linear.materialize: ["weight", "state", "dtype"],
+        linear.accumulate: ["output", "left", "right", "add"],
+        linear.forward_linear: ["x", "weight", "a", "b", "out", "xa", "bias", "residual"],
+        linear.input_gradient: ["dy", "weight", "a", "b", "dx", "low", "add"],
+        linear.parameter_gradients: ["x", "dy", "da", "db", "low", "xa", "add"],
+        linear.projection_parameters: ["module"],
+        linear.can_fuse: ["module", "x"],
+        linear.project_group: ["modules", "x", "tile", "rotary", "residual"],
+        mlp_cuda.activation: ["gate", "up", "gradient", "out"],
+        mlp_cuda.silu_multiply: ["gate", "up"],
+        mlp_cuda._forward_into: ["output", "x", "dtype", "tile", "states", "parameters", "residual", "save"],
+        mlp_cuda.tiled_lora_mlp: ["module", "x", "residual", "tile", "cache"],
+        nf4_cuda.dequantize_nf4: ["weight", "state", "dtype"],
+        core_cuda.rotate_owned_qk: ["query", "key", "cosine", "sine", "head_dim"],
+        core_cuda.inverse_rope_tile: ["grad", "cosine", "sine", "head_dim", "output"],
+    }
+    for function, names in expected.items():
+        target = getattr(function, "__wrapped__", function)
+        assert list(inspect.signature(target).parameters) == names, function.__name__
+    assert inspect.signature(linear.accumulate).parameters["add"].default is True
+    assert inspect.signature(linear.project_group).parameters["tile"].default == 0
+    assert issubclass(linear._LoRAGroup, torch.autograd.Function)
+    assert issubclass(mlp_cuda._TiledLoRAMLP, torch.autograd.Function)
+
+
+def test_can_fuse_predicate():
+    module = Projection(8, 8, bias=True, rank=2, device="cpu")
+
+    class Cuda:
+        is_cuda = True
+    assert linear.can_fuse(module, Cuda())
+    assert not linear.can_fuse(module, torch.zeros(1))
+    module.bias.requires_grad_(True)
+    assert not linear.can_fuse(module, Cuda())
+    module.bias.requires_grad_(False)
+    module.lora_A.requires_grad_(False)
+    assert not linear.can_fuse(module, Cuda())
+    assert not linear.can_fuse(Projection(8, 8, rank=0, device="cpu"), Cuda())
+
+
+def test_projection_parameters_and_initialisation():
+    module = Projection(64, 16, bias=True, rank=4, device="cpu")
+    (weight, a, b, bias), state = linear.projection_parameters(module)
+    assert state is None and weight is module.weight and bias is module.bias
+    assert a.dtype == b.dtype == torch.float32 and a.shape == (4, 64) and b.shape == (16, 4)
+    assert not b.any() and a.abs().max() <= (6 / 64) ** .5
+    assert not weight.requires_grad and not bias.requires_grad and a.requires_grad and b.requires_grad
+
+
+def test_residual_needs_a_single_projection():
+    modules = [Projection(8, 8, rank=2, device="cpu") for _ in range(2)]
+    with pytest.raises(ValueError, match="Residual fusion requires one output projection"):
+        linear.project_group(modules, torch.zeros(1, 3, 8), residual=torch.zeros(1, 3, 8))
+
+
+def test_nf4_install_is_restricted_like_the_reference():
+    module = Projection(8, 8, rank=2, device="cpu")
+    with pytest.raises(ValueError, match="CUDA"):
+        module.install_nf4(module.weight.detach().clone(), "cpu")
+    with pytest.raises(ValueError, match="frozen adapter"):
+        Projection(8, 8, rank=0, device="cpu").install_nf4(torch.zeros(8, 8), "cuda")
+
+
+def test_mlp_cache_bytes_counts_gate_up_and_their_low_rank_inputs():
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cpu")
+    assert module.cache_bytes(14) == 14 * 2 * (2 * 68 + 2 * 4)
+    assert module.tile == 5 and module.cache_intermediates is False
+
+
+@pytest.mark.parametrize("shape,blocksize,nested", [((71, 96), 64, False), ((71, 96), 128, True), ((17, 19), 64, True),
+                                                    ((5, 4096), 4096, False)])
+def test_quantiser_layout_round_trips_through_the_oracle_decode(shape, blocksize, nested):
+    weight = torch.randn(*shape) * 0.02
+    packed, state = quantize_nf4(weight, blocksize=blocksize, nested=nested)
+    n = weight.numel()
+    assert packed.shape == ((n + 1) // 2, 1) and packed.dtype == torch.uint8
+    assert state.shape == weight.shape and state.quant_type == "nf4" and state.blocksize == blocksize
+    assert tuple(state.code.tolist()) == tuple(np.float32(v) for v in NF4_LEVELS)
+    extra = {}
+    if nested:
+        assert state.absmax.dtype == torch.uint8
+        extra = dict(nested=True, code2=state.state2.code.numpy(), absmax2=state.state2.absmax.numpy(),
+                     offset=float(state.offset), blocksize2=state.state2.blocksize)
+    decoded = oracle_nf4.decode(packed.numpy(), state.absmax.numpy(), state.code.numpy(), n, blocksize, **extra)
+    error = np.abs(decoded - weight.reshape(-1).numpy())
+    blocks = np.repeat(np.abs(weight.reshape(-1).numpy().reshape(-1)), 1)
+    # within 17 % of the block's absmax (4-bit levels) plus the 8-bit error of nested statistics
+    limit = 0.17 * weight.abs().max().item() * (1.1 if nested else 1.0)
+    assert error.max() <= limit

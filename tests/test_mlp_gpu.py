@@ -1,0 +1,274 @@
+"""tiled_lora_mlp / _TiledLoRAMLP on the GPU: recompute-in-backward against stored activations,
+against the CPU oracle and the reference-generated fixtures, plus the checkpoint and ownership
+rules the reference's tests pin (tests/test_mlp_cache.py, tests/test_recompute_and_layout.py,
+tests/test_fast_training.py of the reference)."""
+
+import copy
+
+import pytest
+import torch
+from torch.utils.checkpoint import checkpoint, set_checkpoint_early_stop
+
+from causal_tuner_b200 import _lib
+from causal_tuner_b200.kernels import mlp_cuda
+from causal_tuner_b200.modeling.lora import Projection
+from causal_tuner_b200.modeling.model import MLP, Runtime
+from oracle import ops
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
+
+
+class TinyConfig:
+    hidden_size, intermediate_size = 32, 68
+
+
+class WideConfig:
+    hidden_size, intermediate_size = 4096, 14336
+
+
+def relative(actual, expected):
+    actual, expected = actual.float(), expected.float()
+    return ((actual - expected).norm() / expected.norm().clamp_min(1e-20)).item()
+
+
+def randomise_b(module, std):
+    for name, parameter in module.named_parameters():
+        if "lora_B" in name:
+            torch.nn.init.normal_(parameter, std=std)
+
+
+def trainable(module):
+    return tuple(p for p in module.parameters() if p.requires_grad)
+
+
+def oracle_mlp(module, x):
+    triple = lambda p: (p.base_weight().detach(), p.lora_A, p.lora_B)
+    return ops.mlp(x, triple(module.gate_proj), triple(module.up_proj), triple(module.down_proj),
+                   module.gate_proj.compute_dtype)
+
+
+@pytest.mark.parametrize("name", ["mlp_fp32.npz", "mlp_bf16.npz"])
+@pytest.mark.parametrize("cache", [False, True])
+def test_reference_fixture(golden, name, cache):
+    g = golden(name)
+    dtype = torch.bfloat16 if int(g["bf16"]) else torch.float32
+    module = MLP(TinyConfig, Runtime(rank=4, base_dtype=dtype, compute_dtype=dtype, mlp_tile=5), "cuda")
+    with torch.no_grad():
+        for key, parameter in module.named_parameters():
+            parameter.copy_(torch.from_numpy(g["p_" + key.replace(".", "_")]))
+    x = torch.from_numpy(g["x"]).to(dtype).cuda().requires_grad_(True)
+    y = module(x, cache=cache)
+    names = [k for k, p in module.named_parameters() if p.requires_grad]
+    grads = torch.autograd.grad(y, (x, *trainable(module)), torch.from_numpy(g["dy"]).to(dtype).cuda())
+    tolerance = dict(rtol=.04, atol=.004) if dtype == torch.bfloat16 else dict(rtol=3e-5, atol=3e-6)
+    torch.testing.assert_close(y.float().cpu(), torch.from_numpy(g["y"]), **tolerance)
+    torch.testing.assert_close(grads[0].float().cpu(), torch.from_numpy(g["dx"]), **tolerance)
+    for key, grad in zip(names, grads[1:]):
+        assert grad.dtype == torch.float32
+        torch.testing.assert_close(grad.cpu(), torch.from_numpy(g["g_" + key.replace(".", "_")]), **tolerance)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("train_input", [False, True])
+@pytest.mark.parametrize("mixed_ranks", [False, True])
+@pytest.mark.parametrize("cache", [False, True])
+def test_independent_gradients(dtype, train_input, mixed_ranks, cache):
+    module = MLP(TinyConfig, Runtime(rank=4, base_dtype=dtype, compute_dtype=dtype, mlp_tile=5), "cuda")
+    module.cache_intermediates = cache
+    if mixed_ranks:
+        for name, rank in (("gate_proj", 3), ("up_proj", 5), ("down_proj", 7)):
+            original = getattr(module, name)
+            setattr(module, name, Projection(original.weight.shape[1], original.weight.shape[0], rank=rank,
+                                             base_dtype=dtype, compute_dtype=dtype, device="cuda"))
+    randomise_b(module, .1)
+    reference = copy.deepcopy(module)
+    x = torch.randn(2, 7, 32, device="cuda", dtype=dtype, requires_grad=train_input)
+    y = x.detach().clone().requires_grad_(train_input)
+    actual = module(x)
+    expected = oracle_mlp(reference, y)
+    tolerance = dict(rtol=.04, atol=.003) if dtype == torch.bfloat16 else dict(rtol=3e-5, atol=2e-6)
+    torch.testing.assert_close(actual, expected, **tolerance)
+    signal = torch.randn_like(actual)
+    actual.backward(signal)
+    expected.backward(signal)
+    if train_input:
+        torch.testing.assert_close(x.grad, y.grad, **tolerance)
+    for (name, a), (_, b) in zip(module.named_parameters(), reference.named_parameters()):
+        if a.requires_grad:
+            assert a.grad.dtype == torch.float32, name
+            torch.testing.assert_close(a.grad, b.grad, **tolerance)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tile", [0, 5])
+def test_cached_matches_recompute_and_survives_repeated_backward(monkeypatch, dtype, tile):
+    module = MLP(TinyConfig, Runtime(rank=4, base_dtype=dtype, compute_dtype=dtype, mlp_tile=tile), "cuda")
+    randomise_b(module, .05)
+    x = torch.randn(2, 7, 32, device="cuda", dtype=dtype, requires_grad=True)
+    original = x.detach().clone()
+    signal = torch.randn_like(x)
+    params = (x, *trainable(module))
+    expected = module(x, residual=x)
+    reference = torch.autograd.grad(expected, params, signal)
+    module.cache_intermediates = True
+    saved = []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t) or t, lambda t: t):
+        actual = module(x, residual=x)
+    allowed = {x.data_ptr(), *(p.data_ptr() for p in module.parameters())}
+    retained = [t for t in saved if t.data_ptr() not in allowed]
+    assert sum(t.numel() * t.element_size() for t in retained) == module.cache_bytes(14)
+    snapshots = [t.clone() for t in retained]
+
+    def forbidden(*a, **kw):
+        raise AssertionError("Cached backward must not recompute gate/up projections")
+    monkeypatch.setattr(mlp_cuda, "forward_linear", forbidden)
+    gradients = torch.autograd.grad(actual, params, signal, retain_graph=True)
+    repeated = torch.autograd.grad(actual, params, signal)
+    assert torch.equal(actual, expected)
+    for value, expected_grad, repeat in zip(gradients, reference, repeated):
+        assert torch.equal(value, expected_grad) and torch.equal(value, repeat)
+    assert all(g.dtype == torch.float32 for g in gradients[1:])
+    for value, snapshot in zip(retained, snapshots):
+        assert torch.equal(value, snapshot)
+    assert torch.equal(x, original)
+
+
+def test_saves_only_boundary_and_weights(monkeypatch):
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cuda")
+    x = torch.randn(2, 13, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    saved = []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t) or t, lambda t: t):
+        output = module(x)
+    allowed = {x.data_ptr(), *(parameter.data_ptr() for parameter in module.parameters())}
+    assert all(tensor.data_ptr() in allowed for tensor in saved)
+
+    def forbidden(*args, **kwargs):
+        raise AssertionError("The fused MLP backward must not build per-tile autograd graphs")
+    monkeypatch.setattr(torch.autograd, "grad", forbidden)
+    output.sum().backward()
+
+
+@pytest.mark.parametrize("downstream,early_stop,expected_calls", [(False, True, 1), (True, True, 2), (False, False, 2)])
+def test_checkpoint_skips_only_unneeded_forward(monkeypatch, downstream, early_stop, expected_calls):
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cuda")
+    randomise_b(module, .1)
+    reference = copy.deepcopy(module)
+    x = torch.randn(2, 7, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = x.detach().clone().requires_grad_(True)
+    calls = 0
+    original = mlp_cuda._forward_into
+
+    def counted(*args):
+        nonlocal calls
+        calls += 1
+        return original(*args)
+    monkeypatch.setattr(mlp_cuda, "_forward_into", counted)
+
+    def function(value):
+        output = module(value, residual=value)
+        return output.sin() if downstream else output
+    with set_checkpoint_early_stop(early_stop):
+        actual = checkpoint(function, x, use_reentrant=False, preserve_rng_state=False)
+    signal = torch.randn_like(actual)
+    actual.backward(signal)
+    assert calls == expected_calls
+    expected = reference(y) + y
+    if downstream:
+        expected = expected.sin()
+    expected.backward(signal)
+    assert torch.equal(actual, expected) and torch.equal(x.grad, y.grad)
+    for left, right in zip(module.parameters(), reference.parameters()):
+        if left.requires_grad:
+            assert torch.equal(left.grad, right.grad)
+
+
+@pytest.mark.parametrize("alias", [False, True])
+def test_owned_residual(alias):
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cuda")
+    randomise_b(module, .1)
+    x = torch.randn(2, 7, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    residual = x if alias else torch.randn_like(x, requires_grad=True)
+    saved_x, saved_residual = x.detach().clone(), residual.detach().clone()
+    actual, expected = module(x, residual=residual), module(x) + residual
+    assert torch.equal(actual, expected)
+    signal = torch.randn_like(actual)
+    original_signal = signal.clone()
+    parameters = (x, *(() if alias else (residual,)), *trainable(module))
+    first = torch.autograd.grad(actual, parameters, signal, retain_graph=True)
+    second = torch.autograd.grad(actual, parameters, signal)
+    oracle = torch.autograd.grad(expected, parameters, signal)
+    for a, b, c in zip(first, second, oracle):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    assert torch.equal(x, saved_x) and torch.equal(residual, saved_residual) and torch.equal(signal, original_signal)
+
+
+def test_nf4_mlp_gradients():
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cuda")
+    for projection in (module.gate_proj, module.up_proj, module.down_proj):
+        projection.install_nf4(projection.weight.detach().clone(), "cuda")
+        torch.nn.init.normal_(projection.lora_B, std=.1)
+    x = torch.randn(1, 13, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    actual = module(x)
+    expected = oracle_mlp(module, x)
+    signal = torch.randn_like(actual)
+    parameters = (x, *trainable(module))
+    ag = torch.autograd.grad(actual, parameters, signal)
+    eg = torch.autograd.grad(expected, parameters, signal)
+    torch.testing.assert_close(actual, expected, rtol=.04, atol=.003)
+    for a, e in zip(ag, eg):
+        torch.testing.assert_close(a, e.to(a.dtype), rtol=.05, atol=.003)
+
+
+def test_empty_input_returns_zero_parameter_gradients():
+    module = MLP(TinyConfig, Runtime(rank=4, mlp_tile=5), "cuda")
+    x = torch.empty(2, 0, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    output = module(x)
+    gradients = torch.autograd.grad(output.sum(), (x, *trainable(module)))
+    assert gradients[0].shape == x.shape
+    assert all(torch.count_nonzero(gradient) == 0 for gradient in gradients)
+
+
+def test_untiled_store_activations_path_matches_recompute_path():
+    module = MLP(TinyConfig, Runtime(rank=4), "cuda")
+    randomise_b(module, .1)
+    x = torch.randn(3, 11, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    fused, stored = module(x), module.untiled(x)
+    assert relative(fused, stored) < 2e-2
+    signal = torch.randn_like(fused)
+    for a, b in zip(torch.autograd.grad(fused, (x, *trainable(module)), signal),
+                    torch.autograd.grad(stored, (x, *trainable(module)), signal)):
+        assert relative(a, b) < 3e-2
+
+
+def test_full_width_bf16_mlp_block_with_recompute():
+    """Hidden 4096, intermediate 14336, NF4 base weights, rank-256 adapters, 2051 packed tokens:
+    recompute and cached modes bit-identical, both within 2e-2 relative Frobenius error of a bf16
+    PyTorch composition, and the recompute mode retains only x."""
+    torch.manual_seed(3)
+    module = MLP(WideConfig, Runtime(rank=256), "cuda")
+    for projection in (module.gate_proj, module.up_proj, module.down_proj):
+        projection.install_nf4(projection.weight.detach().clone(), "cuda", nested=False)
+        torch.nn.init.normal_(projection.lora_B, std=.005)
+    rows = 2051
+    x = torch.randn(1, rows, 4096, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    signal = torch.randn_like(x)
+    params = (x, *trainable(module))
+    before = _lib.tcgen05_launch_count()
+    saved = []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t) or t, lambda t: t):
+        recomputed = module(x, residual=x, cache=False)
+    allowed = {x.data_ptr(), *(p.data_ptr() for p in module.parameters())}
+    assert all(t.data_ptr() in allowed for t in saved)
+    g_recompute = torch.autograd.grad(recomputed, params, signal)
+    assert _lib.tcgen05_launch_count() > before
+    cached = module(x, residual=x, cache=True)
+    g_cached = torch.autograd.grad(cached, params, signal)
+    assert torch.equal(recomputed, cached)
+    for a, b in zip(g_recompute, g_cached):
+        assert torch.equal(a, b)
+    z = x.detach().clone().requires_grad_(True)
+    expected = oracle_mlp(module, z) + z
+    reference = torch.autograd.grad(expected, (z, *trainable(module)), signal)
+    for name, left, right in zip(["y", "dx"] + ["param"] * 6, (recomputed, *g_recompute), (expected, *reference)):
+        assert torch.isfinite(left).all()
+        assert relative(left, right) < 2e-2, name
