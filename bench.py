@@ -1,0 +1,369 @@
+"""Throughput of the fused NF4 + LoRA projection (forward Y, backward dX, dA, dB).
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...   # the reference's CPU composition
+
+Workload ("projection_fwd_bwd_7b_gate"): one decoder projection of the 7B configuration -
+M = 16384 packed tokens, K = 4096, N = 14336, rank 256, NF4 base weight in 64-element blocks
+with fp32 absmax, bf16 activations, fp32 adapter weights and gradients. X ~ N(0,1),
+W ~ N(0,0.02), A ~ N(0,0.02), B ~ N(0,0.01), dY ~ N(0,1), all synthetic and seeded. A step
+is one forward plus one backward through the public operator (`project_group` + autograd);
+with N > 1 every rank works on its own 16384 tokens (weak scaling) and the fp32 adapter
+gradients are summed across ranks with one NCCL all-reduce inside the step.
+
+One JSON line is printed by rank 0. `value` is whole-job tokens/s with inputs resident in
+HBM; `e2e` is the same step fed from pinned host buffers with every result copied back to
+the host inside the timed region; `roofline` is the tcgen05 GEMM's algorithmic FLOP/s over
+its own CUDA-event time against the measured cuBLAS bf16 peak; `cpu_baseline` times the CPU
+restatement of the reference composition on a bounded sample of rows.
+"""
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, INNER, OUTER, RANK = 16384, 4096, 14336, 256
+CPU_SAMPLE_ROWS = 512
+METRIC = "train tokens/s (NF4 r256 LoRA projection fwd+bwd, 7B gate/up shape)"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def projection_flops(rows):
+    """Algorithmic work of one step: 4TKN + 6TKr + 6TNr (no recomputation counted)."""
+    return 4 * rows * INNER * OUTER + 6 * rows * INNER * RANK + 6 * rows * OUTER * RANK
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def world():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Reads SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index, period=0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_event = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            names = {
+                "nvmlClocksEventReasonHwSlowdown": "hw_slowdown",
+                "nvmlClocksEventReasonHwThermalSlowdown": "hw_thermal_slowdown",
+                "nvmlClocksEventReasonSwThermalSlowdown": "sw_thermal_slowdown",
+                "nvmlClocksEventReasonSwPowerCap": "sw_power_cap",
+                "nvmlClocksThrottleReasonHwSlowdown": "hw_slowdown",
+                "nvmlClocksThrottleReasonHwThermalSlowdown": "hw_thermal_slowdown",
+                "nvmlClocksThrottleReasonSwThermalSlowdown": "sw_thermal_slowdown",
+                "nvmlClocksThrottleReasonSwPowerCap": "sw_power_cap",
+            }
+            masks = {getattr(pynvml, k): v for k, v in names.items() if hasattr(pynvml, k)}
+            read = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop_event.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                active = read(handle)
+                self.reasons.update(label for mask, label in masks.items() if active & mask)
+                time.sleep(self.period)
+        except Exception as error:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(error).__name__}")
+
+    def stop(self):
+        self._stop_event.set()
+        self.join(timeout=2)
+        ordered = sorted(self.samples)
+        median = ordered[len(ordered) // 2] if ordered else None
+        return {"sm_mhz": median, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(ordered)}
+
+
+def physical_gpu_index(local_rank):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        try:
+            return int(visible.split(",")[local_rank])
+        except (ValueError, IndexError):
+            pass
+    return local_rank
+
+
+# ---------------------------------------------------------------------------------------------
+class CpuProjection:
+    """The reference's CPU composition (modeling/lora.py:29-39 + torch autograd) on `rows` tokens of the workload."""
+
+    def __init__(self, rows, dtype, threads):
+        torch.set_num_threads(threads)
+        generator = torch.Generator().manual_seed(1234)
+        self.rows, self.dtype = rows, dtype
+        self.weight = (torch.randn(OUTER, INNER, generator=generator) * .02).to(dtype)
+        self.a = (torch.randn(RANK, INNER, generator=generator) * .02).requires_grad_(True)
+        self.b = (torch.randn(OUTER, RANK, generator=generator) * .01).requires_grad_(True)
+        self.x = torch.randn(rows, INNER, generator=generator).to(dtype).requires_grad_(True)
+        self.dy = torch.randn(rows, OUTER, generator=generator).to(dtype)
+
+    def step(self):
+        from oracle import ops
+        y = ops.projection(self.x, self.weight, self.a, self.b, None, self.dtype)
+        return torch.autograd.grad(y, (self.x, self.a, self.b), self.dy)
+
+    def seconds_per_step(self, steps):
+        start = time.perf_counter()
+        for _ in range(steps):
+            self.step()
+        return (time.perf_counter() - start) / steps
+
+
+def faster_cpu_projection(threads):
+    """bf16 and fp32 compute are both legitimate reference settings; keep whichever this host runs faster."""
+    best = None
+    for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        candidate = CpuProjection(CPU_SAMPLE_ROWS, dtype, threads)
+        candidate.step()
+        seconds = candidate.seconds_per_step(1)
+        if best is None or seconds < best[0]:
+            best = (seconds, name, candidate)
+    return best[1], best[2]
+
+
+def cpu_sample_text(name, steps):
+    return (f"{steps} steps of {CPU_SAMPLE_ROWS} of the {ROWS} rows (full K, N, rank; cost is linear in rows), "
+            f"{name} compute, oracle/ops.py restating the reference CPU branch modeling/lora.py:29-39 + autograd")
+
+
+def cpu_baseline(seconds=12.0):
+    threads = os.cpu_count() or 1
+    name, problem = faster_cpu_projection(threads)
+    one = problem.seconds_per_step(1)
+    steps = max(3, min(200, int(seconds / max(one, 1e-3))))
+    per_step = problem.seconds_per_step(steps)
+    return {"value": CPU_SAMPLE_ROWS / per_step, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": cpu_sample_text(name, steps)}
+
+
+def run_reference(args):
+    """The reference arm: its CPU composition on this machine's host cores, all threads. The reference
+    is a Python package that does not travel to the GPU machine, so the timed code is its restatement in
+    oracle/ops.py; each step is one pass over a bounded sample of the workload's rows."""
+    rank, _, _ = world()
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    name, problem = faster_cpu_projection(threads)
+    for _ in range(max(args.warmup, 1)):
+        problem.step()
+    per_step = problem.seconds_per_step(args.steps)
+    value = CPU_SAMPLE_ROWS / per_step
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": name, "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": cpu_sample_text(name, args.steps)},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(gpus):
+    return {"workload": "projection_fwd_bwd_7b_gate (BASELINE.json configs[1])", "rows_per_gpu": ROWS, "in_features": INNER,
+            "out_features": OUTER, "rank": RANK, "nf4_blocksize": 64, "absmax": "fp32",
+            "parallelism": f"dp{gpus}", "l2": "inputs (134 MB X + 470 MB dY per step) are larger than the 126 MB L2"}
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    rank, local_rank, world_size = world()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path "
+                         "(use --impl reference for the CPU composition)")
+    import torch.distributed as dist
+    from causal_tuner_b200 import _lib
+    from causal_tuner_b200.dp import GradientExchange
+    from causal_tuner_b200.kernels.linear import project_group
+    from causal_tuner_b200.modeling.lora import Projection
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world_size > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+    _lib.load()
+
+    torch.manual_seed(2024)  # identical weights on every rank
+    module = Projection(INNER, OUTER, rank=RANK, device=device)
+    module.install_nf4(module.weight.detach().clone(), device, blocksize=64, nested=False)
+    with torch.no_grad():
+        module.lora_A.normal_(std=.02)
+        module.lora_B.normal_(std=.01)
+    generator = torch.Generator(device="cpu").manual_seed(77 + rank)  # rank-specific rows
+    x_host = torch.randn(ROWS, INNER, generator=generator).bfloat16().pin_memory()
+    dy_host = torch.randn(ROWS, OUTER, generator=generator).bfloat16().pin_memory()
+    x = x_host.to(device).requires_grad_(True)
+    dy = dy_host.to(device)
+    parameters = (module.lora_A, module.lora_B)
+
+    def step(inputs=x, upstream=dy):
+        y = project_group((module,), inputs)[0]
+        dx, da, db = torch.autograd.grad(y, (inputs, *parameters), upstream)
+        if distributed:
+            exchange = GradientExchange()
+            exchange.add(da)
+            exchange.add(db)
+            exchange.finish()
+        return y, dx, da, db
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(function, steps):
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            function()
+        stop.record()
+        barrier()
+        elapsed = torch.tensor([start.elapsed_time(stop)], device=device, dtype=torch.float64)
+        if distributed:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return elapsed.item() / steps
+
+    # ---- device-resident throughput --------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _lib.check_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    launches_before = _lib.launch_count()
+    _lib.timing_enable(True)
+    ms_per_step = timed(step, args.steps)
+    kernel_ms, kernel_flops, kernel_launches = _lib.timing_collect()
+    _lib.timing_enable(False)
+    launches = _lib.launch_count() - launches_before
+    clocks = sampler.stop()
+    _lib.check_device()
+
+    # ---- end to end: host buffers in, every result back out ----------------------------------
+    y_host = torch.empty(ROWS, OUTER, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(ROWS, INNER, dtype=torch.bfloat16).pin_memory()
+    da_host = torch.empty(RANK, INNER, dtype=torch.float32).pin_memory()
+    db_host = torch.empty(OUTER, RANK, dtype=torch.float32).pin_memory()
+    x_dev = torch.empty_like(x, requires_grad=True)
+    dy_dev = torch.empty_like(dy)
+    upload, download = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def e2e_step():
+        compute = torch.cuda.current_stream()
+        upload.wait_stream(compute)
+        with torch.cuda.stream(upload):
+            x_dev.data.copy_(x_host, non_blocking=True)
+            x_ready = torch.cuda.Event()
+            x_ready.record(upload)
+            dy_dev.copy_(dy_host, non_blocking=True)
+            dy_ready = torch.cuda.Event()
+            dy_ready.record(upload)
+        compute.wait_event(x_ready)
+        y = project_group((module,), x_dev)[0]
+        download.wait_stream(compute)
+        with torch.cuda.stream(download):
+            y_host.copy_(y, non_blocking=True)   # overlaps the upload of dY and the backward pass
+        compute.wait_event(dy_ready)
+        dx, da, db = torch.autograd.grad(y, (x_dev, *parameters), dy_dev)
+        if distributed:
+            exchange = GradientExchange()
+            exchange.add(da)
+            exchange.add(db)
+            exchange.finish()
+        download.wait_stream(compute)
+        with torch.cuda.stream(download):
+            dx_host.copy_(dx, non_blocking=True)
+            da_host.copy_(da, non_blocking=True)
+            db_host.copy_(db, non_blocking=True)
+        compute.wait_stream(download)
+        for tensor in (y, dx, da, db):
+            tensor.record_stream(download)
+        torch.cuda.current_stream().synchronize()  # the host owns the results before the next step
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps)
+    h2d = x_host.numel() * 2 + dy_host.numel() * 2
+    d2h = y_host.numel() * 2 + dx_host.numel() * 2 + da_host.numel() * 4 + db_host.numel() * 4
+    _lib.check_device()
+
+    # quick parity guard on the numbers that were just timed
+    checksum_ok = bool(torch.isfinite(y_host[:64].float()).all() and torch.isfinite(da_host).all())
+
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = measured_peaks()
+    tokens = ROWS * world_size
+    achieved = kernel_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
+    peak = float(peaks["bf16_tflops"])
+    line = {
+        "metric": METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world_size,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(world_size),
+        "step_tflops_per_gpu": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12,
+        "step_frac_of_bf16_peak": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12 / peak,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
+                     "peak_source": f"{peak_kind} cuBLAS bf16 burst (MEASURED_PEAKS.json)",
+                     "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps,
+                     "traffic": None},
+        "clocks": clocks,
+        "finite": checksum_ok,
+    }
+    if world_size == 1:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,8 @@ SIGNATURES = {
     "ct_tcgen05_launch_count": (_L, []),
     "ct_check_device": (_I, [_P]),
     "ct_last_error": (ctypes.c_char_p, []),
+    "ct_timing_enable": (_I, [_I]),
+    "ct_timing_collect": (_I, [_P, _P, _P]),
     "ct_nf4_decode": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "ct_cast": (_I, [_P, _I, _L, _P, _I, _L, _L, _L, _P]),
     "ct_matmul": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _L, _L, _I, _I, _I, _I, _P]),
@@ -126,3 +128,15 @@ def launch_count():
 
 def tcgen05_launch_count():
     return int(load().ct_tcgen05_launch_count())
+
+
+def timing_enable(on=True):
+    """Start (or stop) recording CUDA-event times of every tcgen05 GEMM launch."""
+    check(load().ct_timing_enable(int(bool(on))))
+
+
+def timing_collect():
+    """(total device ms, total algorithmic FLOP, launches) of the tcgen05 GEMM since timing_enable."""
+    ms, flops, count = ctypes.c_double(), ctypes.c_double(), ctypes.c_int64()
+    check(load().ct_timing_collect(ctypes.byref(ms), ctypes.byref(flops), ctypes.byref(count)))
+    return ms.value, flops.value, count.value

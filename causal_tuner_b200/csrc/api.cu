@@ -4,6 +4,8 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -33,6 +35,48 @@ int check_launch(const char* what) {
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail(CT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
   return CT_OK;
+}
+
+// ---- per-launch timing -------------------------------------------------------------
+namespace {
+struct TimedLaunch {
+  cudaEvent_t start, stop;
+  double flops;
+};
+std::mutex g_timing_mutex;
+std::vector<TimedLaunch> g_timed;
+std::vector<cudaEvent_t> g_event_pool;
+std::atomic<int> g_timing_on{0};
+cudaEvent_t g_pending_start = nullptr;
+
+cudaEvent_t take_event() {
+  if (!g_event_pool.empty()) {
+    cudaEvent_t e = g_event_pool.back();
+    g_event_pool.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+  return e;
+}
+}  // namespace
+
+bool timing_enabled() { return g_timing_on.load(std::memory_order_relaxed) != 0; }
+
+void timing_begin(cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  g_pending_start = take_event();
+  if (g_pending_start) cudaEventRecord(g_pending_start, stream);
+}
+
+void timing_end(cudaStream_t stream, double flops) {
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  if (!g_pending_start) return;
+  cudaEvent_t stop = take_event();
+  if (!stop) return;
+  cudaEventRecord(stop, stream);
+  g_timed.push_back({g_pending_start, stop, flops});
+  g_pending_start = nullptr;
 }
 
 int* device_error_flag() {
@@ -108,6 +152,40 @@ extern "C" int ct_abi_version(void) { return 1; }
 extern "C" int64_t ct_launch_count(void) { return g_launches.load(); }
 extern "C" int64_t ct_tcgen05_launch_count(void) { return g_tc_launches.load(); }
 extern "C" const char* ct_last_error(void) { return g_error_text; }
+
+extern "C" int ct_timing_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  for (auto& t : g_timed) {
+    g_event_pool.push_back(t.start);
+    g_event_pool.push_back(t.stop);
+  }
+  g_timed.clear();
+  g_timing_on.store(on ? 1 : 0);
+  return CT_OK;
+}
+
+extern "C" int ct_timing_collect(double* total_ms, double* total_flops, int64_t* launches) {
+  if (!total_ms || !total_flops || !launches) return fail(CT_ERR_ARG, "ct_timing_collect: null pointer");
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  double ms = 0, flops = 0;
+  int64_t count = 0;
+  for (auto& t : g_timed) {
+    cudaError_t err = cudaEventSynchronize(t.stop);
+    float one = 0;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&one, t.start, t.stop);
+    if (err != cudaSuccess) return fail(CT_ERR_CUDA, "ct_timing_collect: %s", cudaGetErrorString(err));
+    ms += one;
+    flops += t.flops;
+    ++count;
+    g_event_pool.push_back(t.start);
+    g_event_pool.push_back(t.stop);
+  }
+  g_timed.clear();
+  *total_ms = ms;
+  *total_flops = flops;
+  *launches = count;
+  return CT_OK;
+}
 
 extern "C" int ct_check_device(void* stream) {
   cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

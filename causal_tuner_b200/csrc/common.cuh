@@ -16,6 +16,10 @@ void count_launch(bool tcgen05);
 int check_launch(const char* what);
 // Per-device int the kernels raise when a bounded wait gives up.
 int* device_error_flag();
+// Optional per-launch timing of the tcgen05 GEMM (CUDA events on the launching stream).
+bool timing_enabled();
+void timing_begin(cudaStream_t stream);
+void timing_end(cudaStream_t stream, double flops);
 
 // ---- dtype helpers ------------------------------------------------------------
 __host__ __device__ inline int dtype_size(int dtype) { return dtype == CT_F32 ? 4 : 2; }

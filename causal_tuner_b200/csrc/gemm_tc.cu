@@ -366,6 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
         const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t raw[32];
+        __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped the previous stores
         tmem_load_32(taddr + c * 32, raw);
         if (!row_ok) continue;
         float v[32];
@@ -579,7 +580,14 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   int sms = sm_count();
   if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot read the SM count");
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  const bool timed = timing_enabled();
+  if (timed) timing_begin(stream);
   gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  if (timed) {
+    double k_total = 0;
+    for (int s = 0; s < g.nseg; ++s) k_total += static_cast<double>(g.seg[s].k);
+    timing_end(stream, 2.0 * static_cast<double>(g.M) * static_cast<double>(g.N) * k_total);
+  }
   count_launch(true);
   return check_launch("gemm_tcgen05");
 }

@@ -1,0 +1,91 @@
+"""Batch data parallelism for the adapter gradients: one process per GPU, one exchange step.
+
+Every rank holds a full replica (frozen NF4 base + fp32 adapters) and runs the projection /
+MLP operators on its own packed rows. The only collective is a SUM all-reduce of the fp32
+LoRA gradients (plus, for a trainer, the scalar loss weight and loss) - the insertion point
+is between the last micro-batch backward and the gradient division of the reference's
+Trainer.update (training/engine.py:90-97), which then yields exactly the single-device
+weighted mean. The reference itself is single-device; this module is the added exchange.
+
+Gradients are packed into flat fp32 buckets so that a collective moves tens of megabytes,
+and each bucket's all-reduce is issued asynchronously as soon as it is full, so that the
+collectives of early buckets overlap whatever the caller computes next (NCCL over
+NVLink/NVSwitch on GPUs, gloo on CPU ranks in the tests).
+"""
+
+import torch
+import torch.distributed as dist
+
+
+class GradientExchange:
+    """SUM all-reduce of a list of gradient tensors through flat buckets.
+
+    >>> exchange = GradientExchange(bucket_bytes=64 << 20)
+    >>> exchange.add(da); exchange.add(db)      # may launch a bucket's collective
+    >>> exchange.finish()                       # launches the rest, waits, writes results back in place
+    """
+
+    def __init__(self, group=None, bucket_bytes=64 << 20):
+        if bucket_bytes <= 0:
+            raise ValueError("bucket_bytes must be positive")
+        self.group, self.bucket_bytes = group, bucket_bytes
+        self._pending, self._pending_bytes, self._inflight = [], 0, []
+        self.collectives = 0
+
+    @property
+    def world_size(self):
+        return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
+
+    def add(self, gradient):
+        if gradient.dtype != torch.float32:
+            raise TypeError("adapter gradients are exchanged in fp32")
+        if self.world_size == 1:
+            return
+        self._pending.append(gradient)
+        self._pending_bytes += gradient.numel() * 4
+        if self._pending_bytes >= self.bucket_bytes:
+            self._launch()
+
+    def _launch(self):
+        if not self._pending:
+            return
+        tensors, self._pending, self._pending_bytes = self._pending, [], 0
+        if len(tensors) == 1 and tensors[0].is_contiguous():
+            flat = tensors[0].view(-1)
+        else:
+            flat = torch.cat([t.reshape(-1) for t in tensors])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self.collectives += 1
+        self._inflight.append((work, flat, tensors))
+
+    def finish(self):
+        """Flush the last bucket, wait for every collective and copy the sums back into the gradients."""
+        self._launch()
+        for work, flat, tensors in self._inflight:
+            work.wait()
+            if len(tensors) == 1 and flat.data_ptr() == tensors[0].data_ptr():
+                continue
+            offset = 0
+            for tensor in tensors:
+                count = tensor.numel()
+                tensor.copy_(flat[offset:offset + count].view_as(tensor))
+                offset += count
+        self._inflight = []
+
+
+def exchange_gradients(gradients, group=None, bucket_bytes=64 << 20):
+    """In-place SUM all-reduce of `gradients` across the ranks of `group`; returns the number of collectives."""
+    exchange = GradientExchange(group, bucket_bytes)
+    for gradient in gradients:
+        exchange.add(gradient)
+    exchange.finish()
+    return exchange.collectives
+
+
+def shard_rows(total_rows, rank, world_size):
+    """Contiguous [start, stop) slice of packed rows owned by `rank`; remainders go to the first ranks."""
+    if not 0 <= rank < world_size:
+        raise ValueError("rank outside the world")
+    base, extra = divmod(total_rows, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)

@@ -61,6 +61,15 @@ CT_API int64_t ct_tcgen05_launch_count(void);
  * the current device gave up on a bounded wait since the last call (the flag is
  * cleared), or CT_ERR_CUDA with the sticky CUDA error. */
 CT_API int ct_check_device(void* stream);
+/* Per-launch timing of the tcgen05 GEMM, for roofline reports. While enabled,
+ * every launch is bracketed by CUDA events recorded on the launching stream.
+ * ct_timing_enable(on) clears what was recorded and switches recording on/off;
+ * ct_timing_collect waits for the recorded launches and returns their summed
+ * device time (ms), their summed algorithmic work (2*M*N*K FLOP per launch, true
+ * sizes, no padding) and their number, then clears the record. No counterpart in
+ * the reference (it times whole steps only, train.py:219-223). */
+CT_API int ct_timing_enable(int on);
+CT_API int ct_timing_collect(double* total_ms, double* total_flops, int64_t* launches);
 /* Text of the most recent CT_ERR_* on the calling thread (static storage). */
 CT_API const char* ct_last_error(void);
 
