@@ -267,7 +267,19 @@ def run_ours(args):
     clocks = sampler.stop()
     _lib.check_device()
 
-    # ---- end to end: host buffers in, every result back out ----------------------------------
+    e2e_ms, e2e_steps, h2d, d2h = None, 0, 0, 0
+    if not args.no_e2e:
+        e2e_ms, e2e_steps, h2d, d2h = end_to_end(args, module, parameters, x, dy, x_host, dy_host, distributed, timed)
+    _lib.check_device()
+    finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, h2d, d2h, launches, kernel_ms,
+           kernel_flops, kernel_launches, clocks)
+
+
+def end_to_end(args, module, parameters, x, dy, x_host, dy_host, distributed, timed):
+    """Host buffers in, every result back out, copies overlapped with compute on two side streams."""
+    from causal_tuner_b200.dp import GradientExchange
+    from causal_tuner_b200.kernels.linear import project_group
+    device = x.device
     y_host = torch.empty(ROWS, OUTER, dtype=torch.bfloat16).pin_memory()
     dx_host = torch.empty(ROWS, INNER, dtype=torch.bfloat16).pin_memory()
     da_host = torch.empty(RANK, INNER, dtype=torch.float32).pin_memory()
@@ -314,11 +326,14 @@ def run_ours(args):
     e2e_ms = timed(e2e_step, e2e_steps)
     h2d = x_host.numel() * 2 + dy_host.numel() * 2
     d2h = y_host.numel() * 2 + dx_host.numel() * 2 + da_host.numel() * 4 + db_host.numel() * 4
-    _lib.check_device()
+    if not (torch.isfinite(y_host[:64].float()).all() and torch.isfinite(da_host).all()):
+        raise RuntimeError("end-to-end leg produced non-finite results")
+    return e2e_ms, e2e_steps, h2d, d2h
 
-    # quick parity guard on the numbers that were just timed
-    checksum_ok = bool(torch.isfinite(y_host[:64].float()).all() and torch.isfinite(da_host).all())
 
+def finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, h2d, d2h, launches, kernel_ms,
+           kernel_flops, kernel_launches, clocks):
+    import torch.distributed as dist
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -334,8 +349,9 @@ def run_ours(args):
         "config": workload_config(world_size),
         "step_tflops_per_gpu": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12,
         "step_frac_of_bf16_peak": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12 / peak,
-        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "e2e": None if e2e_ms is None else {
+            "value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
@@ -343,9 +359,8 @@ def run_ours(args):
                      "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps,
                      "traffic": None},
         "clocks": clocks,
-        "finite": checksum_ok,
     }
-    if world_size == 1:
+    if world_size == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
     if distributed:
@@ -353,12 +368,18 @@ def run_ours(args):
 
 
 def main():
+    global ROWS
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--rows", type=int, default=ROWS,
+                        help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
+    parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
     args = parser.parse_args()
+    ROWS = args.rows
     if args.impl == "reference":
         run_reference(args)
     else:
