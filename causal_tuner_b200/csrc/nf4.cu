@@ -1,11 +1,13 @@
 // NF4 decode: packed 4-bit codes + per-block absmax -> dense bf16/fp16/fp32.
 //
 // HBM-bound: 0.5 B of codes + 4/blocksize B of absmax read and 2 B (bf16) or
-// 4 B (fp32) written per element. Each thread takes one 128-bit load of packed
-// codes (32 elements, half of a 64-element block), looks both nibbles of every
-// byte up in a 256-entry shared-memory table of (high, low) code pairs, scales
-// with one fp32 multiply per element and writes 64 contiguous bytes of bf16.
-// A warp therefore reads 512 contiguous bytes and writes 2 KB contiguous bytes.
+// 4 B (fp32) written per element. Per step each thread takes one 32-bit load of
+// packed codes (8 elements), looks every nibble up in a shared-memory copy of
+// the 16-entry code table, scales with one fp32 multiply per element and writes
+// one 16-byte vector of bf16: a warp reads 128 contiguous bytes and writes 512
+// contiguous bytes per step, so every sector is written whole. The table is
+// stored once per lane (entry i of lane l at word 32*i + l), so the
+// data-dependent look-ups of a warp always fall into 32 different banks.
 //
 // Arithmetic follows the reference Triton kernel (kernels/nf4_cuda.py:9-29):
 // high nibble first, fp32 product, nested scale = code2[u8] * absmax2 + offset
@@ -17,7 +19,8 @@ namespace ct {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kChunk = 32;  // elements per thread (16 packed bytes)
+constexpr int kGroup = 8;  // elements per thread per step: 4 packed bytes in, 16 bytes of bf16 out
+constexpr int kSteps = 4;  // steps per thread
 
 struct Nf4Params {
   const uint8_t* packed;
@@ -32,7 +35,7 @@ struct Nf4Params {
   int blocksize2;
   int nested;
   int state_dtype;
-  int vector_ok;  // packed and out are 16-byte aligned
+  int vector_ok;  // packed is 4-byte aligned and out 16-byte aligned
 };
 
 __device__ __forceinline__ float block_scale(const Nf4Params& p, int64_t group) {
@@ -44,86 +47,75 @@ __device__ __forceinline__ float block_scale(const Nf4Params& p, int64_t group) 
 }
 
 template <typename OutT>
-__device__ __forceinline__ void store_chunk(OutT* out, const float (&v)[kChunk]);
+__device__ __forceinline__ void store_group(OutT* out, const float (&v)[kGroup]);
 
 template <>
-__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* out, const float (&v)[kChunk]) {
-  uint4* dst = reinterpret_cast<uint4*>(out);
+__device__ __forceinline__ void store_group<__nv_bfloat16>(__nv_bfloat16* out, const float (&v)[kGroup]) {
+  uint32_t w[4];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __nv_bfloat162 pair = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
-      w[j] = *reinterpret_cast<uint32_t*>(&pair);
-    }
-    dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&pair);
   }
+  *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 template <>
-__device__ __forceinline__ void store_chunk<__half>(__half* out, const float (&v)[kChunk]) {
-  uint4* dst = reinterpret_cast<uint4*>(out);
+__device__ __forceinline__ void store_group<__half>(__half* out, const float (&v)[kGroup]) {
+  uint32_t w[4];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __half2 pair = __floats2half2_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
-      w[j] = *reinterpret_cast<uint32_t*>(&pair);
-    }
-    dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+  for (int j = 0; j < 4; ++j) {
+    __half2 pair = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&pair);
   }
+  *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 template <>
-__device__ __forceinline__ void store_chunk<float>(float* out, const float (&v)[kChunk]) {
+__device__ __forceinline__ void store_group<float>(float* out, const float (&v)[kGroup]) {
   float4* dst = reinterpret_cast<float4*>(out);
-#pragma unroll
-  for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+  dst[1] = make_float4(v[4], v[5], v[6], v[7]);
 }
 
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p) {
-  __shared__ float2 lut[256];
-  {
-    const int b = threadIdx.x;
-    lut[b] = make_float2(__ldg(p.code + (b >> 4)), __ldg(p.code + (b & 15)));
-  }
+  __shared__ float lut[16 * 32];
+  lut[threadIdx.x] = __ldg(p.code + (threadIdx.x >> 5));
+  lut[threadIdx.x + kThreads] = __ldg(p.code + ((threadIdx.x + kThreads) >> 5));
   __syncthreads();
-
-  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  const int64_t first = chunk * kChunk;
-  if (first >= p.n) return;
+  const float* mine = lut + (threadIdx.x & 31);
   OutT* out = static_cast<OutT*>(p.out);
+  const bool vector = p.vector_ok && p.blocksize % kGroup == 0;
 
-  if (p.vector_ok && first + kChunk <= p.n && p.blocksize % kChunk == 0) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.packed + first / 2));
-    const float scale = block_scale(p, first / p.blocksize);
-    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-    float v[kChunk];
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
+#pragma unroll 1
+  for (int step = 0; step < kSteps; ++step) {
+    const int64_t group = (static_cast<int64_t>(blockIdx.x) * kSteps + step) * kThreads + threadIdx.x;
+    const int64_t first = group * kGroup;
+    if (first >= p.n) return;
+    if (vector && first + kGroup <= p.n) {
+      const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.packed + first / 2));
+      const float scale = block_scale(p, first / p.blocksize);
+      float v[kGroup];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        const float2 pair = lut[(words[w] >> (8 * b)) & 255u];
-        v[8 * w + 2 * b] = round_dtype(__fmul_rn(pair.x, scale), p.state_dtype);
-        v[8 * w + 2 * b + 1] = round_dtype(__fmul_rn(pair.y, scale), p.state_dtype);
+        const uint32_t byte = (word >> (8 * b)) & 255u;
+        v[2 * b] = round_dtype(__fmul_rn(mine[(byte >> 4) * 32], scale), p.state_dtype);
+        v[2 * b + 1] = round_dtype(__fmul_rn(mine[(byte & 15u) * 32], scale), p.state_dtype);
       }
+      store_group<OutT>(out + first, v);
+      continue;
     }
-    store_chunk<OutT>(out + first, v);
-    return;
-  }
-
-  // Ragged tail, unaligned buffers or block sizes that are not multiples of 32:
-  // one packed byte at a time, element stores guarded by n.
-  const int64_t last = (first + kChunk < p.n) ? first + kChunk : p.n;
-  for (int64_t e = first; e < last; e += 2) {
-    const uint8_t byte = __ldg(p.packed + e / 2);
-    const float2 pair = lut[byte];
-    const float scale = block_scale(p, e / p.blocksize);
-    out[e] = from_float<OutT>(round_dtype(__fmul_rn(pair.x, scale), p.state_dtype));
-    if (e + 1 < p.n) out[e + 1] = from_float<OutT>(round_dtype(__fmul_rn(pair.y, scale), p.state_dtype));
+    // Ragged tail, unaligned buffers or block sizes that are not multiples of 8:
+    // one packed byte at a time, element stores guarded by n.
+    const int64_t last = (first + kGroup < p.n) ? first + kGroup : p.n;
+    for (int64_t e = first; e < last; e += 2) {
+      const uint8_t byte = __ldg(p.packed + e / 2);
+      const float high = mine[(byte >> 4) * 32], low = mine[(byte & 15) * 32];
+      const float scale = block_scale(p, e / p.blocksize);
+      out[e] = from_float<OutT>(round_dtype(__fmul_rn(high, scale), p.state_dtype));
+      if (e + 1 < p.n) out[e + 1] = from_float<OutT>(round_dtype(__fmul_rn(low, scale), p.state_dtype));
+    }
   }
 }
 
@@ -143,9 +135,9 @@ extern "C" int ct_nf4_decode(const uint8_t* packed, const void* absmax, const fl
     return fail(CT_ERR_ARG, "ct_nf4_decode: dtype");
   Nf4Params p{packed, absmax, code, code2, absmax2, offset, out, n, blocksize, blocksize2 > 0 ? blocksize2 : 1,
               nested, state_dtype,
-              ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(out)) & 15) == 0};
-  const int64_t chunks = (n + kChunk - 1) / kChunk;
-  const unsigned blocks = static_cast<unsigned>((chunks + kThreads - 1) / kThreads);
+              (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0};
+  const int64_t per_block = static_cast<int64_t>(kThreads) * kSteps * kGroup;
+  const unsigned blocks = static_cast<unsigned>((n + per_block - 1) / per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype == CT_BF16) nf4_decode_kernel<__nv_bfloat16><<<blocks, kThreads, 0, s>>>(p);
   else if (out_dtype == CT_F16) nf4_decode_kernel<__half><<<blocks, kThreads, 0, s>>>(p);
