@@ -33,6 +33,8 @@ SIGNATURES = {
     "ct_input_gradient": (_I, [_P, _L, _P, _L, _P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _I, _P]),
     "ct_parameter_gradients_workspace": (_L, [_L, _L, _L, _L, _I, _I]),
     "ct_parameter_gradients": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, _P, _I, _P]),
+    "ct_parameter_gradients_noalloc_capacity": (_L, []),
+    "ct_parameter_gradients_noalloc": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, _I, _P]),
     "ct_swiglu": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P]),
     "ct_rope": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "ct_add_inplace": (_I, [_P, _P, _L, _I, _P]),

@@ -287,3 +287,63 @@ extern "C" int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy
   if (rc != CT_OK) return rc;
   return token_contraction(dy, ld_dy, xa, ld_xa, db, N, r, T, add, dtype, workspace, path, s);
 }
+
+// ---- parameter gradients without any allocation ----------------------------------------------
+// Slice-partial scratch that lives in the library image itself. Every GPU that loads the library
+// holds these bytes until the process exits. In HOST code the array's name is only a stand-in for
+// the symbol; the device address comes from cudaGetSymbolAddress, once per device.
+namespace {
+constexpr int64_t kNoAllocScratchBytes = 16ll << 20;  // e.g. 4 slices of a 256 x 4096 fp32 gradient
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ int g_noalloc_error_flag;
+void* g_noalloc_scratch_address[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// First use on a device: resolve the device addresses of the two symbols above (no allocation).
+int noalloc_setup(void** scratch) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(CT_ERR_CUDA, "ct_parameter_gradients_noalloc: no current device");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_scratch_address[dev]) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+    if (err != cudaSuccess || !address)
+      return fail(CT_ERR_CUDA, "ct_parameter_gradients_noalloc: cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(err));
+    if (!g_error_flags[dev]) {
+      // The GEMM reports bounded-wait timeouts through a per-device int that the other entry points
+      // allocate on first use; here it is a static symbol instead, so this path never allocates.
+      void* flag = nullptr;
+      err = cudaGetSymbolAddress(&flag, g_noalloc_error_flag);
+      if (err != cudaSuccess || !flag)
+        return fail(CT_ERR_CUDA, "ct_parameter_gradients_noalloc: cudaGetSymbolAddress(flag): %s", cudaGetErrorString(err));
+      g_error_flags[dev] = static_cast<int*>(flag);
+    }
+    g_noalloc_scratch_address[dev] = address;
+  }
+  *scratch = g_noalloc_scratch_address[dev];
+  return CT_OK;
+}
+}  // namespace
+
+extern "C" int64_t ct_parameter_gradients_noalloc_capacity(void) { return kNoAllocScratchBytes; }
+
+extern "C" int ct_parameter_gradients_noalloc(const void* x, int64_t ldx, const void* dy, int64_t ld_dy,
+                                              const void* low, int64_t ld_low, const void* xa, int64_t ld_xa,
+                                              float* da, float* db, int64_t T, int64_t K, int64_t N, int64_t r,
+                                              int add, int dtype, int path, void* stream) {
+  const int64_t need = ct_parameter_gradients_workspace(T, K, N, r, dtype, path);
+  if (need > kNoAllocScratchBytes)
+    return fail(CT_ERR_UNSUPPORTED,
+                "ct_parameter_gradients_noalloc: this problem needs %lld bytes of slice scratch, the built-in "
+                "array holds %lld; use ct_parameter_gradients with a caller-provided workspace",
+                (long long)need, (long long)kNoAllocScratchBytes);
+  void* scratch = nullptr;
+  const int rc = noalloc_setup(&scratch);
+  if (rc != CT_OK) return rc;
+  // Nothing in the scratch has to start at zero: every slice plane is written in full by the GEMM
+  // (one store per element) before the ordered reduction reads it.
+  return ct_parameter_gradients(x, ldx, dy, ld_dy, low, ld_low, xa, ld_xa, da, db, T, K, N, r, add, dtype, scratch,
+                                path, stream);
+}

@@ -150,6 +150,35 @@ CT_API int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy, in
                            int64_t N, int64_t r, int add, int dtype, void* workspace,
                            int path, void* stream);
 
+/* ---- LoRA parameter gradients for callers that must not allocate ---------------
+ * No counterpart in the reference (its gradients go through torch's caching
+ * allocator, kernels/linear.py:102). Same arithmetic, same fixed summation order
+ * and bit-identical results as ct_parameter_gradients, but the slice scratch is
+ * a fixed array inside the library image instead of a caller-provided workspace,
+ * and the call performs no cudaMalloc / cudaFree (nor any allocating library
+ * routine). It is meant for hosts that cannot allocate device memory at this
+ * point: a runtime that handed the whole GPU to its own memory pool at start-up
+ * (a raw cudaMalloc would then fail), or a step loop that cannot accept the
+ * device-wide synchronisation a cudaMalloc or cudaFree implies.
+ *   - Capacity: ct_parameter_gradients_noalloc_capacity() bytes (16 MiB, e.g. the
+ *     four slices of a rank-256 gradient over 4096 columns). Every GPU that loads
+ *     the library holds that array until the process exits. A problem whose
+ *     ct_parameter_gradients_workspace(...) exceeds it is refused with
+ *     CT_ERR_UNSUPPORTED and nothing is launched.
+ *   - The first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's partial
+ *     sums; nothing in it needs clearing (every slice is fully overwritten before
+ *     it is read), but two calls whose kernels overlap on the GPU (different
+ *     streams, or several host threads) race on it. Keep calls on one stream or
+ *     order them with events. */
+CT_API int64_t ct_parameter_gradients_noalloc_capacity(void);
+CT_API int ct_parameter_gradients_noalloc(const void* x, int64_t ldx, const void* dy,
+                                   int64_t ld_dy, const void* low, int64_t ld_low,
+                                   const void* xa, int64_t ld_xa, float* da, float* db,
+                                   int64_t T, int64_t K, int64_t N, int64_t r, int add,
+                                   int dtype, int path, void* stream);
+
 /* ---- SwiGLU activation ------------------------------------------------------
  * Replaces kernels/mlp_cuda.py:10-35 (_activation / activation) and the
  * separate-output backward of kernels/mlp_cuda.py:45-51.
