@@ -55,13 +55,16 @@ def world():
 
 # ---------------------------------------------------------------------------------------------
 class ClockSampler(threading.Thread):
-    """Reads SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+    """Reads SM clock and throttle reasons of one GPU through NVML. It is started before the warm-up
+    (NVML start-up takes tens of milliseconds); `window()` keeps the samples taken between `mark()` and
+    `stop()`, i.e. during the timed region."""
 
-    def __init__(self, index, period=0.05):
+    def __init__(self, index, period=0.004):
         super().__init__(daemon=True)
         self.index, self.period = index, period
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.max_mhz, self.error = [], None, None
         self._stop_event = threading.Event()
+        self._start_time = None
 
     def run(self):
         try:
@@ -69,34 +72,40 @@ class ClockSampler(threading.Thread):
             pynvml.nvmlInit()
             handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
-            names = {
-                "nvmlClocksEventReasonHwSlowdown": "hw_slowdown",
-                "nvmlClocksEventReasonHwThermalSlowdown": "hw_thermal_slowdown",
-                "nvmlClocksEventReasonSwThermalSlowdown": "sw_thermal_slowdown",
-                "nvmlClocksEventReasonSwPowerCap": "sw_power_cap",
-                "nvmlClocksThrottleReasonHwSlowdown": "hw_slowdown",
-                "nvmlClocksThrottleReasonHwThermalSlowdown": "hw_thermal_slowdown",
-                "nvmlClocksThrottleReasonSwThermalSlowdown": "sw_thermal_slowdown",
-                "nvmlClocksThrottleReasonSwPowerCap": "sw_power_cap",
-            }
-            masks = {getattr(pynvml, k): v for k, v in names.items() if hasattr(pynvml, k)}
+            names = {"HwSlowdown": "hw_slowdown", "HwThermalSlowdown": "hw_thermal_slowdown",
+                     "SwThermalSlowdown": "sw_thermal_slowdown", "SwPowerCap": "sw_power_cap"}
+            masks = {}
+            for suffix, label in names.items():
+                for prefix in ("nvmlClocksEventReason", "nvmlClocksThrottleReason"):
+                    if hasattr(pynvml, prefix + suffix):
+                        masks[getattr(pynvml, prefix + suffix)] = label
             read = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
                 pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
             while not self._stop_event.is_set():
-                self.samples.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                clock = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
                 active = read(handle)
-                self.reasons.update(label for mask, label in masks.items() if active & mask)
+                labels = tuple(label for mask, label in masks.items() if active & mask)
+                self.samples.append((time.perf_counter(), clock, labels))
                 time.sleep(self.period)
         except Exception as error:  # NVML missing: report that instead of clocks
-            self.reasons.add(f"nvml_unavailable:{type(error).__name__}")
+            self.error = f"nvml_unavailable:{type(error).__name__}"
+
+    def mark(self):
+        self._start_time = time.perf_counter()
 
     def stop(self):
+        end = time.perf_counter()
         self._stop_event.set()
         self.join(timeout=2)
-        ordered = sorted(self.samples)
-        median = ordered[len(ordered) // 2] if ordered else None
-        return {"sm_mhz": median, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(ordered)}
+        inside = [s for s in self.samples if self._start_time is not None and self._start_time <= s[0] <= end]
+        if not inside and self.samples:   # region shorter than one sampling period: nearest sample
+            inside = [min(self.samples, key=lambda s: abs(s[0] - end))]
+        ordered = sorted(s[1] for s in inside)
+        reasons = sorted({label for s in inside for label in s[2]})
+        if self.error:
+            reasons.append(self.error)
+        return {"sm_mhz": ordered[len(ordered) // 2] if ordered else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(ordered)}
 
 
 def physical_gpu_index(local_rank):
@@ -253,11 +262,12 @@ def run_ours(args):
         return elapsed.item() / steps
 
     # ---- device-resident throughput --------------------------------------------------------
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     _lib.check_device()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
+    sampler.mark()
     launches_before = _lib.launch_count()
     _lib.timing_enable(True)
     ms_per_step = timed(step, args.steps)

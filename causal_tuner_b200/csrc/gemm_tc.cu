@@ -24,24 +24,44 @@
 // A contraction can also be split into `splits` slices whose fp32 partial tiles
 // go to separate planes (summed afterwards in a fixed order).
 //
+// Two variants share one body. gemm_tcgen05_kernel: one CTA per 128 x 256 tile, 4 stages of
+// 48 KB. gemm_tcgen05_pair_kernel: a cluster of two CTAs per 256 x 256 tile; each CTA stages
+// its 128 rows of A and its 128 columns of B (6 stages of 32 KB), the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256) for both, the tensor cores fetch the other half of B from
+// the peer's shared memory, TMA completions of both CTAs are counted on the leader's barrier
+// and tcgen05.commit releases stages / publishes accumulators in both CTAs. That halves the
+// B bytes each SM has to stage per MMA.
+//
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA
 // raises the device error flag, stops issuing work, frees its TMEM and exits.
 // No TMA load in this file uses cluster multicast.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ct {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+// BM rows of A per CTA; a tile is (BM * CTAS) x BN where CTAS is 1, or 2 for a CTA pair that
+// shares one cta_group::2 MMA (each CTA then stages BM rows of A and BN / 2 columns of B).
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
-constexpr uint32_t B_TILE_BYTES = BN * BK * 2;  // 32 KB
-constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr uint32_t MN_BOX_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
 constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulators
+constexpr int kMaxStages = 6;
+
+template <int CTAS, int STAGES_>
+struct Shape {
+  static constexpr int kStages = STAGES_;
+  static constexpr int kBRows = BN / CTAS;                    // B columns staged by one CTA
+  static constexpr uint32_t kBTileBytes = kBRows * BK * 2;    // 32 KB or 16 KB
+  static constexpr uint32_t kStageBytes = A_TILE_BYTES + kBTileBytes;
+  static constexpr size_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 constexpr int GROUP_M = 16;                     // tile rasterisation: 16 row tiles share a sweep over columns
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
@@ -99,11 +119,11 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait. Returns false after kWaitLimitNs, having raised the error flag
-// with `code` (which names the waiting role).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
-                                          int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait. The common case (barrier already complete) is one try_wait; the polling loop with
+// its wall-clock limit lives out of line so that the issue loops stay short. Returns false after
+// kWaitLimitNs, having raised the error flag with `code` (which names the waiting role).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
+                                            int code) {
   const uint64_t start = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
@@ -118,6 +138,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, error_flag, code);
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
@@ -129,17 +154,68 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
+// The 64-bit shared-memory descriptors are passed as (low, high) words: the high word is constant
+// per operand orientation, only the start-address field in the low word moves.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- CTA-pair (cluster of two) helpers -----------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load issued by either CTA of a pair; the completion bytes go to `cluster_bar`, which may
+// live in the peer CTA. No multicast: the data lands in the issuing CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (once the MMAs issued so far are complete) on the barrier at this offset in BOTH CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both)
+               : "memory");
 }
 
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -155,22 +231,21 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
-// Offsets are in bytes; the hardware fields hold them divided by 16.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
-  uint64_t d = static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1, as two 32-bit words.
+// Low word: start address >> 4 (bits 0-13) and leading-dimension byte offset >> 4 (bits 16-29).
+// High word: stride byte offset >> 4 (bits 0-13), version 1 (bits 14-15), swizzle mode 2 (bits 29-31).
+__device__ __forceinline__ uint32_t desc_low(uint32_t addr, uint32_t leading_bytes) {
+  return ((addr & 0x3FFFFu) >> 4) | (((leading_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t desc_high(uint32_t stride_bytes) {
+  return ((stride_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
 }
 
-// Instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256.
-__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn) {
+// Instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128 (one CTA) or 256 (CTA pair), N = 256.
+__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, int m) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
          (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-         (static_cast<uint32_t>(BM >> 4) << 24);
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 struct TileCoord {
@@ -204,7 +279,87 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
+// Epilogue of one 32-column chunk of one accumulator row: bias, previous value, rounding, residual, store.
+__device__ __forceinline__ void store_chunk(const TcParams& p, float (&v)[32], char* out_plane, int64_t row,
+                                            int64_t col0) {
+  const bool full = col0 + 32 <= p.N;
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+  }
+  if (p.out_f32) {
+    float* dst = reinterpret_cast<float*>(out_plane) + row * p.ldo + col0;
+    if (full && p.vec_store) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+      if (p.beta) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 o = d4[q];
+          v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = p.beta ? dst[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_plane) + row * p.ldo + col0;
+    const __nv_bfloat16* res = p.residual ? p.residual + row * p.ld_res + col0 : nullptr;
+    if (full && p.vec_store) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      if (p.beta) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 o = d4[q];
+          const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            v[8 * q + 2 * j] += f.x;
+            v[8 * q + 2 * j + 1] += f.y;
+          }
+        }
+      }
+      if (res) {
+        const uint4* r4 = reinterpret_cast<const uint4*>(res);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 o = __ldg(r4 + q);
+          const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            v[8 * q + 2 * j] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j])), f.x);
+            v[8 * q + 2 * j + 1] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j + 1])), f.y);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        d4[q] = make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
+                           pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+        float x = v[j];
+        if (p.beta) x += __bfloat162float(dst[j]);
+        if (res) x = __fadd_rn(__bfloat162float(__float2bfloat16_rn(x)), __bfloat162float(res[j]));
+        dst[j] = __float2bfloat16_rn(x);
+      }
+    }
+  }
+}
+
+// One body for both variants. CTAS == 1: every CTA owns a 128 x 256 tile. CTAS == 2: the two CTAs
+// of a cluster own a 256 x 256 tile; each stages its 128 rows of A and its 128 columns of B, the
+// even ("leader") CTA issues one cta_group::2 MMA per k step for both, and both run their own
+// epilogue on their 128 accumulator rows.
+template <int CTAS, int STAGES_>
+__device__ __forceinline__ void gemm_body(const TcParams& p) {
+  using S = Shape<CTAS, STAGES_>;
+  constexpr int STAGES = S::kStages;
+  constexpr uint32_t STAGE_BYTES = S::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -214,6 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = CTAS == 2 ? cluster_rank() : 0u;  // position in the CTA pair; 0 leads
+  const bool leader = rank == 0;
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -228,118 +385,168 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 4);
+      mbar_init(tmem_empty_bar(a), 4 * CTAS);  // one arrival per epilogue warp of every CTA of the tile
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CTAS == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+  const int first_tile = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
+  constexpr int TILE_M = BM * CTAS;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop (uniform control flow keeps addresses and counters in
+    // uniform registers); lane 0 alone issues the copies.
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+      for (int tile = first_tile; tile < total_tiles && alive; tile += tile_step) {
         const TileCoord tc = tile_coord(tile, p);
         int kb_begin, kb_end;
         split_range(p, tc.split, kb_begin, kb_end);
-        int seg = 0, seg_first = 0;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          while (kb >= seg_first + p.seg[seg].k_blocks) {
-            seg_first += p.seg[seg].k_blocks;
-            ++seg;
-          }
-          const int k0 = (kb - seg_first) * BK;
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.error_flag, 1)) {
-            alive = false;
-            break;
-          }
-          const uint32_t a_dst = smem_base + stage * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
-          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+        const int a_row0 = tc.m * TILE_M + static_cast<int>(rank) * BM;
+        const int b_row0 = tc.n * BN + static_cast<int>(rank) * S::kBRows;
+        int seg_first = 0;
+        for (int seg = 0; seg < p.nseg && alive; ++seg) {
           const TcSegment& sg = p.seg[seg];
-          if (!sg.a_mn) {
-            tma_load_2d(a_dst, &sg.a, full_bar(stage), k0, tc.m * BM);
-          } else {
+          const int lo = max(kb_begin, seg_first) - seg_first;
+          const int hi = min(kb_end, seg_first + sg.k_blocks) - seg_first;
+          seg_first += sg.k_blocks;
+          if (lo >= hi) continue;
+          const CUtensorMap* map_a = &sg.a;
+          const CUtensorMap* map_b = &sg.b;
+          const bool a_mn = sg.a_mn != 0, b_mn = sg.b_mn != 0;
+          for (int k0 = lo * BK; k0 < hi * BK; k0 += BK) {
+            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.error_flag, 1))) {
+              alive = false;
+              break;
+            }
+            if (lane == 0) {
+              const uint32_t a_dst = smem_base + stage * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
+              // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
+              const uint32_t bar = lead_full0 + 8u * stage;
+              if (leader) mbar_expect_tx(full_bar(stage), CTAS * STAGE_BYTES);
+              auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+                if constexpr (CTAS == 1) tma_load_2d(dst, map, bar, x, y);
+                else tma_load_2d_pair(dst, map, bar, x, y);
+              };
+              if (!a_mn) {
+                load(a_dst, map_a, k0, a_row0);
+              } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(a_dst + j * MN_BOX_BYTES, &sg.a, full_bar(stage), tc.m * BM + j * 64, k0);
-          }
-          if (!sg.b_mn) {
-            tma_load_2d(b_dst, &sg.b, full_bar(stage), k0, tc.n * BN);
-          } else {
+                for (int j = 0; j < BM / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
+              }
+              if (!b_mn) {
+                load(b_dst, map_b, k0, b_row0);
+              } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * MN_BOX_BYTES, &sg.b, full_bar(stage), tc.n * BN + j * 64, k0);
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+                for (int j = 0; j < S::kBRows / 64; ++j) load(b_dst + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k0);
+              }
+            }
+            __syncwarp();
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // ------------------------------ MMA issuer (leader CTA only) ---------------
+    // One thread feeds the tensor core, so the loop is kept to a handful of instructions per MMA:
+    // everything that depends only on the segment (instruction descriptor, descriptor high words,
+    // per-k-step increments) is hoisted, and a k-block costs one barrier test, four MMAs, one commit.
+    // The whole warp walks the loop so that control flow stays uniform; lane 0 issues.
+    if (leader) {
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++local_tile) {
+      const uint32_t desc_hi = desc_high(1024);
+      for (int tile = first_tile; tile < total_tiles && alive; tile += tile_step, ++local_tile) {
         const TileCoord tc = tile_coord(tile, p);
         int kb_begin, kb_end;
         split_range(p, tc.split, kb_begin, kb_end);
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.error_flag, 2)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.error_flag, 2)))
+          break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        int seg = 0, seg_first = 0;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          while (kb >= seg_first + p.seg[seg].k_blocks) {
-            seg_first += p.seg[seg].k_blocks;
-            ++seg;
-          }
+        uint32_t accumulate = 0;
+        int seg_first = 0;
+        for (int seg = 0; seg < p.nseg && alive; ++seg) {
           const TcSegment& sg = p.seg[seg];
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.error_flag, 3)) {
-            alive = false;
-            break;
-          }
-          tcgen05_fence_after();
-          const uint32_t a_src = smem_base + stage * STAGE_BYTES, b_src = a_src + A_TILE_BYTES;
-          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn);
+          const int lo = max(kb_begin, seg_first) - seg_first;
+          const int hi = min(kb_end, seg_first + sg.k_blocks) - seg_first;
+          seg_first += sg.k_blocks;
+          if (lo >= hi) continue;
+          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn, TILE_M);
           // K-major: 8-row groups 1024 B apart, 32 B per 16-element k step inside the swizzle atom.
           // MN-major: 64-wide column groups one box (8 KB) apart, 8-k groups 1024 B apart,
           //           16 k rows (2 KB) per k step.
-          const uint64_t a_desc = sg.a_mn ? smem_desc(a_src, MN_BOX_BYTES, 1024) : smem_desc(a_src, 16, 1024);
-          const uint64_t b_desc = sg.b_mn ? smem_desc(b_src, MN_BOX_BYTES, 1024) : smem_desc(b_src, 16, 1024);
-          const uint64_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
-          const uint64_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
+          const uint32_t a_lo0 = desc_low(smem_base, sg.a_mn ? MN_BOX_BYTES : 16u);
+          const uint32_t b_lo0 = desc_low(smem_base + A_TILE_BYTES, sg.b_mn ? MN_BOX_BYTES : 16u);
+          const uint32_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
+          const uint32_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
+          for (int kb = lo; kb < hi; ++kb) {
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.error_flag, 3))) {
+              alive = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
+            if (lane == 0) {
 #pragma unroll
-          for (int j = 0; j < BK / UMMA_K; ++j)
-            umma_bf16(tmem_d, a_desc + a_step * j, b_desc + b_step * j, idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
-          umma_commit(empty_bar(stage));
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+              for (int j = 0; j < BK / UMMA_K; ++j) {
+                if constexpr (CTAS == 1)
+                  umma_bf16(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                            (accumulate | j) ? 1u : 0u);
+                else
+                  umma_bf16_pair(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                                 (accumulate | j) ? 1u : 0u);
+              }
+              if constexpr (CTAS == 1) umma_commit(empty_bar(stage));
+              else umma_commit_pair(empty_bar(stage));
+            }
+            __syncwarp();
+            accumulate = 1;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
-        if (alive) umma_commit(tmem_full_bar(acc));
+        if (alive && lane == 0) {
+          if constexpr (CTAS == 1) umma_commit(tmem_full_bar(acc));
+          else umma_commit_pair(tmem_full_bar(acc));
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
@@ -347,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
     // ------------------------------ epilogue ----------------------------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
     int local_tile = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++local_tile) {
       const TileCoord tc = tile_coord(tile, p);
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
@@ -356,7 +563,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tcgen05_fence_after();
-      const int64_t row = static_cast<int64_t>(tc.m) * BM + quarter * 32 + lane;
+      const int64_t row = static_cast<int64_t>(tc.m) * TILE_M + rank * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       char* out_plane = static_cast<char*>(p.out) +
@@ -372,92 +579,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-        const bool full = col0 + 32 <= p.N;
-        if (p.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-        }
-        if (p.out_f32) {
-          float* dst = reinterpret_cast<float*>(out_plane) + row * p.ldo + col0;
-          if (full && p.vec_store) {
-            float4* d4 = reinterpret_cast<float4*>(dst);
-            if (p.beta) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 o = d4[q];
-                v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
-              }
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = p.beta ? dst[j] + v[j] : v[j];
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_plane) + row * p.ldo + col0;
-          const __nv_bfloat16* res = p.residual ? p.residual + row * p.ld_res + col0 : nullptr;
-          if (full && p.vec_store) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
-            if (p.beta) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 o = d4[q];
-                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-                  v[8 * q + 2 * j] += f.x;
-                  v[8 * q + 2 * j + 1] += f.y;
-                }
-              }
-            }
-            if (res) {
-              const uint4* r4 = reinterpret_cast<const uint4*>(res);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 o = __ldg(r4 + q);
-                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-                  v[8 * q + 2 * j] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j])), f.x);
-                  v[8 * q + 2 * j + 1] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j + 1])), f.y);
-                }
-              }
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              d4[q] = make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
-                                 pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-              float x = v[j];
-              if (p.beta) x += __bfloat162float(dst[j]);
-              if (res) x = __fadd_rn(__bfloat162float(__float2bfloat16_rn(x)), __bfloat162float(res[j]));
-              dst[j] = __float2bfloat16_rn(x);
-            }
-          }
-        }
+        store_chunk(p, v, out_plane, row, col0);
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (lane == 0) {
+        if constexpr (CTAS == 1) mbar_arrive(tmem_empty_bar(acc));
+        else mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
+      }
     }
   }
 
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // neither CTA leaves while the other may still touch it
   if (warp == 1) {
     __syncwarp();
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (CTAS == 1)
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
-// ---- host side ------------------------------------------------------------------
-constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<1, 4>(p);
+}
 
+template <int STAGES_>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<2, STAGES_>(p);
+}
+
+// ---- host side ------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
     void* ptr = nullptr;
@@ -528,19 +684,55 @@ bool gemm_tcgen05_supported(const GemmArgs& g) {
   return tiles < (1LL << 30);
 }
 
+// CTA pairs pay off once a tile's 256 rows are mostly real rows; small-M products (and the
+// token-contracted dA with its 256 rows cut into slices) stay on the single-CTA kernel.
+// The environment variable CT_B200_GEMM_CTAS (1 or 2) pins the choice for experiments and tests.
+int ctas_for(const GemmArgs& g) {
+  const char* text = getenv("CT_B200_GEMM_CTAS");
+  const int pinned = text ? atoi(text) : 0;
+  if (pinned == 1 || pinned == 2) return pinned;
+  return g.M > 2 * BM ? 2 : 1;
+}
+
+template <typename Kernel>
+int configure(Kernel kernel, size_t smem, bool* configured) {
+  if (!*configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
+                  cudaGetErrorString(cudaGetLastError()));
+    *configured = true;
+  }
+  return CT_OK;
+}
+
+template <int STAGES_>
+int launch_pair(const TcParams& p, unsigned grid, int device, cudaStream_t stream) {
+  static bool configured[64] = {};
+  const size_t smem = Shape<2, STAGES_>::kSmemBytes;
+  const int rc = configure(gemm_tcgen05_pair_kernel<STAGES_>, smem, &configured[device]);
+  if (rc != CT_OK) return rc;
+  gemm_tcgen05_pair_kernel<STAGES_><<<grid, kThreads, smem, stream>>>(p);
+  return CT_OK;
+}
+
+int launch_single(const TcParams& p, unsigned grid, int device, cudaStream_t stream) {
+  static bool configured[64] = {};
+  const size_t smem = Shape<1, 4>::kSmemBytes;
+  const int rc = configure(gemm_tcgen05_kernel, smem, &configured[device]);
+  if (rc != CT_OK) return rc;
+  gemm_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(p);
+  return CT_OK;
+}
+
 int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   if (!gemm_tcgen05_supported(g)) return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05: operands break a TMA rule");
-  static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
     return fail(CT_ERR_CUDA, "gemm_tcgen05: no current device");
-  if (!configured[device]) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kSmemBytes)) != cudaSuccess)
-      return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", kSmemBytes,
-                  cudaGetErrorString(cudaGetLastError()));
-    configured[device] = true;
-  }
+  const int ctas = ctas_for(g);
+  int rc = CT_OK;
+  const int tile_m = BM * ctas, b_rows = BN / ctas;
   TcParams p;
   p.nseg = g.nseg;
   p.k_blocks_total = 0;
@@ -551,15 +743,14 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
     p.k_blocks_total += t.k_blocks;
     t.a_mn = sg.a_cs == 1 ? 0 : 1;
     t.b_mn = sg.b_rs == 1 ? 0 : 1;
-    int rc;
     // K-major: contiguous index is k, rows are m (or n). MN-major: contiguous index is m (or n), rows are k.
     rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM);
     if (rc != CT_OK) return rc;
-    rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK) : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, BN);
+    rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK) : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, b_rows);
     if (rc != CT_OK) return rc;
   }
   p.splits = g.split_k > 1 ? g.split_k : 1;
-  p.m_tiles = static_cast<int>((g.M + BM - 1) / BM);
+  p.m_tiles = static_cast<int>((g.M + tile_m - 1) / tile_m);
   p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
   p.M = g.M;
   p.N = g.N;
@@ -579,10 +770,20 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.splits;
   int sms = sm_count();
   if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot read the SM count");
-  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  const int64_t slots = sms / ctas;  // resident tiles: one CTA (or one CTA pair) per SM (pair)
+  const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * ctas);
   const bool timed = timing_enabled();
   if (timed) timing_begin(stream);
-  gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  if (ctas == 2) {
+    const char* text = getenv("CT_B200_GEMM_STAGES");
+    const int stages = text ? atoi(text) : 6;
+    rc = stages == 4 ? launch_pair<4>(p, grid, device, stream)
+       : stages == 7 ? launch_pair<7>(p, grid, device, stream)
+                     : launch_pair<6>(p, grid, device, stream);
+  } else {
+    rc = launch_single(p, grid, device, stream);
+  }
+  if (rc != CT_OK) return rc;
   if (timed) {
     double k_total = 0;
     for (int s = 0; s < g.nseg; ++s) k_total += static_cast<double>(g.seg[s].k);

@@ -9,12 +9,16 @@ from causal_tuner_b200.kernels import linear
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
 
-PATHS = {"simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}
+# name -> (GEMM path, CTAs per tile pinned through CT_B200_GEMM_CTAS)
+PATHS = {"simt": (_lib.PATH_SIMT, None), "tcgen05": (_lib.PATH_TCGEN05, "1"), "tcgen05_pair": (_lib.PATH_TCGEN05, "2")}
 
 
 @pytest.fixture(params=list(PATHS))
 def path(request, monkeypatch):
-    monkeypatch.setattr(_lib, "gemm_path", PATHS[request.param])
+    choice, ctas = PATHS[request.param]
+    monkeypatch.setattr(_lib, "gemm_path", choice)
+    if ctas is not None:
+        monkeypatch.setenv("CT_B200_GEMM_CTAS", ctas)
     return request.param
 
 
@@ -39,7 +43,7 @@ SHAPES = [(128, 256, 64), (304, 520, 200), (2048, 4096, 128), (96, 72, 2048), (1
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_matmul_orientations(path, shape, a_major, b_major, out_dtype):
     m, n, k = shape
-    if path == "tcgen05" and min(m, n, k) < 8:
+    if path.startswith("tcgen05") and min(m, n, k) < 8:
         pytest.skip("degenerate extents go to the SIMT kernel")
     left = operand(m, k, a_major)             # A(m, k): "K" = k contiguous
     right = operand(n, k, b_major).T          # B(k, n): "K" = k contiguous
