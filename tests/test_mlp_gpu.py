@@ -272,3 +272,52 @@ def test_full_width_bf16_mlp_block_with_recompute():
     for name, left, right in zip(["y", "dx"] + ["param"] * 6, (recomputed, *g_recompute), (expected, *reference)):
         assert torch.isfinite(left).all()
         assert relative(left, right) < 2e-2, name
+
+
+def test_config3_recompute_versus_stored_activations(capsys):
+    """One SwiGLU MLP block, hidden 4096, intermediate 14336, NF4 base weights, rank-256 adapters,
+    8 packed rows of 4096 tokens (32768 tokens). Recompute-in-backward must retain only the block
+    input between forward and backward; the cached mode retains exactly `cache_bytes` more; the
+    three-node autograd path (`untiled`) retains the most. Times are printed for the record."""
+    torch.manual_seed(9)
+    module = MLP(WideConfig, Runtime(rank=256), "cuda")
+    for projection in (module.gate_proj, module.up_proj, module.down_proj):
+        projection.install_nf4(projection.weight.detach().clone(), "cuda", nested=False)
+        torch.nn.init.normal_(projection.lora_B, std=.005)
+    rows = 8 * 4096
+    x = torch.randn(8, 4096, 4096, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    signal = torch.randn_like(x)
+    params = (x, *trainable(module))
+    report = {}
+    outputs = {}
+    for name, forward in (("recompute", lambda: module(x, cache=False)), ("cached", lambda: module(x, cache=True)),
+                          ("stored", lambda: module.untiled(x))):
+        for _ in range(2):   # warm-up, then the measured pass (nothing of the first pass stays alive)
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            base = torch.cuda.memory_allocated()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            y = forward()
+            torch.cuda.synchronize()
+            retained = torch.cuda.memory_allocated() - base - y.numel() * 2
+            grads = torch.autograd.grad(y, params, signal)
+            stop.record()
+            torch.cuda.synchronize()
+            peak = torch.cuda.max_memory_allocated() - base
+            report[name] = dict(retained_mb=retained / 2**20, peak_mb=peak / 2**20, ms=start.elapsed_time(stop))
+            outputs[name] = (y.detach(), grads)
+            del y, grads
+            if _ == 0:
+                del outputs[name]
+    with capsys.disabled():
+        print("\nconfig3 (32768 tokens):", {k: {a: round(b, 1) for a, b in v.items()} for k, v in report.items()})
+    assert report["recompute"]["retained_mb"] < 1.0                       # nothing but x (already counted in base)
+    expected_cache = module.cache_bytes(rows) / 2**20
+    assert abs(report["cached"]["retained_mb"] - expected_cache) < 1.0
+    assert report["stored"]["retained_mb"] > report["cached"]["retained_mb"]
+    assert torch.equal(outputs["recompute"][0], outputs["cached"][0])
+    for a, b in zip(outputs["recompute"][1], outputs["cached"][1]):
+        assert torch.equal(a, b)
+    for a, b in zip(outputs["recompute"][1], outputs["stored"][1]):
+        assert relative(a, b) < 3e-2
