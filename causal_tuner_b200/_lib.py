@@ -38,6 +38,9 @@ SIGNATURES = {
     "ct_swiglu": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P]),
     "ct_rope": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "ct_add_inplace": (_I, [_P, _P, _L, _I, _P]),
+    "ct_rmsnorm_forward": (_I, [_P, _P, _P, _P, _L, _L, ctypes.c_float, _I, _I, _P]),
+    "ct_rmsnorm_backward": (_I, [_P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
+    "ct_weighted_ce": (_I, [_P, _P, _P, _P, _L, _L, _I, _I, _P]),
 }
 
 

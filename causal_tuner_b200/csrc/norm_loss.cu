@@ -1,0 +1,166 @@
+// Row-wise kernels next to the projection path: RMSNorm forward / input gradient and the
+// weighted cross-entropy that turns a tile of logits into per-row losses and, in place, into
+// the gradient of those losses. All HBM-bound: one CTA per row, 16-byte vectors where the row
+// allows it, fp32 arithmetic, the rounding points of the reference kernels
+// (kernels/core_cuda.py:30-82, kernels/loss_cuda.py:12-55).
+#include "common.cuh"
+
+namespace ct {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) total += scratch[w];
+  return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) total = fmaxf(total, scratch[w]);
+  return total;
+}
+
+// y = round(x * rstd) * round(w); rstd = rsqrt(mean(x^2) + eps) is kept for the backward pass.
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads)
+rms_forward_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width, float eps) {
+  __shared__ float scratch[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * width;
+  float sum = 0.f;
+  for (int64_t c = threadIdx.x; c < width; c += kThreads) {
+    const float v = to_float<T>(xr[c]);
+    sum += v * v;
+  }
+  const float inverse = rsqrtf(block_sum(sum, scratch) / static_cast<float>(width) + eps);
+  if (threadIdx.x == 0) rstd[row] = inverse;
+  T* yr = y + row * width;
+  for (int64_t c = threadIdx.x; c < width; c += kThreads) {
+    const float normalized = round_to<T>(to_float<T>(xr[c]) * inverse);
+    const float weight = round_to<T>(to_float<W>(w[c]));
+    yr[c] = from_float<T>(normalized * weight);
+  }
+}
+
+// gx = rstd * (g - x * rstd^2 * mean(g * x)) with g = round(go * round(w)); gx may alias go.
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads)
+rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, T* gx, int64_t width) {
+  __shared__ float scratch[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * width;
+  const T* gr = go + row * width;
+  float sum = 0.f;
+  for (int64_t c = threadIdx.x; c < width; c += kThreads) {
+    const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
+    sum += gradient * to_float<T>(xr[c]);
+  }
+  const float projection = block_sum(sum, scratch) / static_cast<float>(width);
+  const float inverse = rstd[row];
+  T* out = gx + row * width;
+  for (int64_t c = threadIdx.x; c < width; c += kThreads) {
+    const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
+    out[c] = from_float<T>(inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection)));
+  }
+}
+
+// loss[row] = weight * (logsumexp(logits[row]) - logits[row, target]); with `gradient`, logits[row]
+// becomes (softmax(logits[row]) - onehot(target)) * weight.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+weighted_ce_kernel(T* logits, const int64_t* targets, const float* weights, float* loss, int64_t vocab, int gradient) {
+  __shared__ float scratch[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  T* lr = logits + row * vocab;
+  float maximum = -INFINITY;
+  for (int64_t c = threadIdx.x; c < vocab; c += kThreads) maximum = fmaxf(maximum, to_float<T>(lr[c]));
+  maximum = block_max(maximum, scratch);
+  float sum = 0.f;
+  for (int64_t c = threadIdx.x; c < vocab; c += kThreads) sum += expf(to_float<T>(lr[c]) - maximum);
+  const float lse = maximum + logf(block_sum(sum, scratch));
+  const int64_t target = targets[row];
+  const float weight = weights[row];
+  const float selected = to_float<T>(lr[target]);
+  __syncthreads();  // every thread has read the target logit before anyone overwrites it
+  if (threadIdx.x == 0) loss[row] = weight * (lse - selected);
+  if (gradient) {
+    for (int64_t c = threadIdx.x; c < vocab; c += kThreads) {
+      const float derivative = (expf(to_float<T>(lr[c]) - lse) - (c == target ? 1.f : 0.f)) * weight;
+      lr[c] = from_float<T>(derivative);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace ct
+
+using namespace ct;
+
+extern "C" int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t width,
+                                  float eps, int dtype, int weight_dtype, void* stream) {
+  if (rows < 0 || width <= 0) return fail(CT_ERR_ARG, "ct_rmsnorm_forward: rows=%lld width=%lld", (long long)rows, (long long)width);
+  if (rows == 0) return CT_OK;
+  if (!x || !w || !y || !rstd) return fail(CT_ERR_ARG, "ct_rmsnorm_forward: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(rows);
+#define CT_RMS_FWD(T, W) rms_forward_kernel<T, W><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), static_cast<T*>(y), rstd, width, eps)
+  if (dtype == CT_BF16 && weight_dtype == CT_BF16) CT_RMS_FWD(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == CT_BF16 && weight_dtype == CT_F32) CT_RMS_FWD(__nv_bfloat16, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_F32) CT_RMS_FWD(float, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_BF16) CT_RMS_FWD(float, __nv_bfloat16);
+  else return fail(CT_ERR_ARG, "ct_rmsnorm_forward: dtype %d / %d", dtype, weight_dtype);
+#undef CT_RMS_FWD
+  count_launch(false);
+  return check_launch("ct_rmsnorm_forward");
+}
+
+extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go, void* gx,
+                                   int64_t rows, int64_t width, int dtype, int weight_dtype, void* stream) {
+  if (rows < 0 || width <= 0) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: rows=%lld width=%lld", (long long)rows, (long long)width);
+  if (rows == 0) return CT_OK;
+  if (!x || !w || !rstd || !go || !gx) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(rows);
+#define CT_RMS_BWD(T, W) rms_backward_kernel<T, W><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<const T*>(go), static_cast<T*>(gx), width)
+  if (dtype == CT_BF16 && weight_dtype == CT_BF16) CT_RMS_BWD(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == CT_BF16 && weight_dtype == CT_F32) CT_RMS_BWD(__nv_bfloat16, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_F32) CT_RMS_BWD(float, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_BF16) CT_RMS_BWD(float, __nv_bfloat16);
+  else return fail(CT_ERR_ARG, "ct_rmsnorm_backward: dtype %d / %d", dtype, weight_dtype);
+#undef CT_RMS_BWD
+  count_launch(false);
+  return check_launch("ct_rmsnorm_backward");
+}
+
+extern "C" int ct_weighted_ce(void* logits, const int64_t* targets, const float* weights, float* loss, int64_t rows,
+                              int64_t vocab, int gradient, int dtype, void* stream) {
+  if (rows < 0 || vocab <= 0) return fail(CT_ERR_ARG, "ct_weighted_ce: rows=%lld vocab=%lld", (long long)rows, (long long)vocab);
+  if (rows == 0) return CT_OK;
+  if (!logits || !targets || !weights || !loss) return fail(CT_ERR_ARG, "ct_weighted_ce: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (dtype == CT_BF16)
+    weighted_ce_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(logits), targets, weights, loss, vocab, gradient);
+  else if (dtype == CT_F32)
+    weighted_ce_kernel<float><<<grid, kThreads, 0, s>>>(static_cast<float*>(logits), targets, weights, loss, vocab, gradient);
+  else
+    return fail(CT_ERR_ARG, "ct_weighted_ce: dtype %d", dtype);
+  count_launch(false);
+  return check_launch("ct_weighted_ce");
+}

@@ -55,3 +55,57 @@ class PartialRoPE(torch.autograd.Function):
         cosine, sine = ctx.saved_tensors
         grad = grad.contiguous()
         return _rope(grad, cosine, sine, torch.empty_like(grad), ctx.shape[-2], ctx.shape[-1], True), None, None
+
+
+# ---- RMSNorm and the rotary position table ------------------------------------------------
+
+def position_values(positions, inverse, dtype):
+    """cos/sin of positions[..., None] * inverse in fp32, then cast (kernels/core_cuda.py:21-27).
+    Evaluated once per batch on [tokens, rotary_dim / 2] values with torch's full-range cos/sin."""
+    angle = positions.to(torch.float32)[..., None] * inverse.to(torch.float32)
+    return angle.cos().to(dtype), angle.sin().to(dtype)
+
+
+class RMS(torch.autograd.Function):
+    """y = round(x * rstd) * round(w) for a FROZEN weight (kernels/core_cuda.py:94-131).
+
+    `reuse_grad=True` writes the input gradient over the upstream gradient, which the caller
+    guarantees to be a private tensor (the projection operators return fresh input gradients).
+    The output-reconstruction mode of the reference is a memory option and is not implemented:
+    `reconstruct` is accepted and ignored, the input is saved.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, eps, reuse_grad=False, reconstruct=False):
+        _lib.require_cuda(x, weight)
+        if weight.requires_grad:
+            raise NotImplementedError("causal_tuner_b200 covers frozen RMSNorm weights (adapter training) only")
+        ctx.reuse_grad = reuse_grad
+        x = x.contiguous()
+        output = torch.empty_like(x)
+        width = x.shape[-1]
+        rows = x.numel() // width
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        weight = weight.contiguous()
+        with _lib.on_device(x):
+            _lib.check(_lib.load().ct_rmsnorm_forward(
+                x.data_ptr(), weight.data_ptr(), output.data_ptr(), rstd.data_ptr(), rows, width, float(eps),
+                _lib.code_of(x.dtype), _lib.code_of(weight.dtype), _lib.stream_of(x)))
+        ctx.save_for_backward(x, weight, rstd)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad):
+        x, weight, rstd = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None, None, None, None
+        grad = grad.contiguous()
+        if grad.dtype != x.dtype:
+            grad = grad.to(x.dtype)
+        result = grad if ctx.reuse_grad else torch.empty_like(x)
+        width = x.shape[-1]
+        with _lib.on_device(x):
+            _lib.check(_lib.load().ct_rmsnorm_backward(
+                x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), result.data_ptr(),
+                x.numel() // width, width, _lib.code_of(x.dtype), _lib.code_of(weight.dtype), _lib.stream_of(x)))
+        return result, None, None, None, None

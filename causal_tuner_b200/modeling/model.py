@@ -67,3 +67,127 @@ class MLP(nn.Module):
         if all(can_fuse(module, x) for module in (self.gate_proj, self.up_proj, self.down_proj)):
             return tiled_lora_mlp(self, x, residual, tile=tile, cache=cache)
         raise NotImplementedError("causal_tuner_b200.MLP needs adapters on gate_proj, up_proj and down_proj")
+
+
+# ---- the decoder around the two operators ------------------------------------------------------
+# RMSNorm, Attention, Layer and CausalLM follow modeling/model.py:39-279 of the reference with the
+# execution policy made explicit: `runtime.checkpoint` recomputes each layer in backward, the MLP
+# always recomputes gate/up unless `layer.mlp.cache_intermediates` is set, nothing is offloaded.
+
+class RMSNorm(nn.Module):
+    def __init__(self, size, eps, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(size, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x, *, reuse_grad=False):
+        from ..kernels.core_cuda import RMS
+        if not x.is_cuda:
+            raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
+        return RMS.apply(x, self.weight, self.eps, reuse_grad, False)
+
+
+class Attention(nn.Module):
+    def __init__(self, config, runtime, device):
+        super().__init__()
+        self.config, self.runtime = config, runtime
+        kwargs = dict(rank=runtime.rank, base_dtype=runtime.base_dtype, train_dtype=runtime.train_dtype,
+                      compute_dtype=runtime.compute_dtype, device=device)
+        h, d = config.hidden_size, config.head_dim
+        self.q_proj = Projection(h, h, bias=True, **kwargs)
+        self.k_proj = Projection(h, d, bias=True, **kwargs)
+        self.v_proj = Projection(h, d, bias=True, **kwargs)
+        self.o_proj = Projection(h, h, **kwargs)
+
+    def forward(self, x, cosine, sine, segments, spans, layout=None, *, residual=None):
+        from ..kernels.attention import dense_attention, flash_dense
+        from ..kernels.linear import project_group
+        b, s, _ = x.shape
+        c, r = self.config, self.runtime
+        q, k, v = project_group((self.q_proj, self.k_proj, self.v_proj), x, r.projection_tile,
+                                rotary=(cosine, sine, c.head_dim))
+        q, k = q.reshape(b, s, c.num_attention_heads, c.head_dim), k.reshape(b, s, 1, c.head_dim)
+        v = v.reshape(b, s, 1, c.head_dim)
+        if r.attention == "vanilla":
+            y = dense_attention(q, k, v, segments)
+        else:
+            y = flash_dense(q, k, v, spans, layout=layout)
+        return project_group((self.o_proj,), y.reshape(b, s, -1), r.projection_tile, residual=residual)[0]
+
+
+class Layer(nn.Module):
+    def __init__(self, config, runtime, device):
+        super().__init__()
+        self.self_attn = Attention(config, runtime, device)
+        self.mlp = MLP(config, runtime, device)
+        self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, runtime.base_dtype, device)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, runtime.base_dtype, device)
+
+    def forward(self, x, *args, mlp_tile=None, mlp_cache=None):
+        # Both norms feed operators that return private input gradients, so the norm backward may
+        # write over its upstream gradient (reuse_grad).
+        x = self.self_attn(self.input_layernorm(x, reuse_grad=True), *args, residual=x)
+        return self.mlp(self.post_attention_layernorm(x, reuse_grad=True), residual=x, tile=mlp_tile, cache=mlp_cache)
+
+
+class Decoder(nn.Module):
+    def __init__(self, config, runtime, device):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, padding_idx=config.pad_token_id,
+                                         dtype=runtime.base_dtype, device=device)
+        self.layers = nn.ModuleList([Layer(config, runtime, device) for _ in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps, runtime.base_dtype, device)
+
+
+class CausalLM(nn.Module):
+    """Adapter-training decoder: every base weight, bias, norm, embedding and the head are frozen;
+    lora_A / lora_B of the seven projections per layer train in `runtime.train_dtype`."""
+
+    def __init__(self, config, runtime, device=None):
+        super().__init__()
+        if not runtime.rank:
+            raise NotImplementedError("causal_tuner_b200 covers adapter training (rank > 0) only")
+        self.config, self.runtime = config, runtime
+        self.model = Decoder(config, runtime, device)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=runtime.base_dtype,
+                                 device=device)
+        for name, param in self.named_parameters():
+            trainable = "lora_" in name
+            param.requires_grad_(trainable)
+            if trainable:
+                param.data = param.data.to(runtime.train_dtype)
+
+    def install_nf4(self, *, blocksize=64, nested=False):
+        """Pack every projection's base weight to NF4 in place (weights must already be on a CUDA device)."""
+        for layer in self.model.layers:
+            for projection in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj,
+                               layer.self_attn.o_proj, layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj):
+                weight = projection.weight.detach()
+                projection.install_nf4(weight, weight.device, blocksize=blocksize, nested=nested)
+        return self
+
+    def adapter_parameters(self):
+        return [p for p in self.parameters() if p.requires_grad]
+
+    def forward(self, batch):
+        from torch.utils.checkpoint import checkpoint
+        from ..kernels.attention import prepare_dense_layout
+        from ..segments import canonical_segments, position_ids, runs
+        from .rotary import rotary_values
+        r = self.runtime
+        segments = canonical_segments(batch["attention_mask"], batch.get("segment_ids"))
+        positions = batch.get("position_ids")
+        if positions is None:
+            positions = position_ids(segments)
+        if (positions < 0).any() or (positions >= self.config.max_position_embeddings).any():
+            raise ValueError("position_ids exceed the model's logical position range")
+        spans = batch.get("_spans") or runs(segments)
+        cosine, sine = rotary_values(positions, self.config, r.compute_dtype)
+        x = self.model.embed_tokens(batch["input_ids"]).to(r.compute_dtype)
+        layout = prepare_dense_layout(x.shape[:2], spans, x.device) if r.attention == "flash_attention_2" else None
+        recompute = r.checkpoint and self.training and torch.is_grad_enabled()
+        for layer in self.model.layers:
+            run = lambda z, layer=layer: layer(z, cosine, sine, segments, spans, layout, mlp_tile=r.mlp_tile,
+                                                mlp_cache=layer.mlp.cache_intermediates)
+            x = checkpoint(run, x, use_reentrant=False, preserve_rng_state=False) if recompute else run(x)
+        return self.model.norm(x)

@@ -1,0 +1,99 @@
+"""One optimizer update over weighted micro-batches, with the data-parallel gradient exchange.
+
+Follows the reference's training/engine.py:10-111 (`make_optimizer`, `Trainer.update`): per
+micro-batch forward, tiled lm_head loss, backward; then gradients are divided by the total
+supervision weight, clipped, and AdamW steps. The reference is single-device; with
+torch.distributed initialised every rank runs its own micro-batches and, between the last
+backward and the division (training/engine.py:90-97), the fp32 adapter gradients, the total
+weight and the total loss are summed across ranks - which makes the update equal to
+single-device accumulation over the concatenated batch (up to fp32 summation order).
+"""
+
+import torch
+import torch.distributed as dist
+
+from .dp import GradientExchange
+from .kernels.loss import active_rows, projection_loss
+from .segments import prediction_targets
+
+
+def make_optimizer(model, *, learning_rate=2e-5, weight_decay=0.0, betas=(0.9, 0.999), eps=1e-8):
+    """AdamW over the trainable parameters; weight decay on matrices only (training/engine.py:10-16)."""
+    parameters = [p for p in model.parameters() if p.requires_grad]
+    groups = [{"params": group, "weight_decay": weight_decay if decay else 0.0}
+              for decay in (True, False) if (group := [p for p in parameters if (p.ndim > 1) == decay])]
+    return torch.optim.AdamW(groups, lr=learning_rate, betas=betas, eps=eps, weight_decay=weight_decay,
+                             foreach=False, fused=all(p.is_cuda for p in parameters))
+
+
+class Trainer:
+    def __init__(self, model, optimizer, *, device, max_grad_norm=1.0, loss_token_budget=4096, group=None,
+                 bucket_bytes=64 << 20):
+        self.model, self.optimizer, self.device = model, optimizer, device
+        self.max_grad_norm, self.loss_token_budget = max_grad_norm, loss_token_budget
+        self.group, self.bucket_bytes = group, bucket_bytes
+
+    def update(self, batches, *, learning_rate=None):
+        self.model.train()
+        self.optimizer.zero_grad(set_to_none=True)
+        total_loss = torch.zeros((), device=self.device, dtype=torch.float32)
+        total_weight = torch.zeros_like(total_loss)
+        microbatches, valid_tokens = 0, 0
+        for batch in batches:
+            microbatches += 1
+            valid_tokens += int(batch["attention_mask"].sum())
+            targets, weights = prediction_targets(batch)
+            rows = active_rows(weights, self.device)
+            targets, weights = targets.to(self.device), weights.to(self.device)
+            batch = {k: v.to(self.device) if torch.is_tensor(v) else v for k, v in batch.items()}
+            hidden = self.model(batch)
+            loss = projection_loss(hidden, self.model.lm_head.weight, targets, weights,
+                                   token_budget=self.loss_token_budget,
+                                   compute_dtype=self.model.runtime.compute_dtype, reuse_hidden=True, rows=rows)
+            del hidden
+            loss.backward()
+            total_loss.add_(loss.detach())
+            total_weight.add_(weights.sum())
+            del loss, batch
+        if microbatches == 0:
+            raise ValueError("An optimizer update requires at least one microbatch")
+        parameters = [p for group in self.optimizer.param_groups for p in group["params"]]
+        for param in parameters:
+            if param.grad is None:
+                raise RuntimeError("A trainable parameter has no gradient; the graph is disconnected")
+        collectives = 0
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            exchange = GradientExchange(self.group, self.bucket_bytes)
+            scalars = torch.stack((total_loss, total_weight))
+            exchange.add(scalars)
+            for param in parameters:
+                if param.grad.dtype == torch.float32:
+                    exchange.add(param.grad)
+                else:                                  # 16-bit training dtype: exchange in fp32, round once
+                    wide = param.grad.float()
+                    exchange.add(wide)
+                    param._exchange = wide
+            exchange.finish()
+            for param in parameters:
+                wide = getattr(param, "_exchange", None)
+                if wide is not None:
+                    param.grad.copy_(wide)
+                    del param._exchange
+            total_loss, total_weight = scalars[0], scalars[1]
+            collectives = exchange.collectives
+        denominator = total_weight.clamp_min(1.0)
+        torch._foreach_div_([param.grad for param in parameters], denominator)
+        if self.max_grad_norm:
+            norm = torch.nn.utils.clip_grad_norm_(parameters, self.max_grad_norm, error_if_nonfinite=True,
+                                                  foreach=all(p.is_cuda for p in parameters))
+        else:
+            norm = torch.sqrt(sum(p.grad.float().norm().square() for p in parameters))
+            if not torch.isfinite(norm):
+                raise FloatingPointError("Non-finite gradient norm")
+        if learning_rate is not None:
+            for group in self.optimizer.param_groups:
+                group["lr"] = learning_rate
+        self.optimizer.step()
+        return {"loss": (total_loss / denominator).item(), "effective_weight": total_weight.item(),
+                "grad_norm": norm.item(), "microbatches": microbatches, "valid_tokens": valid_tokens,
+                "collectives": collectives}

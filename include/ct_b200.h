@@ -206,6 +206,30 @@ CT_API int ct_rope(const void* x, const void* cosine, const void* sine, void* y,
  * `output.add_(residual)` (kernels/mlp_cuda.py:79-80): y = round(y + r). */
 CT_API int ct_add_inplace(void* y, const void* r, int64_t n, int dtype, void* stream);
 
+/* ---- RMSNorm ---------------------------------------------------------------------
+ * Replaces kernels/core_cuda.py:30-40 (_rms_forward) and the input-gradient branch of
+ * kernels/core_cuda.py:43-82 (_rms_gradient_row / _rms_backward with a frozen weight).
+ *   rstd[row] = rsqrt(mean(x[row]^2) + eps)
+ *   y  = round(x * rstd) * round(w)
+ *   gx = rstd * (g - x * rstd^2 * mean(g * x)),  g = round(go * round(w))
+ * round() rounds to `dtype` (the activation dtype); `w` has `weight_dtype`. x, y, go, gx are
+ * [rows, width] contiguous; gx may alias go (the reference's reuse of a private upstream
+ * gradient, kernels/core_cuda.py:113-115). */
+CT_API int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* rstd, int64_t rows,
+                              int64_t width, float eps, int dtype, int weight_dtype, void* stream);
+CT_API int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go,
+                               void* gx, int64_t rows, int64_t width, int dtype, int weight_dtype,
+                               void* stream);
+
+/* ---- weighted cross-entropy over a tile of logits -------------------------------
+ * Replaces kernels/loss_cuda.py:12-72 (_statistics, _finish, weighted_ce).
+ *   loss[row] = weights[row] * (logsumexp(logits[row]) - logits[row, targets[row]])
+ * and, when `gradient` != 0, logits[row] is overwritten by
+ *   (softmax(logits[row]) - onehot(targets[row])) * weights[row].
+ * logits[rows, vocab] contiguous in `dtype`, targets int64, weights and loss fp32. */
+CT_API int ct_weighted_ce(void* logits, const int64_t* targets, const float* weights, float* loss,
+                          int64_t rows, int64_t vocab, int gradient, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
