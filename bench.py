@@ -377,6 +377,128 @@ def finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, 
         dist.destroy_process_group()
 
 
+STEP_METRIC = "train tokens/s (NF4 r256 LoRA, MQA decoder, one optimizer update)"
+
+
+def step_config(name, gpus):
+    import bench_step
+    spec = bench_step.WORKLOADS[name]
+    return {"workload": f"{name} ({spec['reference']})", **spec["config"], "rank": bench_step.RANK,
+            "rows_per_gpu": spec["rows"], "seq_len": spec["length"], "global_batch": spec["rows"] * gpus,
+            "nf4_blocksize": 64, "absmax": "fp32", "attention": "flash_attention_2 (library, as in the reference)",
+            "activation_checkpointing": False, "mlp": "recompute gate/up in backward", "parallelism": f"dp{gpus}",
+            "l2": "per-layer operands (>= 134 MB activations + 117 MB decoded weight) exceed the 126 MB L2"}
+
+
+def run_step_reference(args):
+    import bench_step
+    rank, _, _ = world()
+    if rank != 0:
+        return
+    estimate = bench_step.cpu_estimate(args.workload, passes=max(1, min(args.steps, 5)))
+    line = {"impl": "reference", "metric": STEP_METRIC, "value": estimate["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * bench_step.CPU_SAMPLE_TOKENS / estimate["value"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": step_config(args.workload, args.gpus), "cpu_baseline": estimate,
+            "e2e": {"value": estimate["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_step(args):
+    """One optimizer update per step through `Trainer.update`: host batch -> device, forward, tiled loss,
+    backward, (N > 1: NCCL all-reduce of the fp32 adapter gradients), clip, AdamW, loss back to the host."""
+    import torch.distributed as dist
+    import bench_step
+    from causal_tuner_b200 import _lib
+    from causal_tuner_b200.training import Trainer, make_optimizer
+    rank, local_rank, world_size = world()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path "
+                         "(use --impl reference for the CPU composition)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world_size > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+    _lib.load()
+    spec = bench_step.WORKLOADS[args.workload]
+    model = bench_step.build_model(args.workload, device)
+    optimizer = make_optimizer(model, learning_rate=2e-5)
+    trainer = Trainer(model, optimizer, device=device, loss_token_budget=4096)
+    host_batch = bench_step.synthetic_batch(spec["rows"], spec["length"], spec["config"]["vocab_size"], seed=1000 + rank)
+    host_batch = {k: v.pin_memory() for k, v in host_batch.items()}
+    device_batch = {k: v.to(device) for k, v in host_batch.items()}
+    tokens_per_rank = spec["rows"] * spec["length"]
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(batch, steps):
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        losses = [trainer.update([batch])["loss"] for _ in range(steps)]
+        stop.record()
+        barrier()
+        elapsed = torch.tensor([start.elapsed_time(stop)], device=device, dtype=torch.float64)
+        if distributed:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return elapsed.item() / steps, losses
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        trainer.update([device_batch])
+    _lib.check_device()
+    sampler.mark()
+    launches_before = _lib.launch_count()
+    _lib.timing_enable(True)
+    ms_per_step, losses = timed(device_batch, args.steps)
+    kernel_ms, kernel_flops, kernel_launches = _lib.timing_collect()
+    _lib.timing_enable(False)
+    launches = _lib.launch_count() - launches_before
+    clocks = sampler.stop()
+    e2e_ms, _ = timed(host_batch, max(2, min(args.steps, 5)))   # ids from pinned host memory, loss back to host
+    _lib.check_device()
+    peak_memory = torch.cuda.max_memory_allocated(device)
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+    tokens = tokens_per_rank * world_size
+    flops = bench_step.step_flops(spec["config"], tokens_per_rank)
+    achieved = kernel_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
+    h2d = sum(v.numel() * v.element_size() for v in host_batch.values())
+    line = {
+        "metric": STEP_METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world_size,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": step_config(args.workload, world_size),
+        "step_tflops_per_gpu": flops / (ms_per_step * 1e-3) / 1e12,
+        "step_frac_of_bf16_peak": flops / (ms_per_step * 1e-3) / 1e12 / peak,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel / gemm_tcgen05_pair_kernel",
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
+                     "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
+                     "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps, "traffic": None},
+        "clocks": clocks, "loss_first": losses[0], "loss_last": losses[-1],
+        "peak_memory_gb": peak_memory / 1e9,
+    }
+    if world_size == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = bench_step.cpu_estimate(args.workload)
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
 def main():
     global ROWS
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
@@ -388,12 +510,15 @@ def main():
                         help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
+    parser.add_argument("--workload", choices=("step7b", "step1b", "projection"), default="step7b",
+                        help="step7b: 7B-class decoder update (the headline metric); step1b: the 1.3B decoder; "
+                             "projection: one fused NF4+LoRA projection, forward+backward")
     args = parser.parse_args()
     ROWS = args.rows
-    if args.impl == "reference":
-        run_reference(args)
+    if args.workload == "projection":
+        run_reference(args) if args.impl == "reference" else run_ours(args)
     else:
-        run_ours(args)
+        run_step_reference(args) if args.impl == "reference" else run_step(args)
 
 
 if __name__ == "__main__":

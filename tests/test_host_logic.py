@@ -109,3 +109,52 @@ def test_quantiser_layout_round_trips_through_the_oracle_decode(shape, blocksize
     # within 17 % of the block's absmax (4-bit levels) plus the 8-bit error of nested statistics
     limit = 0.17 * weight.abs().max().item() * (1.1 if nested else 1.0)
     assert error.max() <= limit
+
+
+def test_default_parameter_counts_match_the_reference_numbers():
+    from causal_tuner_b200.modeling.config import ModelConfig
+    assert ModelConfig().parameter_counts(256) == (9574004736, 796917760)
+    seven_b = ModelConfig(hidden_size=4096, intermediate_size=14336, vocab_size=49152, num_hidden_layers=32)
+    assert seven_b.parameter_counts(256)[1] == 656408576      # fp32 all-reduce payload of the 7B step: 2.63 GB
+    with pytest.raises(ValueError):
+        ModelConfig(num_key_value_heads=2)
+
+
+def test_segments_positions_and_targets_never_cross_documents():
+    from causal_tuner_b200 import segments as seg
+    from oracle import model as oracle_model
+    labels = torch.tensor([[1, 1, 1, 2, 2, 2, 2, 3, 3], [5, 5, 0, 0, 7, 7, 7, 7, 7]])
+    mask = torch.tensor([[1] * 9, [1, 1, 0, 0, 1, 1, 1, 1, 1]])
+    canonical = seg.canonical_segments(mask, labels)
+    assert canonical.tolist() == [[1, 1, 1, 2, 2, 2, 2, 3, 3], [1, 1, 0, 0, 2, 2, 2, 2, 2]]
+    assert torch.equal(canonical, oracle_model.segments_of(mask, labels))
+    positions = seg.position_ids(canonical)
+    assert positions.tolist() == [[0, 1, 2, 0, 1, 2, 3, 0, 1], [0, 1, 0, 0, 0, 1, 2, 3, 4]]
+    assert torch.equal(positions, oracle_model.positions_of(canonical))
+    assert seg.runs(canonical) == ((0, 0, 3), (0, 3, 7), (0, 7, 9), (1, 0, 2), (1, 4, 9))
+    ids = torch.arange(18).reshape(2, 9)
+    targets, weights = seg.prediction_targets({"input_ids": ids, "attention_mask": mask, "segment_ids": labels})
+    assert weights.tolist() == [[1, 1, 0, 1, 1, 1, 0, 1, 0], [1, 0, 0, 0, 1, 1, 1, 1, 0]]
+    assert targets[0, :2].tolist() == [1, 2] and targets[weights == 0].eq(0).all()
+
+
+def test_active_rows_prefers_slices():
+    from causal_tuner_b200.kernels.loss import active_rows, row_count
+    assert active_rows(torch.tensor([0., 1, 2, 0])) == slice(1, 3)
+    assert active_rows(torch.ones(4)) == slice(0, 4) and active_rows(torch.zeros(4)) == slice(0, 0)
+    gaps = active_rows(torch.tensor([1., 0, 1, 1]))
+    assert gaps.tolist() == [0, 2, 3] and row_count(gaps) == 3 and row_count(slice(2, 7)) == 5
+
+
+def test_trainer_and_loss_surface():
+    from causal_tuner_b200.kernels import loss, loss_cuda
+    from causal_tuner_b200.training import Trainer, make_optimizer
+    assert list(inspect.signature(loss.projection_loss).parameters) == [
+        "hidden", "head", "targets", "weights", "token_budget", "compute_dtype", "implementation", "cut_chunk_size",
+        "reuse_hidden", "rows"]
+    assert list(inspect.signature(loss_cuda.weighted_ce).parameters) == ["logits", "targets", "weights", "gradient",
+                                                                         "loss", "partials"]
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        loss.projection_loss(torch.zeros(2, 4), torch.zeros(3, 4), torch.zeros(2, dtype=torch.long), torch.ones(2))
+    with pytest.raises(ValueError):
+        loss.projection_loss(torch.zeros(2, 4), torch.zeros(3, 4), torch.zeros(2), torch.ones(2), token_budget=0)
