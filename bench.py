@@ -380,13 +380,16 @@ def finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, 
 STEP_METRIC = "train tokens/s (NF4 r256 LoRA, MQA decoder, one optimizer update)"
 
 
-def step_config(name, gpus):
+def step_config(name, gpus, mlp_cache_gib=0, execution=None):
     import bench_step
     spec = bench_step.WORKLOADS[name]
+    cached = (execution or {}).get("mlp_cache_layers", 0)
     return {"workload": f"{name} ({spec['reference']})", **spec["config"], "rank": bench_step.RANK,
             "rows_per_gpu": spec["rows"], "seq_len": spec["length"], "global_batch": spec["rows"] * gpus,
             "nf4_blocksize": 64, "absmax": "fp32", "attention": "flash_attention_2 (library, as in the reference)",
-            "activation_checkpointing": False, "mlp": "recompute gate/up in backward", "parallelism": f"dp{gpus}",
+            "activation_checkpointing": False,
+            "mlp": (f"gate/up kept for backward in {cached} layers ({mlp_cache_gib} GiB budget, last layers first), "
+                    f"recomputed in backward in the others"), "parallelism": f"dp{gpus}",
             "l2": "per-layer operands (>= 134 MB activations + 117 MB decoded weight) exceed the 126 MB L2"}
 
 
@@ -424,7 +427,7 @@ def run_step(args):
         dist.init_process_group("nccl", device_id=device)
     _lib.load()
     spec = bench_step.WORKLOADS[args.workload]
-    model = bench_step.build_model(args.workload, device)
+    model = bench_step.build_model(args.workload, device, args.mlp_cache_gib)
     optimizer = make_optimizer(model, learning_rate=2e-5)
     trainer = Trainer(model, optimizer, device=device, loss_token_budget=4096)
     host_batch = bench_step.synthetic_batch(spec["rows"], spec["length"], spec["config"]["vocab_size"], seed=1000 + rank)
@@ -479,7 +482,7 @@ def run_step(args):
         "metric": STEP_METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world_size,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": step_config(args.workload, world_size),
+        "config": step_config(args.workload, world_size, args.mlp_cache_gib, model.last_execution),
         "step_tflops_per_gpu": flops / (ms_per_step * 1e-3) / 1e12,
         "step_frac_of_bf16_peak": flops / (ms_per_step * 1e-3) / 1e12 / peak,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -510,6 +513,9 @@ def main():
                         help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
+    parser.add_argument("--mlp-cache-gib", type=float, default=64.0,
+                        help="per-GPU byte budget for keeping MLP gate/up activations instead of recomputing them "
+                             "(0: always recompute)")
     parser.add_argument("--workload", choices=("step7b", "step1b", "projection"), default="step7b",
                         help="step7b: 7B-class decoder update (the headline metric); step1b: the 1.3B decoder; "
                              "projection: one fused NF4+LoRA projection, forward+backward")

@@ -148,6 +148,7 @@ class CausalLM(nn.Module):
         if not runtime.rank:
             raise NotImplementedError("causal_tuner_b200 covers adapter training (rank > 0) only")
         self.config, self.runtime = config, runtime
+        self.last_execution = {}
         self.model = Decoder(config, runtime, device)
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=runtime.base_dtype,
                                  device=device)
@@ -186,6 +187,21 @@ class CausalLM(nn.Module):
         x = self.model.embed_tokens(batch["input_ids"]).to(r.compute_dtype)
         layout = prepare_dense_layout(x.shape[:2], spans, x.device) if r.attention == "flash_attention_2" else None
         recompute = r.checkpoint and self.training and torch.is_grad_enabled()
+        # MLP activation cache: layers keep gate/up (instead of recomputing them in backward) while
+        # the byte budget lasts, last layers first (modeling/model.py:228-239 of the reference).
+        remaining = r.mlp_cache_budget_bytes or 0
+        if not torch.is_grad_enabled() or recompute:
+            remaining = 0
+        tokens = x.numel() // x.shape[-1]
+        retained = 0
+        for layer in reversed(self.model.layers):
+            cost = layer.mlp.cache_bytes(tokens) if remaining else 0
+            layer.mlp.cache_intermediates = bool(cost and cost <= remaining)
+            if layer.mlp.cache_intermediates:
+                remaining -= cost
+                retained += cost
+        self.last_execution = dict(rows=tokens, checkpoint=recompute, mlp_cache_bytes=retained,
+                                   mlp_cache_layers=sum(l.mlp.cache_intermediates for l in self.model.layers))
         for layer in self.model.layers:
             run = lambda z, layer=layer: layer(z, cosine, sine, segments, spans, layout, mlp_tile=r.mlp_tile,
                                                 mlp_cache=layer.mlp.cache_intermediates)

@@ -82,7 +82,9 @@ class Trainer:
             total_loss, total_weight = scalars[0], scalars[1]
             collectives = exchange.collectives
         denominator = total_weight.clamp_min(1.0)
-        torch._foreach_div_([param.grad for param in parameters], denominator)
+        # A Python scalar keeps the fused multi-tensor path (a tensor divisor is applied gradient by
+        # gradient); the value is needed on the host for the returned metrics anyway.
+        torch._foreach_div_([param.grad for param in parameters], float(denominator))
         if self.max_grad_norm:
             norm = torch.nn.utils.clip_grad_norm_(parameters, self.max_grad_norm, error_if_nonfinite=True,
                                                   foreach=all(p.is_cuda for p in parameters))
