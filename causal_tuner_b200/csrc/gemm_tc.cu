@@ -26,7 +26,7 @@
 //
 // Two variants share one body. gemm_tcgen05_kernel: one CTA per 128 x 256 tile, 4 stages of
 // 48 KB. gemm_tcgen05_pair_kernel: a cluster of two CTAs per 256 x 256 tile; each CTA stages
-// its 128 rows of A and its 128 columns of B (6 stages of 32 KB), the even CTA issues
+// its 128 rows of A and its 128 columns of B (3 stages of two 32 KB k-blocks), the even CTA issues
 // tcgen05.mma.cta_group::2 (M = 256) for both, the tensor cores fetch the other half of B from
 // the peer's shared memory, TMA completions of both CTAs are counted on the leader's barrier
 // and tcgen05.commit releases stages / publishes accumulators in both CTAs. That halves the
@@ -54,12 +54,14 @@ constexpr uint32_t MN_BOX_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an 
 constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulators
 constexpr int kMaxStages = 6;
 
-template <int CTAS, int STAGES_>
+template <int CTAS, int STAGES_, int KSUB_ = 1>
 struct Shape {
   static constexpr int kStages = STAGES_;
+  static constexpr int kSub = KSUB_;                          // 64-wide k-blocks per ring stage
   static constexpr int kBRows = BN / CTAS;                    // B columns staged by one CTA
   static constexpr uint32_t kBTileBytes = kBRows * BK * 2;    // 32 KB or 16 KB
-  static constexpr uint32_t kStageBytes = A_TILE_BYTES + kBTileBytes;
+  static constexpr uint32_t kSubBytes = A_TILE_BYTES + kBTileBytes;
+  static constexpr uint32_t kStageBytes = kSub * kSubBytes;
   static constexpr size_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 constexpr int GROUP_M = 16;                     // tile rasterisation: 16 row tiles share a sweep over columns
@@ -355,9 +357,11 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, float (&v)[32], c
 // of a cluster own a 256 x 256 tile; each stages its 128 rows of A and its 128 columns of B, the
 // even ("leader") CTA issues one cta_group::2 MMA per k step for both, and both run their own
 // epilogue on their 128 accumulator rows.
-template <int CTAS, int STAGES_>
+template <int CTAS, int STAGES_, int KSUB_>
 __device__ __forceinline__ void gemm_body(const TcParams& p) {
-  using S = Shape<CTAS, STAGES_>;
+  using S = Shape<CTAS, STAGES_, KSUB_>;
+  constexpr int KSUB = KSUB_;
+  constexpr uint32_t SUB_BYTES = S::kSubBytes;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t STAGE_BYTES = S::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
@@ -439,31 +443,37 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
           const CUtensorMap* map_a = &sg.a;
           const CUtensorMap* map_b = &sg.b;
           const bool a_mn = sg.a_mn != 0, b_mn = sg.b_mn != 0;
-          for (int k0 = lo * BK; k0 < hi * BK; k0 += BK) {
+          for (int kb = lo; kb < hi; kb += KSUB) {
             if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.error_flag, 1))) {
               alive = false;
               break;
             }
             if (lane == 0) {
-              const uint32_t a_dst = smem_base + stage * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
+              const int subs = min(KSUB, hi - kb);   // a stage holds up to KSUB 64-wide k-blocks
               // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
               const uint32_t bar = lead_full0 + 8u * stage;
-              if (leader) mbar_expect_tx(full_bar(stage), CTAS * STAGE_BYTES);
+              if (leader) mbar_expect_tx(full_bar(stage), CTAS * subs * SUB_BYTES);
               auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
                 if constexpr (CTAS == 1) tma_load_2d(dst, map, bar, x, y);
                 else tma_load_2d_pair(dst, map, bar, x, y);
               };
-              if (!a_mn) {
-                load(a_dst, map_a, k0, a_row0);
-              } else {
 #pragma unroll
-                for (int j = 0; j < BM / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
-              }
-              if (!b_mn) {
-                load(b_dst, map_b, k0, b_row0);
-              } else {
+              for (int sub = 0; sub < KSUB; ++sub) {
+                if (sub >= subs) break;
+                const int k0 = (kb + sub) * BK;
+                const uint32_t a_dst = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES, b_dst = a_dst + A_TILE_BYTES;
+                if (!a_mn) {
+                  load(a_dst, map_a, k0, a_row0);
+                } else {
 #pragma unroll
-                for (int j = 0; j < S::kBRows / 64; ++j) load(b_dst + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k0);
+                  for (int j = 0; j < BM / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
+                }
+                if (!b_mn) {
+                  load(b_dst, map_b, k0, b_row0);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < S::kBRows / 64; ++j) load(b_dst + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k0);
+                }
               }
             }
             __syncwarp();
@@ -514,22 +524,28 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
           const uint32_t b_lo0 = desc_low(smem_base + A_TILE_BYTES, sg.b_mn ? MN_BOX_BYTES : 16u);
           const uint32_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
           const uint32_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
-          for (int kb = lo; kb < hi; ++kb) {
+          for (int kb = lo; kb < hi; kb += KSUB) {
             if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.error_flag, 3))) {
               alive = false;
               break;
             }
             tcgen05_fence_after();
-            const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
+            const int subs = min(KSUB, hi - kb);
             if (lane == 0) {
 #pragma unroll
-              for (int j = 0; j < BK / UMMA_K; ++j) {
-                if constexpr (CTAS == 1)
-                  umma_bf16(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
-                            (accumulate | j) ? 1u : 0u);
-                else
-                  umma_bf16_pair(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
-                                 (accumulate | j) ? 1u : 0u);
+              for (int sub = 0; sub < KSUB; ++sub) {
+                if (sub >= subs) break;
+                const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4) + sub * (SUB_BYTES >> 4);
+                const uint32_t b_lo = b_lo0 + stage * (STAGE_BYTES >> 4) + sub * (SUB_BYTES >> 4);
+#pragma unroll
+                for (int j = 0; j < BK / UMMA_K; ++j) {
+                  if constexpr (CTAS == 1)
+                    umma_bf16(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                              (accumulate | sub | j) ? 1u : 0u);
+                  else
+                    umma_bf16_pair(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                                   (accumulate | sub | j) ? 1u : 0u);
+                }
               }
               if constexpr (CTAS == 1) umma_commit(empty_bar(stage));
               else umma_commit_pair(empty_bar(stage));
@@ -604,13 +620,13 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
-  gemm_body<1, 4>(p);
+  gemm_body<1, 4, 1>(p);
 }
 
-template <int STAGES_>
+template <int STAGES_, int KSUB_>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ TcParams p) {
-  gemm_body<2, STAGES_>(p);
+  gemm_body<2, STAGES_, KSUB_>(p);
 }
 
 // ---- host side ------------------------------------------------------------------
@@ -706,19 +722,19 @@ int configure(Kernel kernel, size_t smem, bool* configured) {
   return CT_OK;
 }
 
-template <int STAGES_>
+template <int STAGES_, int KSUB_>
 int launch_pair(const TcParams& p, unsigned grid, int device, cudaStream_t stream) {
   static bool configured[64] = {};
-  const size_t smem = Shape<2, STAGES_>::kSmemBytes;
-  const int rc = configure(gemm_tcgen05_pair_kernel<STAGES_>, smem, &configured[device]);
+  const size_t smem = Shape<2, STAGES_, KSUB_>::kSmemBytes;
+  const int rc = configure(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, smem, &configured[device]);
   if (rc != CT_OK) return rc;
-  gemm_tcgen05_pair_kernel<STAGES_><<<grid, kThreads, smem, stream>>>(p);
+  gemm_tcgen05_pair_kernel<STAGES_, KSUB_><<<grid, kThreads, smem, stream>>>(p);
   return CT_OK;
 }
 
 int launch_single(const TcParams& p, unsigned grid, int device, cudaStream_t stream) {
   static bool configured[64] = {};
-  const size_t smem = Shape<1, 4>::kSmemBytes;
+  const size_t smem = Shape<1, 4, 1>::kSmemBytes;
   const int rc = configure(gemm_tcgen05_kernel, smem, &configured[device]);
   if (rc != CT_OK) return rc;
   gemm_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(p);
@@ -775,11 +791,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   const bool timed = timing_enabled();
   if (timed) timing_begin(stream);
   if (ctas == 2) {
-    const char* text = getenv("CT_B200_GEMM_STAGES");
-    const int stages = text ? atoi(text) : 6;
-    rc = stages == 4 ? launch_pair<4>(p, grid, device, stream)
-       : stages == 7 ? launch_pair<7>(p, grid, device, stream)
-                     : launch_pair<6>(p, grid, device, stream);
+    // Default: 3 stages of two 64-wide k-blocks (one barrier round per 8 MMAs). CT_B200_GEMM_KSUB=1
+    // selects 6 stages of one k-block (one round per 4 MMAs) for comparison runs.
+    const char* ksub_text = getenv("CT_B200_GEMM_KSUB");
+    const int ksub = ksub_text ? atoi(ksub_text) : 2;
+    rc = ksub == 1 ? launch_pair<6, 1>(p, grid, device, stream) : launch_pair<3, 2>(p, grid, device, stream);
   } else {
     rc = launch_single(p, grid, device, stream);
   }
