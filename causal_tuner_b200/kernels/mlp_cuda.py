@@ -155,16 +155,18 @@ class _TiledLoRAMLP(torch.autograd.Function):
             xa = [buffer[:count] for buffer in low_inputs]
             low = [low_grad[:count, :a.shape[0]] for a, _ in adapters]
             if ctx.cache:
-                # The activation backward overwrites its tile buffers; copy the tile so that the
-                # saved tensors survive a repeated backward pass.
-                gate.copy_(saved[0][start:stop])
-                up.copy_(saved[1][start:stop])
                 xa[0], xa[1] = saved[2][start:stop], saved[3][start:stop]
             else:
                 forward_linear(part, matrices[0], *adapters[0], out=gate, xa=xa[0])
                 forward_linear(part, matrices[1], *adapters[1], out=up, xa=xa[1])
             input_gradient(dy, matrices[2], *adapters[2], dh, low[2])
-            hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
+            if ctx.cache:
+                # Read the saved gate/up, write (d_gate, d_up, hidden) into the tile buffers: the saved
+                # tensors stay untouched and survive a repeated backward pass, without a copy.
+                _swiglu(saved[0][start:stop], saved[1][start:stop], dh, dh, gate, up, True)
+                hidden = dh
+            else:
+                hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
             matmul(hidden, adapters[2][0].T, out=xa[2])
             parameter_gradients(hidden, dy, *gradients[2], low[2], xa[2], add=start > 0)
             for index, signal in enumerate((gate, up)):

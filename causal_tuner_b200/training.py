@@ -39,7 +39,25 @@ class Trainer:
         total_loss = torch.zeros((), device=self.device, dtype=torch.float32)
         total_weight = torch.zeros_like(total_loss)
         microbatches, valid_tokens = 0, 0
-        for batch in batches:
+        batches = list(batches)
+        parameters = [p for group in self.optimizer.param_groups for p in group["params"]]
+        distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+        exchange, hooks = None, []
+        for index, batch in enumerate(batches):
+            if distributed and index == len(batches) - 1:
+                # Last micro-batch: every gradient is final as soon as autograd has accumulated it, so
+                # it joins a bucket right away and full buckets are all-reduced under the rest of the
+                # backward pass.
+                exchange = GradientExchange(self.group, self.bucket_bytes)
+                wide = {}
+
+                def ready(param, exchange=exchange, wide=wide):
+                    if param.grad.dtype == torch.float32:
+                        exchange.add(param.grad)
+                    else:                              # 16-bit training dtype: exchange in fp32, round once
+                        wide[param] = param.grad.float()
+                        exchange.add(wide[param])
+                hooks = [p.register_post_accumulate_grad_hook(ready) for p in parameters]
             microbatches += 1
             valid_tokens += int(batch["attention_mask"].sum())
             targets, weights = prediction_targets(batch)
@@ -57,28 +75,18 @@ class Trainer:
             del loss, batch
         if microbatches == 0:
             raise ValueError("An optimizer update requires at least one microbatch")
-        parameters = [p for group in self.optimizer.param_groups for p in group["params"]]
+        for hook in hooks:
+            hook.remove()
         for param in parameters:
             if param.grad is None:
                 raise RuntimeError("A trainable parameter has no gradient; the graph is disconnected")
         collectives = 0
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            exchange = GradientExchange(self.group, self.bucket_bytes)
+        if exchange is not None:
             scalars = torch.stack((total_loss, total_weight))
             exchange.add(scalars)
-            for param in parameters:
-                if param.grad.dtype == torch.float32:
-                    exchange.add(param.grad)
-                else:                                  # 16-bit training dtype: exchange in fp32, round once
-                    wide = param.grad.float()
-                    exchange.add(wide)
-                    param._exchange = wide
             exchange.finish()
-            for param in parameters:
-                wide = getattr(param, "_exchange", None)
-                if wide is not None:
-                    param.grad.copy_(wide)
-                    del param._exchange
+            for param, value in wide.items():
+                param.grad.copy_(value)
             total_loss, total_weight = scalars[0], scalars[1]
             collectives = exchange.collectives
         denominator = total_weight.clamp_min(1.0)
