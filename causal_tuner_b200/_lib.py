@@ -31,6 +31,7 @@ SIGNATURES = {
     "ct_matmul": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _L, _L, _I, _I, _I, _I, _P]),
     "ct_forward_linear": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _P]),
     "ct_input_gradient": (_I, [_P, _L, _P, _L, _P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _I, _P]),
+    "ct_input_gradient_group": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _I, _P]),
     "ct_parameter_gradients_workspace": (_L, [_L, _L, _L, _L, _I, _I]),
     "ct_parameter_gradients": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, _P, _I, _P]),
     "ct_parameter_gradients_noalloc_capacity": (_L, []),

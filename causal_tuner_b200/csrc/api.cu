@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -42,6 +43,7 @@ namespace {
 struct TimedLaunch {
   cudaEvent_t start, stop;
   double flops;
+  long long m, n, k;
 };
 std::mutex g_timing_mutex;
 std::vector<TimedLaunch> g_timed;
@@ -69,13 +71,13 @@ void timing_begin(cudaStream_t stream) {
   if (g_pending_start) cudaEventRecord(g_pending_start, stream);
 }
 
-void timing_end(cudaStream_t stream, double flops) {
+void timing_end(cudaStream_t stream, double flops, long long m, long long n, long long k) {
   std::lock_guard<std::mutex> lock(g_timing_mutex);
   if (!g_pending_start) return;
   cudaEvent_t stop = take_event();
   if (!stop) return;
   cudaEventRecord(stop, stream);
-  g_timed.push_back({g_pending_start, stop, flops});
+  g_timed.push_back({g_pending_start, stop, flops, m, n, k});
   g_pending_start = nullptr;
 }
 
@@ -115,9 +117,11 @@ GemmArgs blank(int64_t M, int64_t N, int in_dtype, void* out, int64_t ldo, int o
 // shapes alone (148 is the B200 SM count), so a given problem is always summed in
 // the same order.
 int gradient_splits(int64_t rows, int64_t cols, int64_t T) {
-  const int64_t tiles = ((rows + 127) / 128) * ((cols + 255) / 256);
+  // Output tiles are 256 x 256 on 74 CTA pairs from 256 rows up, 128 x 256 on 148 CTAs below.
+  const bool pairs = rows >= 256;
+  const int64_t tiles = ((rows + (pairs ? 255 : 127)) / (pairs ? 256 : 128)) * ((cols + 255) / 256);
   const int64_t k_blocks = (T + 63) / 64;
-  int64_t splits = tiles > 0 ? 148 / tiles : 1;
+  int64_t splits = tiles > 0 ? (pairs ? 74 : 148) / tiles : 1;
   if (splits > 16) splits = 16;
   if (splits > k_blocks / 8) splits = k_blocks / 8;  // keep at least 8 k-blocks per slice
   if (splits < 1) splits = 1;
@@ -169,6 +173,9 @@ extern "C" int ct_timing_collect(double* total_ms, double* total_flops, int64_t*
   std::lock_guard<std::mutex> lock(g_timing_mutex);
   double ms = 0, flops = 0;
   int64_t count = 0;
+  // CT_B200_TIMING_LOG=<file>: append one "M,N,K,ms" line per recorded launch (shape studies).
+  const char* log_path = getenv("CT_B200_TIMING_LOG");
+  FILE* shape_log = log_path ? fopen(log_path, "a") : nullptr;
   for (auto& t : g_timed) {
     cudaError_t err = cudaEventSynchronize(t.stop);
     float one = 0;
@@ -177,10 +184,12 @@ extern "C" int ct_timing_collect(double* total_ms, double* total_flops, int64_t*
     ms += one;
     flops += t.flops;
     ++count;
+    if (shape_log) fprintf(shape_log, "%lld,%lld,%lld,%.6f\n", t.m, t.n, t.k, one);
     g_event_pool.push_back(t.start);
     g_event_pool.push_back(t.stop);
   }
   g_timed.clear();
+  if (shape_log) fclose(shape_log);
   *total_ms = ms;
   *total_flops = flops;
   *launches = count;
@@ -263,6 +272,36 @@ extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, i
   GemmArgs g = blank(T, K, dtype, dx, ld_dx, dtype);
   g.seg[g.nseg++] = segment(dy, ld_dy, 1, w, ldw, 1, N);
   if (r > 0) g.seg[g.nseg++] = segment(low, ld_low, 1, a, K, 1, r);
+  g.beta = add;
+  return gemm_dispatch(g, path, s);
+}
+
+extern "C" int ct_input_gradient_group(int count, const void* const* dy, const int64_t* ld_dy, const void* const* w,
+                                       const int64_t* ldw, const void* const* a, const void* const* b,
+                                       const int64_t* N, const int64_t* r, void* dx, int64_t ld_dx, void* const* low,
+                                       const int64_t* ld_low, int64_t T, int64_t K, int add, int dtype, int path,
+                                       void* stream) {
+  if (count < 1 || 2 * count > kMaxSegments) return fail(CT_ERR_ARG, "ct_input_gradient_group: count %d", count);
+  if (T < 0 || K < 0) return fail(CT_ERR_ARG, "ct_input_gradient_group: negative size");
+  if (T == 0 || K == 0) return CT_OK;
+  if (!dy || !ld_dy || !w || !ldw || !a || !b || !N || !r || !dx || !low || !ld_low)
+    return fail(CT_ERR_ARG, "ct_input_gradient_group: null pointer");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_input_gradient_group: dtype %d", dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < count; ++i) {
+    if (N[i] <= 0 || r[i] <= 0 || !dy[i] || !w[i] || !a[i] || !b[i] || !low[i])
+      return fail(CT_ERR_ARG, "ct_input_gradient_group: projection %d is incomplete", i);
+    GemmArgs g = blank(T, r[i], dtype, low[i], ld_low[i], dtype);
+    g.nseg = 1;
+    g.seg[0] = segment(dy[i], ld_dy[i], 1, b[i], r[i], 1, N[i]);
+    const int rc = gemm_dispatch(g, path, s);
+    if (rc != CT_OK) return rc;
+  }
+  GemmArgs g = blank(T, K, dtype, dx, ld_dx, dtype);
+  for (int i = 0; i < count; ++i) {
+    g.seg[g.nseg++] = segment(dy[i], ld_dy[i], 1, w[i], ldw[i], 1, N[i]);
+    g.seg[g.nseg++] = segment(low[i], ld_low[i], 1, a[i], K, 1, r[i]);
+  }
   g.beta = add;
   return gemm_dispatch(g, path, s);
 }

@@ -19,7 +19,7 @@ int* device_error_flag();
 // Optional per-launch timing of the tcgen05 GEMM (CUDA events on the launching stream).
 bool timing_enabled();
 void timing_begin(cudaStream_t stream);
-void timing_end(cudaStream_t stream, double flops);
+void timing_end(cudaStream_t stream, double flops, long long m, long long n, long long k);
 
 // ---- dtype helpers ------------------------------------------------------------
 __host__ __device__ inline int dtype_size(int dtype) { return dtype == CT_F32 ? 4 : 2; }
@@ -60,7 +60,7 @@ __device__ __forceinline__ float round_dtype(float v, int dtype) {
 // then (optionally)  D = round(D) + residual, rounded again.
 // Element (m, k) of A_s is at a[m * a_rs + k * a_cs]; element (k, n) of B_s at
 // b[k * b_rs + n * b_cs]. One stride of each pair is 1.
-constexpr int kMaxSegments = 4;
+constexpr int kMaxSegments = 6;
 
 struct Segment {
   const void* a;

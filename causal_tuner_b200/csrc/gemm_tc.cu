@@ -700,14 +700,14 @@ bool gemm_tcgen05_supported(const GemmArgs& g) {
   return tiles < (1LL << 30);
 }
 
-// CTA pairs pay off once a tile's 256 rows are mostly real rows; small-M products (and the
-// token-contracted dA with its 256 rows cut into slices) stay on the single-CTA kernel.
+// CTA pairs pay off once a tile's 256 rows are real rows; products with fewer than 256 rows stay
+// on the single-CTA kernel.
 // The environment variable CT_B200_GEMM_CTAS (1 or 2) pins the choice for experiments and tests.
 int ctas_for(const GemmArgs& g) {
   const char* text = getenv("CT_B200_GEMM_CTAS");
   const int pinned = text ? atoi(text) : 0;
   if (pinned == 1 || pinned == 2) return pinned;
-  return g.M > 2 * BM ? 2 : 1;
+  return g.M >= 2 * BM ? 2 : 1;
 }
 
 template <typename Kernel>
@@ -803,7 +803,8 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   if (timed) {
     double k_total = 0;
     for (int s = 0; s < g.nseg; ++s) k_total += static_cast<double>(g.seg[s].k);
-    timing_end(stream, 2.0 * static_cast<double>(g.M) * static_cast<double>(g.N) * k_total);
+    timing_end(stream, 2.0 * static_cast<double>(g.M) * static_cast<double>(g.N) * k_total, g.M, g.N,
+               static_cast<long long>(k_total));
   }
   count_launch(true);
   return check_launch("gemm_tcgen05");

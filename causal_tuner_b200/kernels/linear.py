@@ -161,6 +161,32 @@ def input_gradient(dy, weight, a, b, dx, low, *, add=False):
             _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
 
 
+def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
+    """Input gradient of projections that share their input, in one GEMM:
+    low_i = dy_i @ b_i and dx = (add ? dx : 0) + sum_i (dy_i @ weight_i + low_i @ a_i).
+    Same arithmetic as calling `input_gradient` per projection with add=index > 0
+    (kernels/linear.py:122), except that dx is rounded once."""
+    import ctypes
+    count = len(dys)
+    _lib.require_cuda(dx, *dys, *weights, *lows)
+    dys = [_readable(t) for t in dys]
+    weights = [_readable(t) for t in weights]
+    a_list, b_list = [t.contiguous() for t in a_list], [t.contiguous() for t in b_list]
+    _writable(dx, "dx")
+    for low in lows:
+        _writable(low, "low")
+    pointers = lambda tensors: (ctypes.c_void_p * count)(*[t.data_ptr() for t in tensors])
+    sizes = lambda values: (ctypes.c_int64 * count)(*values)
+    rows, inner = dys[0].shape[0], weights[0].shape[1]
+    with _lib.on_device(dx):
+        _lib.check(_lib.load().ct_input_gradient_group(
+            count, pointers(dys), sizes([_leading(t) for t in dys]), pointers(weights),
+            sizes([_leading(t) for t in weights]), pointers(a_list), pointers(b_list),
+            sizes([t.shape[0] for t in weights]), sizes([t.shape[0] for t in a_list]), dx.data_ptr(), _leading(dx),
+            pointers(lows), sizes([_leading(t) for t in lows]), rows, inner, int(bool(add)),
+            _lib.code_of(dx.dtype), _lib.gemm_path, _lib.stream_of(dx)))
+
+
 def parameter_gradients(x, dy, da, db, low, xa, *, add):
     """da (+)= low.T @ x and db (+)= dy.T @ xa in fp32 (kernels/linear.py:42-44), summed in a fixed order."""
     _lib.require_cuda(x, dy, da, db, low, xa)
@@ -260,6 +286,28 @@ class _LoRAGroup(torch.autograd.Function):
             width = max(parameters[4 * i + 2].shape[0] for i in range(min(2, len(states))))
             rotary = torch.empty(min(step, rows) * width, device=x.device, dtype=dtype)
         results = []
+        if want_dx and len(states) > 1 and step >= rows > 0:
+            # Untiled group (q/k/v): one GEMM sums the input gradients of all projections.
+            prepared = []
+            for index, (state, grad) in enumerate(zip(states, grad_outputs)):
+                weight, a, b, _ = parameters[4 * index:4 * index + 4]
+                signal = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
+                if ctx.head_dim and index < 2:
+                    signal = core_cuda.inverse_rope_tile(signal, cosine, sine, ctx.head_dim, torch.empty_like(signal))
+                prepared.append((materialize(weight, state, dtype), cast(a, dtype), cast(b, dtype), signal,
+                                 torch.empty((rows, a.shape[0]), device=x.device, dtype=dtype)))
+            input_gradient_group([p[3] for p in prepared], [p[0] for p in prepared], [p[1] for p in prepared],
+                                 [p[2] for p in prepared], dx, [p[4] for p in prepared])
+            for index, (matrix, a16, b16, signal, low) in enumerate(prepared):
+                a, b = parameters[4 * index + 1], parameters[4 * index + 2]
+                da, db = torch.empty_like(a), torch.empty_like(b)
+                xa = workspace[1, :rows, :a.shape[0]]
+                matmul(flat, a16.T, out=xa)
+                parameter_gradients(flat, signal, da, db, low, xa, add=False)
+                results.extend((None, da, db, None))
+            del prepared
+            residual_grad = grad_outputs[0] if ctx.needs_input_grad[7] else None
+            return (cast(dx.reshape(x.shape), x.dtype), None, None, None, None, None, None, residual_grad, *results)
         for index, (state, grad) in enumerate(zip(states, grad_outputs)):
             weight, a, b, _ = parameters[4 * index:4 * index + 4]
             matrix = materialize(weight, state, dtype) if want_dx else None

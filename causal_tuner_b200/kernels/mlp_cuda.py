@@ -10,8 +10,8 @@ and its in-place backward are ct_swiglu.
 import torch
 
 from .. import _lib
-from .linear import (cast, materialize, forward_linear, input_gradient, parameter_gradients, projection_parameters,
-                     matmul)
+from .linear import (cast, materialize, forward_linear, input_gradient, input_gradient_group, parameter_gradients,
+                     projection_parameters, matmul)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -146,14 +146,14 @@ class _TiledLoRAMLP(torch.autograd.Function):
         width = matrices[0].shape[0]
         workspace = torch.empty((3, held, width), device=x.device, dtype=dtype)
         low_inputs = [torch.empty((held, a.shape[0]), device=x.device, dtype=dtype) for a, _ in adapters]
-        low_grad = torch.empty((held, max(a.shape[0] for a, _ in adapters)), device=x.device, dtype=dtype)
+        low_grad = torch.empty((3, held, max(a.shape[0] for a, _ in adapters)), device=x.device, dtype=dtype)
         for start in range(0, rows, step):
             stop = min(start + step, rows)
             count = stop - start
             part, dy = flat[start:stop], upstream[start:stop]
             gate, up, dh = workspace[0, :count], workspace[1, :count], workspace[2, :count]
             xa = [buffer[:count] for buffer in low_inputs]
-            low = [low_grad[:count, :a.shape[0]] for a, _ in adapters]
+            low = [low_grad[i, :count, :a.shape[0]] for i, (a, _) in enumerate(adapters)]
             if ctx.cache:
                 xa[0], xa[1] = saved[2][start:stop], saved[3][start:stop]
             else:
@@ -169,11 +169,12 @@ class _TiledLoRAMLP(torch.autograd.Function):
                 hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
             matmul(hidden, adapters[2][0].T, out=xa[2])
             parameter_gradients(hidden, dy, *gradients[2], low[2], xa[2], add=start > 0)
+            if want_dx:
+                # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
+                input_gradient_group((gate, up), matrices[:2], [adapters[0][0], adapters[1][0]],
+                                     [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
             for index, signal in enumerate((gate, up)):
-                if want_dx:
-                    input_gradient(signal, matrices[index], *adapters[index], dx[start:stop], low[index],
-                                   add=index > 0)
-                else:
+                if not want_dx:
                     matmul(signal, adapters[index][1], out=low[index])
                 parameter_gradients(part, signal, *gradients[index], low[index], xa[index], add=start > 0)
         result = [value for da, db in gradients for value in (None, da, db, None)]

@@ -134,6 +134,21 @@ CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64
                       void* low, int64_t ld_low, int64_t T, int64_t K, int64_t N,
                       int64_t r, int add, int dtype, int path, void* stream);
 
+/* ---- fused input gradient of a projection group ---------------------------------
+ * Replaces the per-projection accumulation `add=index > 0` of kernels/linear.py:122 for the
+ * projections that share one input (q/k/v, gate/up): `count` (1..3) projections,
+ *   low_i = round(dy_i @ b_i)                                             [T, r_i]
+ *   dx    = round((add ? dx : 0) + sum_i (dy_i @ w_i + low_i @ a_i))      [T, K]
+ * in ONE GEMM over the concatenated contraction [dy_0 | low_0 | dy_1 | low_1 | ...], so dx is
+ * written (and rounded) once instead of being re-read and re-rounded per projection. Arrays of
+ * `count` device pointers / sizes live in HOST memory. dy_i[T, N_i], w_i[N_i, K], a_i[r_i, K],
+ * b_i[N_i, r_i] contiguous. */
+CT_API int ct_input_gradient_group(int count, const void* const* dy, const int64_t* ld_dy,
+                                   const void* const* w, const int64_t* ldw, const void* const* a,
+                                   const void* const* b, const int64_t* N, const int64_t* r, void* dx,
+                                   int64_t ld_dx, void* const* low, const int64_t* ld_low, int64_t T,
+                                   int64_t K, int add, int dtype, int path, void* stream);
+
 /* ---- LoRA parameter gradients ----------------------------------------------
  * Replaces kernels/linear.py:42-44 (parameter_gradients).
  *   da[r, K] = (add ? da : 0) + low^T @ x     fp32
