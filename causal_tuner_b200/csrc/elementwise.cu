@@ -141,6 +141,48 @@ rope_kernel(const T* x, const T* cosine, const T* sine, T* y, int64_t rows, int 
   }
 }
 
+// 16-bit types, 8 elements (4 pairs) per thread: one 16-byte load/store of x and one 8-byte load each of
+// cos and sin. Needs head_dim % 8 == 0, half % 4 == 0 and 16-byte aligned x / y (8-byte cos / sin).
+// `rotated_only`: y aliases x, so the pass-through part of every head is left alone.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rope_vec_kernel(const T* x, const T* cosine, const T* sine, T* y, int64_t rows, int heads, int head_dim, int half,
+                int inverse, int rotated_only) {
+  const int chunks_per_head = head_dim / 8, rotated_chunks = half / 4;
+  const int per_head = rotated_only ? rotated_chunks : chunks_per_head;
+  const int64_t total = rows * heads * per_head;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int chunk = static_cast<int>(i % per_head);
+    const int64_t head_index = i / per_head;             // token * heads + head
+    const int64_t token = head_index / heads;
+    const int64_t offset = head_index * head_dim + chunk * 8;
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + offset);
+    if (chunk >= rotated_chunks) {
+      *reinterpret_cast<uint4*>(y + offset) = raw;
+      continue;
+    }
+    const uint2 craw = __ldg(reinterpret_cast<const uint2*>(cosine + token * half + chunk * 4));
+    const uint2 sraw = __ldg(reinterpret_cast<const uint2*>(sine + token * half + chunk * 4));
+    const T* xv = reinterpret_cast<const T*>(&raw);
+    const T* cv = reinterpret_cast<const T*>(&craw);
+    const T* sv = reinterpret_cast<const T*>(&sraw);
+    uint4 result;
+    T* yv = reinterpret_cast<T*>(&result);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float even = to_float<T>(xv[2 * j]), odd = to_float<T>(xv[2 * j + 1]);
+      const float c = to_float<T>(cv[j]);
+      const float sn = inverse ? -to_float<T>(sv[j]) : to_float<T>(sv[j]);
+      const float ec = round_to<T>(__fmul_rn(even, c)), os = round_to<T>(__fmul_rn(odd, sn));
+      const float oc = round_to<T>(__fmul_rn(odd, c)), es = round_to<T>(__fmul_rn(even, sn));
+      yv[2 * j] = from_float<T>(__fsub_rn(ec, os));
+      yv[2 * j + 1] = from_float<T>(__fadd_rn(oc, es));
+    }
+    *reinterpret_cast<uint4*>(y + offset) = result;
+  }
+}
+
 // ---- residual add -----------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads) add_kernel(T* y, const T* r, int64_t n) {
@@ -262,6 +304,23 @@ extern "C" int ct_rope(const void* x, const void* cosine, const void* sine, void
   if (!x || !y || (half && (!cosine || !sine))) return fail(CT_ERR_ARG, "ct_rope: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = rows * heads * (head_dim / 2);
+  const bool vec = dtype != CT_F32 && head_dim % 8 == 0 && half % 4 == 0 && half > 0 && aligned16(x) && aligned16(y) &&
+                   (reinterpret_cast<uintptr_t>(cosine) & 7) == 0 && (reinterpret_cast<uintptr_t>(sine) & 7) == 0;
+  if (vec) {
+    const int rotated_only = x == y;
+    const int64_t work = rows * heads * (rotated_only ? half / 4 : head_dim / 8);
+    if (dtype == CT_BF16)
+      rope_vec_kernel<__nv_bfloat16><<<grid_for(work), kThreads, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cosine),
+          static_cast<const __nv_bfloat16*>(sine), static_cast<__nv_bfloat16*>(y), rows, heads, head_dim, half, inverse,
+          rotated_only);
+    else
+      rope_vec_kernel<__half><<<grid_for(work), kThreads, 0, s>>>(
+          static_cast<const __half*>(x), static_cast<const __half*>(cosine), static_cast<const __half*>(sine),
+          static_cast<__half*>(y), rows, heads, head_dim, half, inverse, rotated_only);
+    count_launch(false);
+    return check_launch("ct_rope");
+  }
   if (dtype == CT_BF16)
     rope_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cosine),

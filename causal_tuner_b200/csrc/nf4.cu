@@ -20,7 +20,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kGroup = 8;  // elements per thread per step: 4 packed bytes in, 16 bytes of bf16 out
-constexpr int kSteps = 4;  // steps per thread
+constexpr int kSteps = 8;  // steps per thread
 
 struct Nf4Params {
   const uint8_t* packed;
@@ -87,6 +87,33 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
   const float* mine = lut + (threadIdx.x & 31);
   OutT* out = static_cast<OutT*>(p.out);
   const bool vector = p.vector_ok && p.blocksize % kGroup == 0;
+  const int64_t block_first = static_cast<int64_t>(blockIdx.x) * kSteps * kThreads * kGroup;
+
+  if (vector && block_first + static_cast<int64_t>(kSteps) * kThreads * kGroup <= p.n) {
+    // Whole block in range: issue every load of the thread before the first use, so that four
+    // independent 4-byte reads (plus their scales) are in flight per thread.
+    uint32_t word[kSteps];
+    float scale[kSteps];
+#pragma unroll
+    for (int step = 0; step < kSteps; ++step) {
+      const int64_t first = block_first + (static_cast<int64_t>(step) * kThreads + threadIdx.x) * kGroup;
+      word[step] = __ldg(reinterpret_cast<const uint32_t*>(p.packed + first / 2));
+      scale[step] = block_scale(p, first / p.blocksize);
+    }
+#pragma unroll
+    for (int step = 0; step < kSteps; ++step) {
+      const int64_t first = block_first + (static_cast<int64_t>(step) * kThreads + threadIdx.x) * kGroup;
+      float v[kGroup];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t byte = (word[step] >> (8 * b)) & 255u;
+        v[2 * b] = round_dtype(__fmul_rn(mine[(byte >> 4) * 32], scale[step]), p.state_dtype);
+        v[2 * b + 1] = round_dtype(__fmul_rn(mine[(byte & 15u) * 32], scale[step]), p.state_dtype);
+      }
+      store_group<OutT>(out + first, v);
+    }
+    return;
+  }
 
 #pragma unroll 1
   for (int step = 0; step < kSteps; ++step) {
