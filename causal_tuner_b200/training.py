@@ -12,6 +12,7 @@ single-device accumulation over the concatenated batch (up to fp32 summation ord
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from .dp import GradientExchange
 from .kernels.loss import active_rows, projection_loss
 from .segments import prediction_targets
@@ -104,6 +105,7 @@ class Trainer:
             for group in self.optimizer.param_groups:
                 group["lr"] = learning_rate
         self.optimizer.step()
+        _lib.check_device()   # a kernel that gave up on a bounded wait must not pass as a finished step
         return {"loss": (total_loss / denominator).item(), "effective_weight": total_weight.item(),
                 "grad_norm": norm.item(), "microbatches": microbatches, "valid_tokens": valid_tokens,
                 "collectives": collectives}

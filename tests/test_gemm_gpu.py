@@ -175,3 +175,29 @@ def test_auto_path_picks_tcgen05_for_aligned_bf16():
     linear.matmul(left, right, out=out)
     assert _lib.tcgen05_launch_count() == before + 1
     assert relative(out, left.float() @ right.float()) < 4e-3
+
+
+@pytest.mark.parametrize("shapes", [((32, 8, 8), (4, 8, 16)), ((4096, 128, 128), (256, 256, 256)), ((520, 520), (16, 24))])
+def test_grouped_input_gradient_equals_the_sum_of_the_projections(path, shapes):
+    outers, ranks = shapes
+    rows, inner = 300 if outers[0] != 4096 else 1024, 32 if outers[0] == 32 else 512
+    dys = [torch.randn(rows, n, device="cuda").bfloat16() for n in outers]
+    weights = [(torch.randn(n, inner, device="cuda") * .05).bfloat16() for n in outers]
+    a_list = [(torch.randn(r, inner, device="cuda") * .05).bfloat16() for r in ranks]
+    b_list = [(torch.randn(n, r, device="cuda") * .05).bfloat16() for n, r in zip(outers, ranks)]
+    lows = [torch.full((rows, r), float("nan"), device="cuda", dtype=torch.bfloat16) for r in ranks]
+    dx = torch.full((rows, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+    linear.input_gradient_group(dys, weights, a_list, b_list, dx, lows)
+    expected = torch.zeros(rows, inner, device="cuda")
+    for dy, w, a, b, low in zip(dys, weights, a_list, b_list, lows):
+        assert relative(low, (dy.float() @ b.float()).bfloat16()) < 4e-3
+        expected += dy.float() @ w.float() + low.float() @ a.float()
+    assert relative(dx, expected) < 4e-3
+    separate = torch.empty_like(dx)
+    scratch = [torch.empty_like(low) for low in lows]
+    for index, (dy, w, a, b) in enumerate(zip(dys, weights, a_list, b_list)):
+        linear.input_gradient(dy, w, a, b, separate, scratch[index], add=index > 0)
+    assert relative(dx, separate) < 8e-3
+    before = dx.clone()
+    linear.input_gradient_group(dys, weights, a_list, b_list, dx, lows, add=True)
+    assert relative(dx, before.float() + expected) < 6e-3

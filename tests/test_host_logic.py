@@ -24,6 +24,7 @@ def test_operator_surface_matches_the_reference_signatures():
         linear.accumulate: ["output", "left", "right", "add"],
         linear.forward_linear: ["x", "weight", "a", "b", "out", "xa", "bias", "residual"],
         linear.input_gradient: ["dy", "weight", "a", "b", "dx", "low", "add"],
+        linear.input_gradient_group: ["dys", "weights", "a_list", "b_list", "dx", "lows", "add"],
         linear.parameter_gradients: ["x", "dy", "da", "db", "low", "xa", "add"],
         linear.projection_parameters: ["module"],
         linear.can_fuse: ["module", "x"],
