@@ -468,6 +468,18 @@ def run_step(args):
     e2e_ms, _ = timed(host_batch, max(2, min(args.steps, 5)))   # ids from pinned host memory, loss back to host
     _lib.check_device()
     peak_memory = torch.cuda.max_memory_allocated(device)
+    # The same update with every layer recomputing its MLP activations in backward (no cache budget):
+    # the low-memory end of the policy, reported beside the headline so that both are on record.
+    recompute = None
+    if args.mlp_cache_gib and model.last_execution.get("mlp_cache_layers"):
+        execution = dict(model.last_execution)
+        model.runtime.mlp_cache_budget_bytes = None
+        torch.cuda.reset_peak_memory_stats(device)
+        trainer.update([device_batch])
+        recompute_ms, _ = timed(device_batch, max(2, min(args.steps, 3)))
+        recompute = {"value": tokens_per_rank * world_size / (recompute_ms * 1e-3), "unit": "tokens/s",
+                     "ms_per_step": recompute_ms, "peak_memory_gb": torch.cuda.max_memory_allocated(device) / 1e9}
+        model.last_execution = execution
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -493,7 +505,7 @@ def run_step(args):
                      "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
                      "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps, "traffic": None},
         "clocks": clocks, "loss_first": losses[0], "loss_last": losses[-1],
-        "peak_memory_gb": peak_memory / 1e9,
+        "peak_memory_gb": peak_memory / 1e9, "mlp_recompute_everywhere": recompute,
     }
     if world_size == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = bench_step.cpu_estimate(args.workload)
