@@ -13,7 +13,7 @@
 //               residual, round, and store 64-byte row segments to global memory
 //               while the MMA warp already works on the next tile in the other
 //               accumulator.
-// The contraction may be a concatenation of up to four (A_s, B_s) segments, each
+// The contraction may be a concatenation of up to six (A_s, B_s) segments, each
 // with its own pair of tensor maps: the LoRA term x.A^T.B^T rides in the same
 // accumulator as the base product as [x | xa] . [W | B]^T, and dX sums
 // dY.W + low.A the same way. Each operand may be K-major (contraction index
@@ -52,7 +52,6 @@ constexpr int kThreads = 192;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr uint32_t MN_BOX_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
 constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulators
-constexpr int kMaxStages = 6;
 
 template <int CTAS, int STAGES_, int KSUB_ = 1>
 struct Shape {
