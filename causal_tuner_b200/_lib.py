@@ -15,7 +15,7 @@ OK, ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE = 0, -1, -2, -3, -4
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
-_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+_P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
 # name -> (restype, argtypes); one entry per declaration in include/ct_b200.h
 SIGNATURES = {
@@ -42,6 +42,9 @@ SIGNATURES = {
     "ct_rmsnorm_forward": (_I, [_P, _P, _P, _P, _L, _L, ctypes.c_float, _I, _I, _P]),
     "ct_rmsnorm_backward": (_I, [_P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
     "ct_weighted_ce": (_I, [_P, _P, _P, _P, _L, _L, _I, _I, _P]),
+    "ct_grad_norm_workspace": (_L, [_I]),
+    "ct_grad_norm": (_I, [_I, _P, _P, _P, _F, _P, _P, _P]),
+    "ct_adamw_update": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _F, _F, _F, _F, _L, _I, _P]),
 }
 
 

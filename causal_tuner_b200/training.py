@@ -14,15 +14,19 @@ import torch.distributed as dist
 
 from . import _lib
 from .dp import GradientExchange
+from .optim import FusedAdamW
 from .kernels.loss import active_rows, projection_loss
 from .segments import prediction_targets
 
 
 def make_optimizer(model, *, learning_rate=2e-5, weight_decay=0.0, betas=(0.9, 0.999), eps=1e-8):
-    """AdamW over the trainable parameters; weight decay on matrices only (training/engine.py:10-16)."""
+    """AdamW over the trainable parameters; weight decay on matrices only (training/engine.py:10-16).
+    fp32 CUDA adapters get the optimizer whose step also scales and clips (optim.py)."""
     parameters = [p for p in model.parameters() if p.requires_grad]
     groups = [{"params": group, "weight_decay": weight_decay if decay else 0.0}
               for decay in (True, False) if (group := [p for p in parameters if (p.ndim > 1) == decay])]
+    if FusedAdamW.supports(parameters):
+        return FusedAdamW(groups, lr=learning_rate, betas=betas, eps=eps, weight_decay=weight_decay)
     return torch.optim.AdamW(groups, lr=learning_rate, betas=betas, eps=eps, weight_decay=weight_decay,
                              foreach=False, fused=all(p.is_cuda for p in parameters))
 
@@ -91,20 +95,31 @@ class Trainer:
             total_loss, total_weight = scalars[0], scalars[1]
             collectives = exchange.collectives
         denominator = total_weight.clamp_min(1.0)
-        # A Python scalar keeps the fused multi-tensor path (a tensor divisor is applied gradient by
-        # gradient); the value is needed on the host for the returned metrics anyway.
-        torch._foreach_div_([param.grad for param in parameters], float(denominator))
-        if self.max_grad_norm:
-            norm = torch.nn.utils.clip_grad_norm_(parameters, self.max_grad_norm, error_if_nonfinite=True,
-                                                  foreach=all(p.is_cuda for p in parameters))
-        else:
-            norm = torch.sqrt(sum(p.grad.float().norm().square() for p in parameters))
-            if not torch.isfinite(norm):
-                raise FloatingPointError("Non-finite gradient norm")
         if learning_rate is not None:
             for group in self.optimizer.param_groups:
                 group["lr"] = learning_rate
-        self.optimizer.step()
+        if (isinstance(self.optimizer, FusedAdamW) and FusedAdamW.supports(parameters)
+                and all(p.grad.dtype == torch.float32 and p.grad.is_contiguous() for p in parameters)):
+            # Divide, measure, clip and step in two passes over the gradients; the denominator stays on
+            # the device. A non-finite norm steps nothing and is raised below, as the reference does
+            # before its optimizer step.
+            norm = self.optimizer.scale_clip_step(denominator, self.max_grad_norm or 0.0)[0]
+            if not torch.isfinite(norm):
+                self.optimizer.rollback()
+                if self.max_grad_norm:
+                    raise RuntimeError("The total norm of the gradients is non-finite, so it cannot be clipped")
+                raise FloatingPointError("Non-finite gradient norm")
+        else:
+            # A Python scalar keeps the multi-tensor path (a tensor divisor is applied gradient by gradient).
+            torch._foreach_div_([param.grad for param in parameters], float(denominator))
+            if self.max_grad_norm:
+                norm = torch.nn.utils.clip_grad_norm_(parameters, self.max_grad_norm, error_if_nonfinite=True,
+                                                      foreach=all(p.is_cuda for p in parameters))
+            else:
+                norm = torch.sqrt(sum(p.grad.float().norm().square() for p in parameters))
+                if not torch.isfinite(norm):
+                    raise FloatingPointError("Non-finite gradient norm")
+            self.optimizer.step()
         _lib.check_device()   # a kernel that gave up on a bounded wait must not pass as a finished step
         return {"loss": (total_loss / denominator).item(), "effective_weight": total_weight.item(),
                 "grad_norm": norm.item(), "microbatches": microbatches, "valid_tokens": valid_tokens,

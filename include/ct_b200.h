@@ -245,6 +245,32 @@ CT_API int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, 
 CT_API int ct_weighted_ce(void* logits, const int64_t* targets, const float* weights, float* loss,
                           int64_t rows, int64_t vocab, int gradient, int dtype, void* stream);
 
+/* ---- gradient scale + global-norm clip + AdamW --------------------------------
+ * Replace the tail of Trainer.update (training/engine.py:97-107): `_foreach_div_(grads,
+ * denominator)`, `clip_grad_norm_(parameters, max_norm)` and the fused `AdamW.step()`
+ * (training/engine.py:10-16), as two passes over `count` fp32 tensors on one device.
+ * ct_grad_norm:
+ *   norm = || g / *divisor ||_2 over all tensors, coef = min(1, max_norm / (norm + 1e-6))
+ *          (coef = 1 when max_norm <= 0); norm_out[0] = norm, norm_out[1] = coef.
+ *   The sum runs in a fixed order, so the value is reproducible run to run.
+ * ct_adamw_update, with `norm` = the two floats above:
+ *   g' = g / *divisor * coef;  p *= 1 - lr * weight_decay[i];  m += (g' - m) * (1 - beta1);
+ *   v = beta2 * v + (1 - beta2) * g'^2;
+ *   p -= lr / (1 - beta1^step) * m / (sqrt(v) / sqrt(1 - beta2^step) + eps)
+ *   and g' is written back over g when `write_grads` != 0 (what the reference leaves in .grad).
+ *   If norm[0] is not finite no tensor is modified; the caller reads it and raises
+ *   (error_if_nonfinite=True in the reference).
+ * The pointer tables, `sizes` (elements) and `weight_decay` are HOST arrays of length `count`;
+ * `divisor` (1 float), `norm_out` / `norm` (2 floats) and `workspace`
+ * (ct_grad_norm_workspace(count) bytes) are device memory. `step` counts from 1. */
+CT_API int64_t ct_grad_norm_workspace(int count);
+CT_API int ct_grad_norm(int count, void* const* grads, const int64_t* sizes, const float* divisor,
+                        float max_norm, float* norm_out, void* workspace, void* stream);
+CT_API int ct_adamw_update(int count, void* const* grads, void* const* params, void* const* exp_avg,
+                           void* const* exp_avg_sq, const int64_t* sizes, const float* weight_decay,
+                           const float* divisor, const float* norm, float lr, float beta1, float beta2,
+                           float eps, int64_t step, int write_grads, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,3 +88,33 @@ def test_row_sharding_covers_every_row_once():
         assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
     with pytest.raises(ValueError):
         shard_rows(4, 2, 2)
+
+
+def test_balanced_assignment_evens_out_attention_cost():
+    from causal_tuner_b200.dp import balance_rows, row_costs
+    generator = torch.Generator().manual_seed(5)
+    rows, width, world = 16, 512, 4
+    segments = torch.zeros(rows, width, dtype=torch.long)
+    for row in range(rows):
+        cursor, index = 0, 1
+        while cursor < width:
+            size = int(torch.randint(8, width + 1, (), generator=generator)) if row % 2 else width
+            segments[row, cursor:cursor + size] = index
+            cursor, index = cursor + size, index + 1
+    mask = torch.ones_like(segments)
+    costs = row_costs(mask, segments, width=width)
+    assert max(costs) == pytest.approx(width + width / 12)        # one full-width document
+    assignment = balance_rows(costs, world)
+    assert sorted(r for rows_ in assignment for r in rows_) == list(range(rows))
+    assert all(len(rows_) == rows // world for rows_ in assignment)
+    load = lambda members: sum(costs[r] for r in members)
+    contiguous = [list(range(*shard_rows(rows, r, world))) for r in range(world)]
+    assert max(map(load, assignment)) <= max(map(load, contiguous))
+    assert max(map(load, assignment)) - min(map(load, assignment)) <= max(costs) - min(costs)
+    assert assignment == balance_rows(list(costs), world)          # same on every rank
+    # ragged: 7 rows over 3 ranks -> at most 3 each; padding tokens cost nothing
+    ragged = balance_rows([5., 1., 1., 1., 4., 1., 3.], 3)
+    assert [len(m) for m in ragged] == [3, 2, 2] or max(len(m) for m in ragged) <= 3
+    assert row_costs(torch.zeros(2, 8, dtype=torch.long)) == [0.0, 0.0]
+    with pytest.raises(ValueError):
+        balance_rows([1.0], 0)
