@@ -38,10 +38,13 @@ SIGNATURES = {
     "ct_parameter_gradients_noalloc": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, _I, _P]),
     "ct_swiglu": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P]),
     "ct_rope": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
+    "ct_position_values": (_I, [_P, _P, _P, _P, _L, _I, _I, _P]),
     "ct_add_inplace": (_I, [_P, _P, _L, _I, _P]),
     "ct_rmsnorm_forward": (_I, [_P, _P, _P, _P, _L, _L, ctypes.c_float, _I, _I, _P]),
     "ct_rmsnorm_backward": (_I, [_P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
     "ct_weighted_ce": (_I, [_P, _P, _P, _P, _L, _L, _I, _I, _P]),
+    "ct_nf4_encode": (_I, [_P, _L, _I, _I, _P, _P, _P, _P]),
+    "ct_nf4_nest": (_I, [_P, _L, _I, _P, _P, _P, _P, _P]),
     "ct_grad_norm_workspace": (_L, [_I]),
     "ct_grad_norm": (_I, [_I, _P, _P, _P, _F, _P, _P, _P]),
     "ct_adamw_update": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _F, _F, _F, _F, _L, _I, _P]),

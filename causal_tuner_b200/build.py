@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(ROOT, "csrc")
 LIBRARY = os.path.join(ROOT, "libct_b200.so")
 STAMP = os.path.join(ROOT, "libct_b200.so.stamp")
-SOURCES = ("api.cu", "nf4.cu", "elementwise.cu", "norm_loss.cu", "optimizer.cu", "gemm_simt.cu", "gemm_tc.cu")
+SOURCES = ("api.cu", "nf4.cu", "nf4_encode.cu", "elementwise.cu", "norm_loss.cu", "optimizer.cu", "gemm_simt.cu", "gemm_tc.cu")
 FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")
 

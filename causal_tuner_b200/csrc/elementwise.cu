@@ -224,6 +224,19 @@ reduce_partials_kernel(const float* __restrict__ partials, int slices, int64_t r
   }
 }
 
+// cos / sin of position * inverse frequency: fp32 product, full-range evaluation, rounded to T.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+position_values_kernel(const int64_t* __restrict__ positions, const float* __restrict__ inverse, T* __restrict__ cosine,
+                       T* __restrict__ sine, int64_t total, int half) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const float angle = __fmul_rn(static_cast<float>(positions[i / half]), inverse[i % half]);
+    cosine[i] = from_float<T>(cosf(angle));
+    sine[i] = from_float<T>(sinf(angle));
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -362,4 +375,26 @@ extern "C" int ct_add_inplace(void* y, const void* r, int64_t n, int dtype, void
   }
   count_launch(false);
   return check_launch("ct_add_inplace");
+}
+
+extern "C" int ct_position_values(const int64_t* positions, const float* inverse, void* cosine, void* sine,
+                                  int64_t count, int half, int dtype, void* stream) {
+  if (count < 0 || half < 0) return fail(CT_ERR_ARG, "ct_position_values: count=%lld half=%d", (long long)count, half);
+  if (count == 0 || half == 0) return CT_OK;
+  if (!positions || !inverse || !cosine || !sine) return fail(CT_ERR_ARG, "ct_position_values: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = count * half;
+  if (dtype == CT_BF16)
+    position_values_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+        positions, inverse, static_cast<__nv_bfloat16*>(cosine), static_cast<__nv_bfloat16*>(sine), total, half);
+  else if (dtype == CT_F16)
+    position_values_kernel<__half><<<grid_for(total), kThreads, 0, s>>>(
+        positions, inverse, static_cast<__half*>(cosine), static_cast<__half*>(sine), total, half);
+  else if (dtype == CT_F32)
+    position_values_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
+        positions, inverse, static_cast<float*>(cosine), static_cast<float*>(sine), total, half);
+  else
+    return fail(CT_ERR_ARG, "ct_position_values: dtype %d", dtype);
+  count_launch(false);
+  return check_launch("ct_position_values");
 }

@@ -60,10 +60,19 @@ class PartialRoPE(torch.autograd.Function):
 # ---- RMSNorm and the rotary position table ------------------------------------------------
 
 def position_values(positions, inverse, dtype):
-    """cos/sin of positions[..., None] * inverse in fp32, then cast (kernels/core_cuda.py:21-27).
-    Evaluated once per batch on [tokens, rotary_dim / 2] values with torch's full-range cos/sin."""
-    angle = positions.to(torch.float32)[..., None] * inverse.to(torch.float32)
-    return angle.cos().to(dtype), angle.sin().to(dtype)
+    """cos/sin of positions[..., None] * inverse, fp32 product and full-range evaluation, then rounded
+    to `dtype` (kernels/core_cuda.py:11-27). One launch per batch on [tokens, rotary_dim / 2] values."""
+    _lib.require_cuda(positions, inverse)
+    half = len(inverse)
+    cosine = torch.empty((*positions.shape, half), device=positions.device, dtype=dtype)
+    sine = torch.empty_like(cosine)
+    positions = positions.to(torch.int64).contiguous()
+    inverse = inverse.to(torch.float32).contiguous()
+    with _lib.on_device(positions):
+        _lib.check(_lib.load().ct_position_values(
+            positions.data_ptr(), inverse.data_ptr(), cosine.data_ptr(), sine.data_ptr(), positions.numel(), half,
+            _lib.code_of(dtype), _lib.stream_of(positions)))
+    return cosine, sine
 
 
 class RMS(torch.autograd.Function):

@@ -1,7 +1,8 @@
 """NF4 quantisation of frozen base weights and the quant-state record the decode kernel reads.
 
-Quantisation is set-up work done once per weight (plain tensor ops on whatever device the
-weight lives on); only decoding is on the training path. The layout is the one the
+Quantisation is set-up work done once per weight: `ct_nf4_encode` / `ct_nf4_nest` for a weight
+on a GPU, the same rule in plain tensor ops for a host tensor (the two agree bit for bit); only
+decoding is on the training path. The layout is the one the
 reference consumes (kernels/nf4_cuda.py:9-29): blocks of `blocksize` consecutive elements
 of the flattened weight share one fp32 absmax; element 2j of the flattened weight sits in
 the high nibble of byte j, element 2j+1 in the low nibble. With `nested=True` the absmax
@@ -72,6 +73,8 @@ def quantize_nf4(weight, blocksize=64, nested=False, blocksize2=256):
     if blocksize <= 0 or blocksize % 2:
         raise ValueError("blocksize must be a positive even number")
     device = weight.device
+    if weight.is_cuda and _device_encoder_takes(weight, blocksize, blocksize2):
+        return _quantize_on_device(weight, blocksize, nested, blocksize2)
     flat = weight.detach().reshape(-1).to(torch.float32)
     n = flat.numel()
     blocks = -(-n // blocksize)
@@ -87,7 +90,7 @@ def quantize_nf4(weight, blocksize=64, nested=False, blocksize2=256):
     packed = (indices[0::2] << 4) | indices[1::2]
     state = QuantState(shape=weight.shape, dtype=weight.dtype, blocksize=blocksize, absmax=absmax, code=code)
     if nested:
-        offset = absmax.mean()
+        offset = absmax.double().mean().float()   # fp64 accumulation: the value does not depend on the summation order
         centred = absmax - offset
         groups = -(-blocks // blocksize2)
         grid = torch.zeros(groups * blocksize2, dtype=torch.float32, device=device)
@@ -100,3 +103,37 @@ def quantize_nf4(weight, blocksize=64, nested=False, blocksize2=256):
         state.nested, state.offset = True, offset.reshape(())
         state.state2 = NestedState(code=table, absmax=absmax2, blocksize=blocksize2)
     return packed.reshape(-1, 1).contiguous(), state
+
+
+def _device_encoder_takes(weight, blocksize, blocksize2):
+    return (weight.dtype in (torch.float32, torch.bfloat16, torch.float16) and 8 <= blocksize <= 256
+            and blocksize & (blocksize - 1) == 0 and blocksize2 > 0)
+
+
+def _quantize_on_device(weight, blocksize, nested, blocksize2):
+    """`quantize_nf4` through the CUDA encoder; same outputs as the tensor-op rule above."""
+    from . import _lib
+    device = weight.device
+    flat = weight.detach().reshape(-1).contiguous()
+    n = flat.numel()
+    blocks = -(-n // blocksize)
+    packed = torch.empty((n + 1) // 2, dtype=torch.uint8, device=device)
+    absmax = torch.empty(blocks, dtype=torch.float32, device=device)
+    code = nf4_code(device)
+    library = _lib.load()
+    with _lib.on_device(flat):
+        stream = _lib.stream_of(flat)
+        _lib.check(library.ct_nf4_encode(flat.data_ptr(), n, _lib.code_of(flat.dtype), blocksize, code.data_ptr(),
+                                         packed.data_ptr(), absmax.data_ptr(), stream))
+        state = QuantState(shape=weight.shape, dtype=weight.dtype, blocksize=blocksize, absmax=absmax, code=code)
+        if nested:
+            groups = -(-blocks // blocksize2)
+            table = scale_code(device)
+            quantised = torch.empty(blocks, dtype=torch.uint8, device=device)
+            absmax2 = torch.empty(groups, dtype=torch.float32, device=device)
+            offset = torch.empty((), dtype=torch.float32, device=device)
+            _lib.check(library.ct_nf4_nest(absmax.data_ptr(), blocks, blocksize2, table.data_ptr(),
+                                           quantised.data_ptr(), absmax2.data_ptr(), offset.data_ptr(), stream))
+            state.absmax, state.nested, state.offset = quantised, True, offset
+            state.state2 = NestedState(code=table, absmax=absmax2, blocksize=blocksize2)
+    return packed.reshape(-1, 1), state

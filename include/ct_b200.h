@@ -88,6 +88,25 @@ CT_API int ct_nf4_decode(const uint8_t* packed, const void* absmax, const float*
                   void* out, int64_t n, int blocksize, int blocksize2, int nested,
                   int state_dtype, int out_dtype, void* stream);
 
+/* ---- NF4 encode ---------------------------------------------------------
+ * Replaces the bitsandbytes quantiser the reference calls when it installs a frozen base
+ * weight (modeling/lora.py:41-56, `Params4bit(..., quant_type="nf4", compress_statistics=True)`).
+ * ct_nf4_encode: for each block g of `blocksize` consecutive elements of weight[n] (`dtype`):
+ *   absmax[g] = max |w|;  index(w) = number of midpoints (code[i] + code[i+1]) / 2 strictly
+ *   below w / max(absmax[g], FLT_MIN);  packed[j] = index(w[2j]) << 4 | index(w[2j+1]);
+ *   elements past n count as 0. (n+1)/2 packed bytes, ceil(n / blocksize) absmax values.
+ *   `blocksize` is a power of two from 8 to 256 (CT_ERR_UNSUPPORTED otherwise).
+ * ct_nf4_nest: nested statistics of `blocks` absmax values:
+ *   offset[0] = mean(absmax) (fp64 accumulation in a fixed order, rounded to fp32);
+ *   absmax2[h] = max |absmax - offset| over group h of `blocksize2` values;
+ *   quantised[g] = number of midpoints of the 256-entry table `code2` strictly below
+ *   (absmax[g] - offset) / max(absmax2[h], FLT_MIN).
+ * ct_nf4_decode inverts both. All pointers are device memory. */
+CT_API int ct_nf4_encode(const void* weight, int64_t n, int dtype, int blocksize, const float* code,
+                         uint8_t* packed, float* absmax, void* stream);
+CT_API int ct_nf4_nest(const float* absmax, int64_t blocks, int blocksize2, const float* code2,
+                       uint8_t* quantised, float* absmax2, float* offset, void* stream);
+
 /* ---- dtype cast ---------------------------------------------------------
  * Replaces the per-call `a.to(dtype)`, `b.to(dtype)`, `bias.to(dtype)` casts of
  * kernels/linear.py:70-71 and kernels/mlp_cuda.py:62. src[rows, cols] (ld_src)
@@ -215,6 +234,14 @@ CT_API int ct_swiglu(const void* gate, const void* up, const void* grad, void* o
  * y may alias x. */
 CT_API int ct_rope(const void* x, const void* cosine, const void* sine, void* y, int64_t rows,
             int heads, int head_dim, int half, int inverse, int dtype, void* stream);
+
+/* ---- rotary position table --------------------------------------------------
+ * Replaces kernels/core_cuda.py:11-27 (_position_values, position_values):
+ *   cosine[t, c] = round(cos(float(positions[t]) * inverse[c])), sine likewise, c < half,
+ * the product in fp32 and cos / sin with full-range argument reduction (long logical
+ * positions), rounded to `dtype`. positions int64[count], inverse fp32[half]. */
+CT_API int ct_position_values(const int64_t* positions, const float* inverse, void* cosine,
+                              void* sine, int64_t count, int half, int dtype, void* stream);
 
 /* ---- elementwise add ---------------------------------------------------------
  * Replaces `outputs[0].add_(residual)` (kernels/linear.py:90-91) and

@@ -58,3 +58,30 @@ def encode(weight, blocksize=64):
     indices = np.searchsorted(midpoints, scaled.reshape(-1), side="left").astype(np.uint8)[:n + (n & 1)]
     packed = (indices[0::2] << 4) | indices[1::2]
     return packed.astype(np.uint8), absmax
+
+
+def scale_levels():
+    """The 256-level table of the nested statistics: sign(s) * s^2 for 256 evenly spaced s in [-1, 1]."""
+    steps = np.linspace(-1.0, 1.0, 256, dtype=np.float64)
+    return (np.sign(steps) * np.abs(steps) ** 2).astype(np.float32)
+
+
+def encode_statistics(absmax, blocksize2=256, code2=None):
+    """Nested statistics of the per-block absmax values: (uint8 indices, absmax2, offset).
+    offset = mean in fp64 rounded to fp32; the centred values are scaled by their group's
+    largest magnitude and mapped to the nearest table level (lowest index on ties).
+    Not pinned by the reference (the rule lives in bitsandbytes)."""
+    absmax = np.asarray(absmax, dtype=np.float32)
+    code2 = scale_levels() if code2 is None else np.asarray(code2, dtype=np.float32)
+    blocks = absmax.size
+    offset = np.float32(absmax.astype(np.float64).mean())
+    centred = (absmax - offset).astype(np.float32)
+    groups = (blocks + blocksize2 - 1) // blocksize2
+    grid = np.zeros(groups * blocksize2, dtype=np.float32)
+    grid[:blocks] = centred
+    grid = grid.reshape(groups, blocksize2)
+    absmax2 = np.abs(grid).max(axis=1).astype(np.float32)
+    normal = (grid / np.maximum(absmax2, np.finfo(np.float32).tiny)[:, None]).astype(np.float32)
+    midpoints = ((code2[1:] + code2[:-1]) / 2).astype(np.float32)
+    indices = np.searchsorted(midpoints, normal.reshape(-1), side="left").astype(np.uint8)[:blocks]
+    return indices, absmax2, offset

@@ -105,3 +105,23 @@ def test_cast_and_residual_add(shape):
         expected = y + r
         linear._add_inplace(y, r)
         assert torch.equal(y, expected)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_position_table_full_range(dtype):
+    from causal_tuner_b200.kernels.core_cuda import position_values
+    # ordinary packed positions and very long logical ones (argument reduction far outside [-pi, pi])
+    positions = torch.cat((torch.arange(0, 4096), torch.tensor([131071, 1 << 20, 12345678, (1 << 31) + 5]))).cuda()
+    positions = positions.reshape(2, -1)
+    inverse = (1.0 / (1e6 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))).cuda()
+    cosine, sine = position_values(positions, inverse, dtype)
+    assert cosine.shape == (*positions.shape, 32) and cosine.dtype == dtype and sine.dtype == dtype
+    angle = (positions.float()[..., None] * inverse).double()      # the fp32 product, evaluated exactly
+    tolerance = {torch.float32: 5e-7, torch.bfloat16: 4e-3, torch.float16: 5e-4}[dtype]
+    assert (cosine.double() - angle.cos()).abs().max() <= tolerance
+    assert (sine.double() - angle.sin()).abs().max() <= tolerance
+    # same values as the plain tensor expression of the reference's CPU branch (modeling/rotary.py:20-24)
+    plain = positions.float()[..., None] * inverse
+    assert (cosine.float() - plain.cos().to(dtype).float()).abs().max() <= tolerance
+    empty = position_values(positions[:, :0], inverse, dtype)
+    assert empty[0].shape == (2, 0, 32)

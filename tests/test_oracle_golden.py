@@ -51,6 +51,22 @@ def test_nf4_encoder_agrees_with_package_quantiser():
     assert (error <= 0.16 * expected_absmax[:, None] + 1e-8).all()
 
 
+@pytest.mark.parametrize("blocks,blocksize2", [(917, 256), (256, 256), (5, 64)])
+def test_nested_statistics_agree_with_package_quantiser(blocks, blocksize2):
+    from causal_tuner_b200.quant import quantize_nf4, scale_code
+    weight = torch.randn(blocks, 64) * torch.rand(blocks, 1) * 0.05
+    packed, state = quantize_nf4(weight, blocksize=64, nested=True, blocksize2=blocksize2)
+    _, absmax = nf4.encode(weight.numpy(), 64)
+    indices, absmax2, offset = nf4.encode_statistics(absmax, blocksize2)
+    assert np.array_equal(scale_code().numpy(), nf4.scale_levels())
+    assert np.array_equal(state.absmax.numpy(), indices)
+    assert np.array_equal(state.state2.absmax.numpy(), absmax2)
+    assert np.float32(state.offset) == offset
+    # the decoded scale lands within half the widest table gap (2 / 255, doubled by the square) of the true one
+    decoded = nf4.scale_levels()[indices] * np.repeat(absmax2, blocksize2)[:blocks] + offset
+    assert (np.abs(decoded - absmax) <= np.repeat(absmax2, blocksize2)[:blocks] * 8e-3 + 1e-9).all()
+
+
 @pytest.mark.parametrize("name", PROJECTION_FILES)
 def test_projection_forward_and_backward(golden, name):
     g = golden(name)
