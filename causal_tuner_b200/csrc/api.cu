@@ -81,6 +81,14 @@ void timing_end(cudaStream_t stream, double flops, long long m, long long n, lon
   g_pending_start = nullptr;
 }
 
+bool dependent_launch_enabled() {
+  static const bool enabled = [] {
+    const char* text = getenv("CT_B200_PDL");
+    return !(text && text[0] == '0');
+  }();
+  return enabled;
+}
+
 int* device_error_flag() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;

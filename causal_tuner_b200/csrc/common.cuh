@@ -21,6 +21,35 @@ bool timing_enabled();
 void timing_begin(cudaStream_t stream);
 void timing_end(cudaStream_t stream, double flops, long long m, long long n, long long k);
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched through launch_dependent() may be scheduled while the previous kernel of the
+// stream is still running: its prologue overlaps that kernel's tail, and grid_dependency_wait()
+// then blocks until the previous kernel has completed and its writes are visible. Only kernels
+// that call grid_dependency_wait() before their first access to global memory may be launched
+// this way. CT_B200_PDL=0 in the environment turns the attribute off (plain stream order).
+bool dependent_launch_enabled();
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // ---- dtype helpers ------------------------------------------------------------
 __host__ __device__ inline int dtype_size(int dtype) { return dtype == CT_F32 ? 4 : 2; }
 

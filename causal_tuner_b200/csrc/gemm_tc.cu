@@ -412,6 +412,9 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
   if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above ran while the previous kernel of the stream may still have been finishing;
+  // global memory is touched only below.
+  grid_dependency_wait();
 
   const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
   const int first_tile = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
@@ -727,7 +730,7 @@ int launch_pair(const TcParams& p, unsigned grid, int device, cudaStream_t strea
   const size_t smem = Shape<2, STAGES_, KSUB_>::kSmemBytes;
   const int rc = configure(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, smem, &configured[device]);
   if (rc != CT_OK) return rc;
-  gemm_tcgen05_pair_kernel<STAGES_, KSUB_><<<grid, kThreads, smem, stream>>>(p);
+  launch_dependent(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, dim3(grid), dim3(kThreads), smem, stream, p);
   return CT_OK;
 }
 
@@ -736,7 +739,7 @@ int launch_single(const TcParams& p, unsigned grid, int device, cudaStream_t str
   const size_t smem = Shape<1, 4, 1>::kSmemBytes;
   const int rc = configure(gemm_tcgen05_kernel, smem, &configured[device]);
   if (rc != CT_OK) return rc;
-  gemm_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(p);
+  launch_dependent(gemm_tcgen05_kernel, dim3(grid), dim3(kThreads), smem, stream, p);
   return CT_OK;
 }
 
