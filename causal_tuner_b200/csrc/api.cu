@@ -129,11 +129,21 @@ int gradient_splits(int64_t rows, int64_t cols, int64_t T) {
   const bool pairs = rows >= 256;
   const int64_t tiles = ((rows + (pairs ? 255 : 127)) / (pairs ? 256 : 128)) * ((cols + 255) / 256);
   const int64_t k_blocks = (T + 63) / 64;
-  int64_t splits = tiles > 0 ? (pairs ? 74 : 148) / tiles : 1;
-  if (splits > 16) splits = 16;
-  if (splits > k_blocks / 8) splits = k_blocks / 8;  // keep at least 8 k-blocks per slice
-  if (splits < 1) splits = 1;
-  return static_cast<int>(splits);
+  const int64_t slots = pairs ? 74 : 148;
+  if (tiles <= 0 || tiles >= slots) return 1;
+  // Cost of s slices in k-block times: rounds of resident tiles, each (k_blocks / s) long plus a fixed
+  // fill + epilogue share, plus the ordered sum of s partial planes. Smallest cost wins, fewest
+  // slices on a tie; at least 8 k-blocks per slice.
+  int64_t best = 1, best_cost = -1;
+  for (int64_t s = 1; s <= 16 && s * 8 <= (k_blocks > 8 ? k_blocks : 8); ++s) {
+    const int64_t rounds = (tiles * s + slots - 1) / slots;
+    const int64_t cost = rounds * ((k_blocks + s - 1) / s + 16) + (s > 1 ? 4 * s : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return static_cast<int>(best);
 }
 
 // out[rows, cols] (fp32) (+)= A^T . B over T rows; A is [T, rows], B is [T, cols].
@@ -241,10 +251,10 @@ extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int6
                                  int path, void* stream) {
   if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_forward_linear: negative size");
   if (T == 0 || N == 0) return CT_OK;
-  if (!out || (K > 0 && (!x || !w)) || (r > 0 && (!a || !b || !xa))) return fail(CT_ERR_ARG, "ct_forward_linear: null pointer");
+  if (!out || (K > 0 && (!x || !w)) || (r > 0 && (!b || !xa))) return fail(CT_ERR_ARG, "ct_forward_linear: null pointer");
   if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_forward_linear: dtype %d", dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (r > 0) {
+  if (r > 0 && a) {   // a == NULL: xa already holds x . a^T (computed for several projections at once)
     GemmArgs low = blank(T, r, dtype, xa, ld_xa, dtype);
     low.nseg = 1;
     low.seg[0] = segment(x, ldx, 1, a, 1, K, K);
@@ -333,6 +343,23 @@ extern "C" int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy
   int rc = token_contraction(low, ld_low, x, ldx, da, r, K, T, add, dtype, workspace, path, s);
   if (rc != CT_OK) return rc;
   return token_contraction(dy, ld_dy, xa, ld_xa, db, N, r, T, add, dtype, workspace, path, s);
+}
+
+extern "C" int64_t ct_accumulate_workspace(int64_t rows, int64_t cols, int64_t T, int dtype, int path) {
+  if (dtype != CT_BF16 || path == CT_PATH_SIMT || T <= 0 || rows <= 0 || cols <= 0) return 0;
+  const int splits = gradient_splits(rows, cols, T);
+  return splits > 1 ? static_cast<int64_t>(splits) * rows * cols * static_cast<int64_t>(sizeof(float)) : 0;
+}
+
+extern "C" int ct_accumulate(const void* left, int64_t ld_left, const void* right, int64_t ld_right, float* out,
+                             int64_t rows, int64_t cols, int64_t T, int add, int dtype, void* workspace, int path,
+                             void* stream) {
+  if (rows < 0 || cols < 0 || T < 0) return fail(CT_ERR_ARG, "ct_accumulate: negative size");
+  if (rows == 0 || cols == 0) return CT_OK;
+  if (!out || (T > 0 && (!left || !right))) return fail(CT_ERR_ARG, "ct_accumulate: null pointer");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_accumulate: dtype %d", dtype);
+  return token_contraction(left, ld_left, right, ld_right, out, rows, cols, T, add, dtype, workspace, path,
+                           static_cast<cudaStream_t>(stream));
 }
 
 // ---- parameter gradients without any allocation ----------------------------------------------

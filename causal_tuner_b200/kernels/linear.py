@@ -26,13 +26,16 @@ from . import core_cuda
 
 # ---- tensor plumbing --------------------------------------------------------------------
 
-def cast(tensor, dtype):
-    """`tensor.to(dtype)` through ct_cast; returns the tensor itself when the dtype already matches."""
-    if tensor is None or tensor.dtype == dtype:
+def cast(tensor, dtype, out=None):
+    """`tensor.to(dtype)` through ct_cast; returns the tensor itself when the dtype already matches.
+    With `out` (contiguous, same shape) the values always land there."""
+    if tensor is None or (tensor.dtype == dtype and out is None):
         return tensor
     _lib.require_cuda(tensor)
     source = tensor.contiguous()
-    output = torch.empty(source.shape, device=source.device, dtype=dtype)
+    if out is not None and (out.shape != source.shape or out.dtype != dtype or not out.is_contiguous()):
+        raise ValueError("cast destination must be contiguous with the source's shape")
+    output = torch.empty(source.shape, device=source.device, dtype=dtype) if out is None else out
     count = source.numel()
     if count:
         with _lib.on_device(source):
@@ -187,6 +190,60 @@ def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
             _lib.code_of(dx.dtype), _lib.gemm_path, _lib.stream_of(dx)))
 
 
+def stack_adapters(matrices, dtype):
+    """Row-wise stack of the `a` matrices of projections that share their input, cast to `dtype`,
+    and the row offset of each: one product x @ stack.T then yields every projection's low-rank
+    input as a column slice, reading x once."""
+    total = sum(m.shape[0] for m in matrices)
+    stacked = torch.empty((total, matrices[0].shape[1]), device=matrices[0].device, dtype=dtype)
+    offsets, cursor = [], 0
+    for matrix in matrices:
+        cast(matrix, dtype, out=stacked[cursor:cursor + matrix.shape[0]])
+        offsets.append(cursor)
+        cursor += matrix.shape[0]
+    return stacked, offsets
+
+
+def apply_projection(x, weight, b, xa, *, out, bias=None, residual=None):
+    """`forward_linear` with the low-rank input xa = x @ a.T already computed (a column slice of a
+    stacked product): out = x @ weight.T + bias + xa @ b.T [+ residual]."""
+    _lib.require_cuda(x, weight, out, xa)
+    x, weight, xa = _readable(x), _readable(weight), _readable(xa)
+    _writable(out, "out")
+    b = b.contiguous()
+    rows, inner = x.shape
+    if residual is not None:
+        residual = _readable(residual)
+    with _lib.on_device(x):
+        _lib.check(_lib.load().ct_forward_linear(
+            x.data_ptr(), _leading(x), weight.data_ptr(), _leading(weight), None, b.data_ptr(), _lib.pointer(bias),
+            _lib.pointer(residual), _leading(residual) if residual is not None else 0, out.data_ptr(), _leading(out),
+            xa.data_ptr(), _leading(xa), rows, inner, weight.shape[0], b.shape[1], _lib.code_of(x.dtype),
+            _lib.gemm_path, _lib.stream_of(x)))
+
+
+def token_gradient(left, right, out, *, add=False):
+    """out (+)= left.T @ right in fp32, contracted over the shared token dimension in the fixed slice
+    order of `parameter_gradients` (kernels/linear.py:16-24 as called at :42-44). `left` may hold the
+    low matrices of several projections side by side; `out` is then their stacked dA."""
+    _lib.require_cuda(left, right, out)
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise ValueError("token_gradient writes a contiguous fp32 matrix")
+    left, right = _readable(left), _readable(right)
+    tokens, rows = left.shape
+    cols = right.shape[1]
+    if right.shape[0] != tokens or out.shape != (rows, cols):
+        raise ValueError("token_gradient shape mismatch")
+    library = _lib.load()
+    code = _lib.code_of(left.dtype)
+    need = library.ct_accumulate_workspace(rows, cols, tokens, code, _lib.gemm_path)
+    workspace = torch.empty(need, device=left.device, dtype=torch.uint8) if need else None
+    with _lib.on_device(left):
+        _lib.check(library.ct_accumulate(left.data_ptr(), _leading(left), right.data_ptr(), _leading(right),
+                                         out.data_ptr(), rows, cols, tokens, int(bool(add)), code,
+                                         _lib.pointer(workspace), _lib.gemm_path, _lib.stream_of(left)))
+
+
 def parameter_gradients(x, dy, da, db, low, xa, *, add):
     """da (+)= low.T @ x and db (+)= dy.T @ xa in fp32 (kernels/linear.py:42-44), summed in a fixed order."""
     _lib.require_cuda(x, dy, da, db, low, xa)
@@ -250,9 +307,23 @@ class _LoRAGroup(torch.autograd.Function):
         fuse_residual = residual is not None and not head_dim
         shortcut = residual.reshape(rows, residual.shape[-1]) if fuse_residual else None
         outputs = []
+        stacked = len(states) > 1 and step >= rows > 0
+        if stacked:
+            # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x.
+            a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
+            xa_all = torch.empty((rows, a_all.shape[0]), device=x.device, dtype=dtype)
+            matmul(flat, a_all.T, out=xa_all)
+            del a_all
         for index, state in enumerate(states):
             weight, a, b, bias = parameters[4 * index:4 * index + 4]
             matrix = materialize(weight, state, dtype)
+            if stacked:
+                out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
+                apply_projection(flat, matrix, cast(b, dtype), xa_all[:, offsets[index]:offsets[index] + a.shape[0]],
+                                 out=out, bias=cast(bias, dtype))
+                outputs.append(out.reshape(*x.shape[:-1], matrix.shape[0]))
+                del matrix
+                continue
             a16, b16, bias16 = cast(a, dtype), cast(b, dtype), cast(bias, dtype)
             out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
             for start in range(0, rows, step):
@@ -289,22 +360,32 @@ class _LoRAGroup(torch.autograd.Function):
         if want_dx and len(states) > 1 and step >= rows > 0:
             # Untiled group (q/k/v): one GEMM sums the input gradients of all projections.
             prepared = []
+            a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
+            total = a_all.shape[0]
+            low_all = torch.empty((rows, total), device=x.device, dtype=dtype)
             for index, (state, grad) in enumerate(zip(states, grad_outputs)):
                 weight, a, b, _ = parameters[4 * index:4 * index + 4]
                 signal = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
                 if ctx.head_dim and index < 2:
                     signal = core_cuda.inverse_rope_tile(signal, cosine, sine, ctx.head_dim, torch.empty_like(signal))
-                prepared.append((materialize(weight, state, dtype), cast(a, dtype), cast(b, dtype), signal,
-                                 torch.empty((rows, a.shape[0]), device=x.device, dtype=dtype)))
+                span = slice(offsets[index], offsets[index] + a.shape[0])
+                prepared.append((materialize(weight, state, dtype), a_all[span], cast(b, dtype), signal,
+                                 low_all[:, span]))
             input_gradient_group([p[3] for p in prepared], [p[0] for p in prepared], [p[1] for p in prepared],
                                  [p[2] for p in prepared], dx, [p[4] for p in prepared])
+            # One product recomputes every projection's low-rank input, one more gives the stacked dA
+            # (each reads x once); dB is per projection.
+            xa_all = torch.empty((rows, total), device=x.device, dtype=dtype)
+            matmul(flat, a_all.T, out=xa_all)
+            da_all = torch.empty((total, flat.shape[1]), device=x.device, dtype=torch.float32)
+            token_gradient(low_all, flat, da_all)
             for index, (matrix, a16, b16, signal, low) in enumerate(prepared):
                 a, b = parameters[4 * index + 1], parameters[4 * index + 2]
-                da, db = torch.empty_like(a), torch.empty_like(b)
-                xa = workspace[1, :rows, :a.shape[0]]
-                matmul(flat, a16.T, out=xa)
-                parameter_gradients(flat, signal, da, db, low, xa, add=False)
-                results.extend((None, da, db, None))
+                span = slice(offsets[index], offsets[index] + a.shape[0])
+                da, db = da_all[span], torch.empty(b.shape, device=x.device, dtype=torch.float32)
+                token_gradient(signal, xa_all[:, span], db)
+                results.extend((None, da if a.dtype == torch.float32 else da.to(a.dtype),
+                                db if b.dtype == torch.float32 else db.to(b.dtype), None))
             del prepared
             residual_grad = grad_outputs[0] if ctx.needs_input_grad[7] else None
             return (cast(dx.reshape(x.shape), x.dtype), None, None, None, None, None, None, residual_grad, *results)

@@ -10,8 +10,8 @@ and its in-place backward are ct_swiglu.
 import torch
 
 from .. import _lib
-from .linear import (cast, materialize, forward_linear, input_gradient, input_gradient_group, parameter_gradients,
-                     projection_parameters, matmul)
+from .linear import (apply_projection, cast, materialize, forward_linear, input_gradient, input_gradient_group,
+                     parameter_gradients, projection_parameters, matmul, stack_adapters, token_gradient)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -65,9 +65,14 @@ def silu_multiply(gate, up):
 
 
 def _prepare(parameters, states, dtype):
+    """Decoded base weights, cast adapters, and the gate/up `a` matrices stacked row-wise (their
+    low-rank inputs come from one product over x)."""
     matrices = [materialize(parameters[4 * i], state, dtype) for i, state in enumerate(states)]
-    adapters = [(cast(parameters[4 * i + 1], dtype), cast(parameters[4 * i + 2], dtype)) for i in range(3)]
-    return matrices, adapters
+    stacked, offsets = stack_adapters([parameters[1], parameters[5]], dtype)
+    ranks = [parameters[1].shape[0], parameters[5].shape[0]]
+    adapters = [(stacked[offsets[i]:offsets[i] + ranks[i]], cast(parameters[4 * i + 2], dtype)) for i in range(2)]
+    adapters.append((cast(parameters[9], dtype), cast(parameters[10], dtype)))
+    return matrices, adapters, stacked
 
 
 @torch.no_grad()
@@ -79,16 +84,19 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
     """
     flat = cast(x.reshape(-1, x.shape[-1]), dtype)
     rows = flat.shape[0]
-    matrices, adapters = _prepare(parameters, states, dtype)
+    matrices, adapters, stacked = _prepare(parameters, states, dtype)
     width = matrices[0].shape[0]
+    ranks = [a.shape[0] for a, _ in adapters]
     step = max(1, min(tile, rows))
     held = min(step, rows)
     workspace = torch.empty((1 if save else 2, held, width), device=x.device, dtype=dtype)
-    low = torch.empty((held, max(a.shape[0] for a, _ in adapters)), device=x.device, dtype=dtype)
+    low = torch.empty((held, stacked.shape[0]), device=x.device, dtype=dtype)
+    low_down = torch.empty((held, ranks[2]), device=x.device, dtype=dtype)
     saved = ()
     if save:
+        kept = torch.empty((rows, stacked.shape[0]), device=x.device, dtype=dtype)   # [xa_gate | xa_up]
         saved = (*(torch.empty((rows, width), device=x.device, dtype=dtype) for _ in range(2)),
-                 *(torch.empty((rows, a.shape[0]), device=x.device, dtype=dtype) for a, _ in adapters[:2]))
+                 kept[:, :ranks[0]], kept[:, ranks[0]:])
     destination = output.view(rows, output.shape[-1])
     shortcut = None if residual is None else residual.reshape(rows, residual.shape[-1])
     for start in range(0, rows, step):
@@ -96,14 +104,15 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
         part, count = flat[start:stop], stop - start
         if save:
             gate, up = saved[0][start:stop], saved[1][start:stop]
-            xa = [saved[2][start:stop], saved[3][start:stop], low[:count, :adapters[2][0].shape[0]]]
+            both = kept[start:stop]
         else:
             gate, up = workspace[0, :count], workspace[1, :count]
-            xa = [low[:count, :a.shape[0]] for a, _ in adapters]
-        forward_linear(part, matrices[0], *adapters[0], out=gate, xa=xa[0])
-        forward_linear(part, matrices[1], *adapters[1], out=up, xa=xa[1])
+            both = low[:count]
+        matmul(part, stacked.T, out=both)           # low-rank inputs of gate and up, reading x once
+        apply_projection(part, matrices[0], adapters[0][1], both[:, :ranks[0]], out=gate)
+        apply_projection(part, matrices[1], adapters[1][1], both[:, ranks[0]:], out=up)
         hidden = activation(gate, up, out=workspace[0, :count] if save else gate)
-        forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop], xa=xa[2],
+        forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop], xa=low_down[:count],
                        residual=None if shortcut is None else shortcut[start:stop])
     return saved
 
@@ -138,27 +147,35 @@ class _TiledLoRAMLP(torch.autograd.Function):
         upstream = cast(grad.reshape(rows, grad.shape[-1]), dtype).contiguous()
         want_dx = ctx.needs_input_grad[0]
         dx = torch.empty_like(flat) if want_dx else None
-        matrices, adapters = _prepare(parameters, ctx.states, dtype)
-        make = torch.empty_like if rows else torch.zeros_like
-        gradients = [(make(parameters[4 * i + 1]), make(parameters[4 * i + 2])) for i in range(3)]
+        matrices, adapters, stacked = _prepare(parameters, ctx.states, dtype)
+        ranks = [a.shape[0] for a, _ in adapters]
+        make = torch.empty if rows else torch.zeros
+        wide = dict(device=x.device, dtype=torch.float32)
+        # fp32 accumulators: d(a_gate) and d(a_up) stacked (one product over x yields both), the rest apart
+        da_both = make((stacked.shape[0], flat.shape[1]), **wide)
+        da_down = make(parameters[9].shape, **wide)
+        db = [make(parameters[4 * i + 2].shape, **wide) for i in range(3)]
         step = max(1, min(ctx.tile, rows))
         held = min(step, rows)
         width = matrices[0].shape[0]
         workspace = torch.empty((3, held, width), device=x.device, dtype=dtype)
-        low_inputs = [torch.empty((held, a.shape[0]), device=x.device, dtype=dtype) for a, _ in adapters]
-        low_grad = torch.empty((3, held, max(a.shape[0] for a, _ in adapters)), device=x.device, dtype=dtype)
+        xa_both = torch.empty((held, stacked.shape[0]), device=x.device, dtype=dtype)
+        xa_down = torch.empty((held, ranks[2]), device=x.device, dtype=dtype)
+        low_both = torch.empty((held, stacked.shape[0]), device=x.device, dtype=dtype)
+        low_down = torch.empty((held, ranks[2]), device=x.device, dtype=dtype)
         for start in range(0, rows, step):
             stop = min(start + step, rows)
             count = stop - start
             part, dy = flat[start:stop], upstream[start:stop]
             gate, up, dh = workspace[0, :count], workspace[1, :count], workspace[2, :count]
-            xa = [buffer[:count] for buffer in low_inputs]
-            low = [low_grad[i, :count, :a.shape[0]] for i, (a, _) in enumerate(adapters)]
+            low = [low_both[:count, :ranks[0]], low_both[:count, ranks[0]:], low_down[:count]]
             if ctx.cache:
-                xa[0], xa[1] = saved[2][start:stop], saved[3][start:stop]
+                xa = [saved[2][start:stop], saved[3][start:stop]]
             else:
-                forward_linear(part, matrices[0], *adapters[0], out=gate, xa=xa[0])
-                forward_linear(part, matrices[1], *adapters[1], out=up, xa=xa[1])
+                matmul(part, stacked.T, out=xa_both[:count])
+                xa = [xa_both[:count, :ranks[0]], xa_both[:count, ranks[0]:]]
+                apply_projection(part, matrices[0], adapters[0][1], xa[0], out=gate)
+                apply_projection(part, matrices[1], adapters[1][1], xa[1], out=up)
             input_gradient(dy, matrices[2], *adapters[2], dh, low[2])
             if ctx.cache:
                 # Read the saved gate/up, write (d_gate, d_up, hidden) into the tile buffers: the saved
@@ -167,17 +184,22 @@ class _TiledLoRAMLP(torch.autograd.Function):
                 hidden = dh
             else:
                 hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
-            matmul(hidden, adapters[2][0].T, out=xa[2])
-            parameter_gradients(hidden, dy, *gradients[2], low[2], xa[2], add=start > 0)
+            matmul(hidden, adapters[2][0].T, out=xa_down[:count])
+            parameter_gradients(hidden, dy, da_down, db[2], low[2], xa_down[:count], add=start > 0)
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
                 input_gradient_group((gate, up), matrices[:2], [adapters[0][0], adapters[1][0]],
                                      [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
-            for index, signal in enumerate((gate, up)):
-                if not want_dx:
+            else:
+                for index, signal in enumerate((gate, up)):
                     matmul(signal, adapters[index][1], out=low[index])
-                parameter_gradients(part, signal, *gradients[index], low[index], xa[index], add=start > 0)
-        result = [value for da, db in gradients for value in (None, da, db, None)]
+            token_gradient(low_both[:count], part, da_both, add=start > 0)
+            for index, signal in enumerate((gate, up)):
+                token_gradient(signal, xa[index], db[index], add=start > 0)
+        da = [da_both[:ranks[0]], da_both[ranks[0]:], da_down]
+        like = lambda value, parameter: value if parameter.dtype == torch.float32 else value.to(parameter.dtype)
+        result = [value for i in range(3)
+                  for value in (None, like(da[i], parameters[4 * i + 1]), like(db[i], parameters[4 * i + 2]), None)]
         dx_out = None if dx is None else cast(dx.reshape(x.shape), x.dtype)
         return (dx_out, None, None, None, residual_grad, None, *result)
 

@@ -135,7 +135,10 @@ CT_API int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* B, i
  * low-rank term enters the same accumulator as the base product (one GEMM over
  * the concatenated contraction [x | xa] . [w | b]^T), so `out` is rounded once
  * where the reference rounds after the base product and again after the
- * low-rank update. r may be 0 (a, b, xa ignored). */
+ * low-rank update. r may be 0 (a, b, xa ignored). With r > 0 and a == NULL, `xa`
+ * is an INPUT that already holds round(x @ a^T) - projections that share x compute
+ * their low-rank inputs in one stacked product (ct_matmul with the a matrices
+ * stacked row-wise) and pass column slices of the result (ld_xa = total rank). */
 CT_API int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw,
                       const void* a, const void* b, const void* bias,
                       const void* residual, int64_t ld_res, void* out, int64_t ld_out,
@@ -183,6 +186,20 @@ CT_API int ct_parameter_gradients(const void* x, int64_t ldx, const void* dy, in
                            int64_t ld_xa, float* da, float* db, int64_t T, int64_t K,
                            int64_t N, int64_t r, int add, int dtype, void* workspace,
                            int path, void* stream);
+
+/* ---- token-contracted fp32 accumulation ------------------------------------
+ * Replaces kernels/linear.py:16-24 (accumulate) as parameter_gradients uses it
+ * (kernels/linear.py:42-44, `accumulate(da, low.T, x)`):
+ *   out[rows, cols] = (add ? out : 0) + left^T @ right     fp32, out contiguous
+ * left[T, rows] (ld_left), right[T, cols] (ld_right) of `dtype`. Same fixed-order
+ * slicing of the contraction over T as ct_parameter_gradients, which is this call
+ * twice; with the low matrices of several projections stacked column-wise in
+ * `left`, one call yields their stacked dA. `workspace` holds
+ * ct_accumulate_workspace(...) bytes (NULL when that is 0). */
+CT_API int64_t ct_accumulate_workspace(int64_t rows, int64_t cols, int64_t T, int dtype, int path);
+CT_API int ct_accumulate(const void* left, int64_t ld_left, const void* right, int64_t ld_right,
+                         float* out, int64_t rows, int64_t cols, int64_t T, int add, int dtype,
+                         void* workspace, int path, void* stream);
 
 /* ---- LoRA parameter gradients for callers that must not allocate ---------------
  * No counterpart in the reference (its gradients go through torch's caching

@@ -125,3 +125,48 @@ def test_position_table_full_range(dtype):
     assert (cosine.float() - plain.cos().to(dtype).float()).abs().max() <= tolerance
     empty = position_values(positions[:, :0], inverse, dtype)
     assert empty[0].shape == (2, 0, 32)
+
+
+def test_owned_rotary_beyond_512k_rows():
+    # One token more than 2^19: exercises the tail after 65,536 position tiles (the reference checks the same
+    # size); every token and head is compared with a bounded plain-PyTorch bf16 expression.
+    rows, head_dim, rotary_dim = 524289, 128, 64
+    query = torch.randn(rows, 3 * head_dim, device="cuda", dtype=torch.bfloat16)
+    key = torch.randn(rows, head_dim, device="cuda", dtype=torch.bfloat16)
+    original = (query.clone(), key.clone())
+    angles = torch.randn(rows, rotary_dim // 2, device="cuda")
+    cosine, sine = angles.cos().bfloat16(), angles.sin().bfloat16()
+    core_cuda.rotate_owned_qk(query, key, cosine, sine, head_dim)
+    for actual, raw in zip((query, key), original):
+        for start in range(0, rows, 65536):
+            source = raw[start:start + 65536].reshape(-1, raw.shape[-1] // head_dim, head_dim)
+            expected = source.clone()
+            c, s = cosine[start:start + 65536, None], sine[start:start + 65536, None]
+            even, odd = source[..., :rotary_dim:2], source[..., 1:rotary_dim:2]
+            expected[..., :rotary_dim:2] = even * c - odd * s
+            expected[..., 1:rotary_dim:2] = odd * c + even * s
+            assert torch.equal(actual[start:start + 65536].reshape_as(expected), expected)
+
+
+def test_swiglu_and_add_index_past_two_to_the_31():
+    # 2^31 + 4104 bf16 elements per buffer (4.3 GB each): element offsets no longer fit 32 bits.
+    total = (1 << 31) + 4104
+    gate = torch.empty(total, device="cuda", dtype=torch.bfloat16)
+    up = torch.empty_like(gate)
+    for buffer, seed in ((gate, 1), (up, 2)):
+        generator = torch.Generator(device="cuda").manual_seed(seed)
+        pattern = torch.randn(1 << 20, device="cuda", generator=generator).bfloat16()
+        buffer.view(-1)[:(total // pattern.numel()) * pattern.numel()].view(-1, pattern.numel()).copy_(pattern)
+        buffer[(total // pattern.numel()) * pattern.numel():] = pattern[:total % pattern.numel()]
+    hidden = mlp_cuda.activation(gate.view(1, -1), up.view(1, -1)).view(-1)
+    for start in (0, (1 << 31) - 2048, total - 4096):
+        g, u = gate[start:start + 4096].float(), up[start:start + 4096].float()
+        expected = ((g * torch.sigmoid(g)).bfloat16().float() * u).bfloat16()
+        assert (hidden[start:start + 4096].float() - expected.float()).abs().max() <= 0.02 * expected.float().abs().max()
+    assert bool((hidden[-8:] != 0).any())
+    tail = slice(total - 4096, total)
+    before = hidden[tail].clone()
+    linear._add_inplace(hidden, up)
+    assert torch.equal(hidden[tail], (before.float() + up[tail].float()).bfloat16())
+    del gate, up, hidden
+    torch.cuda.empty_cache()

@@ -130,7 +130,7 @@ def test_input_gradient_and_parameter_gradients(path, rows, inner, outer, rank):
 
 def test_split_contraction_matches_single_pass_and_is_repeatable(monkeypatch):
     # rank-16 adapter over 4096 tokens: dA has a single output tile, so the token contraction is
-    # cut into 8 slices that are summed in slice order.
+    # cut into several slices that are summed in slice order.
     monkeypatch.setattr(_lib, "gemm_path", _lib.PATH_TCGEN05)
     rows, inner, outer, rank = 4096, 256, 512, 16
     assert _lib.load().ct_parameter_gradients_workspace(rows, inner, outer, rank, _lib.BF16, _lib.PATH_TCGEN05) > 0
