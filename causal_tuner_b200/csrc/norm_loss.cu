@@ -80,8 +80,28 @@ rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, T* g
   }
 }
 
-// 16-bit activations, width % 8 == 0, 16-byte aligned rows: the same arithmetic with 16-byte loads and
-// stores (the second pass over the 8 KB row is served by L1).
+// 16-bit activations, width % 8 == 0, 16-byte aligned rows and weights: the same arithmetic with 16-byte loads and
+// stores. Rows of up to kHeld * kThreads chunks (4096 elements) stay in registers between the two
+// passes, and all of a thread's loads are issued before the first use; longer rows are read again
+// (from L1).
+constexpr int kHeld = 2;
+
+// Eight consecutive weights, rounded to the activation type T, from one or two 16-byte loads.
+template <typename T, typename W>
+__device__ __forceinline__ void load_weights(const W* w, int64_t c, float (&out)[8]) {
+  if constexpr (sizeof(W) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(w + c * 8);
+    const W* v = reinterpret_cast<const W*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = round_to<T>(to_float<W>(v[j]));
+  } else {
+    const float4 lo = *reinterpret_cast<const float4*>(w + c * 8), hi = *reinterpret_cast<const float4*>(w + c * 8 + 4);
+    const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = round_to<T>(v[j]);
+  }
+}
+
 template <typename T, typename W>
 __global__ void __launch_bounds__(kThreads)
 rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width, float eps) {
@@ -89,30 +109,52 @@ rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width,
   const int64_t row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * width);
   const int64_t chunks = width / 8;
+  const bool held = chunks <= kHeld * kThreads;
+  uint4 kept[kHeld];
   float sum = 0.f;
-  for (int64_t c = threadIdx.x; c < chunks; c += kThreads) {
-    const uint4 raw = xr[c];
+  auto square = [&](const uint4& raw) {
     const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float f = to_float<T>(v[j]);
       sum += f * f;
     }
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int64_t c = threadIdx.x + i * kThreads;
+      kept[i] = c < chunks ? xr[c] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) square(kept[i]);
+  } else {
+    for (int64_t c = threadIdx.x; c < chunks; c += kThreads) square(xr[c]);
   }
   const float inverse = rsqrtf(block_sum(sum, scratch) / static_cast<float>(width) + eps);
   if (threadIdx.x == 0) rstd[row] = inverse;
   uint4* yr = reinterpret_cast<uint4*>(y + row * width);
-  for (int64_t c = threadIdx.x; c < chunks; c += kThreads) {
-    const uint4 raw = xr[c];
+  auto emit = [&](const uint4& raw, int64_t c) {
     const T* v = reinterpret_cast<const T*>(&raw);
     uint4 out;
     T* o = reinterpret_cast<T*>(&out);
+    float weight[8];
+    load_weights<T, W>(w, c, weight);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float normalized = round_to<T>(to_float<T>(v[j]) * inverse);
-      o[j] = from_float<T>(normalized * round_to<T>(to_float<W>(w[c * 8 + j])));
+      o[j] = from_float<T>(normalized * weight[j]);
     }
     yr[c] = out;
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int64_t c = threadIdx.x + i * kThreads;
+      if (c < chunks) emit(kept[i], c);
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < chunks; c += kThreads) emit(xr[c], c);
   }
 }
 
@@ -124,31 +166,58 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * width);
   const uint4* gr = reinterpret_cast<const uint4*>(go + row * width);
   const int64_t chunks = width / 8;
+  const bool held = chunks <= kHeld * kThreads;
+  uint4 kept_x[kHeld], kept_g[kHeld];
   float sum = 0.f;
-  for (int64_t c = threadIdx.x; c < chunks; c += kThreads) {
-    const uint4 xraw = xr[c], graw = gr[c];
+  auto project = [&](const uint4& xraw, const uint4& graw, int64_t c) {
     const T* xv = reinterpret_cast<const T*>(&xraw);
     const T* gv = reinterpret_cast<const T*>(&graw);
+    float weight[8];
+    load_weights<T, W>(w, c, weight);
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      sum += round_to<T>(to_float<T>(gv[j]) * round_to<T>(to_float<W>(w[c * 8 + j]))) * to_float<T>(xv[j]);
+    for (int j = 0; j < 8; ++j) sum += round_to<T>(to_float<T>(gv[j]) * weight[j]) * to_float<T>(xv[j]);
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int64_t c = threadIdx.x + i * kThreads;
+      kept_x[i] = c < chunks ? xr[c] : make_uint4(0, 0, 0, 0);
+      kept_g[i] = c < chunks ? gr[c] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int64_t c = threadIdx.x + i * kThreads;
+      if (c < chunks) project(kept_x[i], kept_g[i], c);
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < chunks; c += kThreads) project(xr[c], gr[c], c);
   }
   const float projection = block_sum(sum, scratch) / static_cast<float>(width);
   const float inverse = rstd[row];
   const float factor = inverse * inverse * projection;
   uint4* out = reinterpret_cast<uint4*>(gx + row * width);
-  for (int64_t c = threadIdx.x; c < chunks; c += kThreads) {
-    const uint4 xraw = xr[c], graw = gr[c];
+  auto emit = [&](const uint4& xraw, const uint4& graw, int64_t c) {
     const T* xv = reinterpret_cast<const T*>(&xraw);
     const T* gv = reinterpret_cast<const T*>(&graw);
     uint4 result;
     T* o = reinterpret_cast<T*>(&result);
+    float weight[8];
+    load_weights<T, W>(w, c, weight);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float gradient = round_to<T>(to_float<T>(gv[j]) * round_to<T>(to_float<W>(w[c * 8 + j])));
+      const float gradient = round_to<T>(to_float<T>(gv[j]) * weight[j]);
       o[j] = from_float<T>(inverse * (gradient - to_float<T>(xv[j]) * factor));
     }
     out[c] = result;
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int64_t c = threadIdx.x + i * kThreads;
+      if (c < chunks) emit(kept_x[i], kept_g[i], c);
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < chunks; c += kThreads) emit(xr[c], gr[c], c);
   }
 }
 
@@ -191,7 +260,7 @@ extern "C" int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* 
   if (!x || !w || !y || !rstd) return fail(CT_ERR_ARG, "ct_rmsnorm_forward: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(rows);
-  const bool vec = dtype == CT_BF16 && width % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const bool vec = dtype == CT_BF16 && width % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (vec && weight_dtype == CT_BF16) {
     rms_forward_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rstd, width, eps);
     count_launch(false);
@@ -221,7 +290,8 @@ extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rs
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(rows);
   const bool vec = dtype == CT_BF16 && width % 8 == 0 &&
-                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(gx)) & 15) == 0;
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(gx) |
+                     reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (vec && weight_dtype == CT_BF16) {
     rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<__nv_bfloat16*>(gx), width);
     count_launch(false);
