@@ -471,7 +471,7 @@ def run_step(args):
     # The same update with every layer recomputing its MLP activations in backward (no cache budget):
     # the low-memory end of the policy, reported beside the headline so that both are on record.
     recompute = None
-    if args.mlp_cache_gib and model.last_execution.get("mlp_cache_layers"):
+    if args.mlp_cache_gib and model.last_execution.get("mlp_cache_layers") and not args.no_recompute_arm:
         execution = dict(model.last_execution)
         model.runtime.mlp_cache_budget_bytes = None
         torch.cuda.reset_peak_memory_stats(device)
@@ -525,6 +525,8 @@ def main():
                         help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
+    parser.add_argument("--no-recompute-arm", action="store_true",
+                        help="skip the second measurement with every MLP recomputing its activations (profiler captures)")
     parser.add_argument("--mlp-cache-gib", type=float, default=64.0,
                         help="per-GPU byte budget for keeping MLP gate/up activations instead of recomputing them "
                              "(0: always recompute)")
