@@ -380,16 +380,23 @@ def finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, 
 STEP_METRIC = "train tokens/s (NF4 r256 LoRA, MQA decoder, one optimizer update)"
 
 
-def step_config(name, gpus, mlp_cache_gib=0, execution=None):
+def step_config(name, gpus, mlp_cache_gib=0, execution=None, keep_low_rank=False):
     import bench_step
     spec = bench_step.WORKLOADS[name]
-    cached = (execution or {}).get("mlp_cache_layers", 0)
+    config = spec["config"]
+    per_layer = spec["rows"] * spec["length"] * 2 * (2 * config["intermediate_size"] + 2 * bench_step.RANK)
+    planned = min(config["num_hidden_layers"], int(mlp_cache_gib * 2**30) // per_layer)   # MLP.cache_bytes per layer
+    cached = planned if execution is None else execution.get("mlp_cache_layers", 0)
+    kept_mb = 4 * bench_step.RANK * 2 * spec["rows"] * spec["length"] / 1e6
     return {"workload": f"{name} ({spec['reference']})", **spec["config"], "rank": bench_step.RANK,
             "rows_per_gpu": spec["rows"], "seq_len": spec["length"], "global_batch": spec["rows"] * gpus,
             "nf4_blocksize": 64, "absmax": "fp32", "attention": "flash_attention_2 (library, as in the reference)",
             "activation_checkpointing": False,
             "mlp": (f"gate/up kept for backward in {cached} layers ({mlp_cache_gib} GiB budget, last layers first), "
-                    f"recomputed in backward in the others"), "parallelism": f"dp{gpus}",
+                    f"recomputed in backward in the others"),
+            "low_rank_inputs": (f"x.A^T of q/k/v/o kept for backward ({kept_mb:.1f} MB per layer)" if keep_low_rank
+                                else "recomputed in backward (as the reference does)"),
+            "parallelism": f"dp{gpus}",
             "l2": "per-layer operands (>= 134 MB activations + 117 MB decoded weight) exceed the 126 MB L2"}
 
 
@@ -403,7 +410,8 @@ def run_step_reference(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1000.0 * bench_step.CPU_SAMPLE_TOKENS / estimate["value"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": step_config(args.workload, args.gpus), "cpu_baseline": estimate,
+            "config": step_config(args.workload, args.gpus, args.mlp_cache_gib, None, bool(args.keep_low_rank)),
+            "cpu_baseline": estimate,
             "e2e": {"value": estimate["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -427,7 +435,7 @@ def run_step(args):
         dist.init_process_group("nccl", device_id=device)
     _lib.load()
     spec = bench_step.WORKLOADS[args.workload]
-    model = bench_step.build_model(args.workload, device, args.mlp_cache_gib)
+    model = bench_step.build_model(args.workload, device, args.mlp_cache_gib, keep_low_rank=bool(args.keep_low_rank))
     optimizer = make_optimizer(model, learning_rate=2e-5)
     trainer = Trainer(model, optimizer, device=device, loss_token_budget=4096)
     host_batch = bench_step.synthetic_batch(spec["rows"], spec["length"], spec["config"]["vocab_size"], seed=1000 + rank)
@@ -474,6 +482,9 @@ def run_step(args):
     if args.mlp_cache_gib and model.last_execution.get("mlp_cache_layers") and not args.no_recompute_arm:
         execution = dict(model.last_execution)
         model.runtime.mlp_cache_budget_bytes = None
+        for module in model.modules():
+            if hasattr(module, "keep_low_rank"):
+                module.keep_low_rank = False       # the reference's policy: nothing kept beyond x and the parameters
         torch.cuda.reset_peak_memory_stats(device)
         trainer.update([device_batch])
         recompute_ms, _ = timed(device_batch, max(2, min(args.steps, 3)))
@@ -494,7 +505,8 @@ def run_step(args):
         "metric": STEP_METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world_size,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": step_config(args.workload, world_size, args.mlp_cache_gib, model.last_execution),
+        "config": step_config(args.workload, world_size, args.mlp_cache_gib, model.last_execution,
+                              bool(args.keep_low_rank)),
         "step_tflops_per_gpu": flops / (ms_per_step * 1e-3) / 1e12,
         "step_frac_of_bf16_peak": flops / (ms_per_step * 1e-3) / 1e12 / peak,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -525,6 +537,8 @@ def main():
                         help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
+    parser.add_argument("--keep-low-rank", type=int, choices=(0, 1), default=1,
+                        help="step workloads: keep x.A^T of q/k/v/o for backward (1) or recompute it as the reference does (0)")
     parser.add_argument("--no-recompute-arm", action="store_true",
                         help="skip the second measurement with every MLP recomputing its activations (profiler captures)")
     parser.add_argument("--mlp-cache-gib", type=float, default=64.0,

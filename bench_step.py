@@ -51,13 +51,13 @@ def synthetic_batch(rows, length, vocab, seed):
     return {"input_ids": ids, "attention_mask": torch.ones_like(ids), "segment_ids": segments}
 
 
-def build_model(name, device, mlp_cache_gib=0):
+def build_model(name, device, mlp_cache_gib=0, keep_low_rank=False):
     from causal_tuner_b200.modeling.config import ModelConfig
     from causal_tuner_b200.modeling.model import CausalLM, Runtime
     spec = WORKLOADS[name]
     torch.manual_seed(2024)   # identical replica on every rank
     runtime = Runtime(rank=RANK, checkpoint=False, attention="flash_attention_2",
-                      mlp_cache_budget_bytes=int(mlp_cache_gib * 2**30) or None)
+                      mlp_cache_budget_bytes=int(mlp_cache_gib * 2**30) or None, keep_low_rank=keep_low_rank)
     model = CausalLM(ModelConfig(**spec["config"]), runtime, device)
     with torch.no_grad():
         model.model.embed_tokens.weight.normal_(std=.02)

@@ -18,6 +18,8 @@ dtype once per GEMM (the reference rounds after the base product and again after
 low-rank update), and `tile` only bounds workspaces - tile 0 runs all rows in one launch.
 """
 
+import threading
+
 import torch
 
 from .. import _lib
@@ -284,6 +286,11 @@ def can_fuse(module, x):
                 and module.lora_A.requires_grad and module.lora_B.requires_grad)
 
 
+# Set by project_group around the call: the operator's positional signature mirrors the reference's
+# and has no slot for this library's own execution option.
+_policy = threading.local()
+
+
 class _LoRAGroup(torch.autograd.Function):
     """One to three projections that share their input (q/k/v, or a single o/gate/up/down).
 
@@ -308,12 +315,19 @@ class _LoRAGroup(torch.autograd.Function):
         shortcut = residual.reshape(rows, residual.shape[-1]) if fuse_residual else None
         outputs = []
         stacked = len(states) > 1 and step >= rows > 0
+        keep = bool(getattr(_policy, "keep_low_rank", False)) and step >= rows > 0
+        ctx.low_rank = None
         if stacked:
             # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x.
             a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
             xa_all = torch.empty((rows, a_all.shape[0]), device=x.device, dtype=dtype)
             matmul(flat, a_all.T, out=xa_all)
             del a_all
+            if keep:
+                ctx.low_rank = xa_all
+        elif keep:
+            workspace = torch.empty((rows, widest), device=x.device, dtype=dtype)   # its own buffer: it outlives the call
+            ctx.low_rank = workspace[:, :parameters[1].shape[0]]
         for index, state in enumerate(states):
             weight, a, b, bias = parameters[4 * index:4 * index + 4]
             matrix = materialize(weight, state, dtype)
@@ -375,8 +389,10 @@ class _LoRAGroup(torch.autograd.Function):
                                  [p[2] for p in prepared], dx, [p[4] for p in prepared])
             # One product recomputes every projection's low-rank input, one more gives the stacked dA
             # (each reads x once); dB is per projection.
-            xa_all = torch.empty((rows, total), device=x.device, dtype=dtype)
-            matmul(flat, a_all.T, out=xa_all)
+            xa_all = ctx.low_rank
+            if xa_all is None:
+                xa_all = torch.empty((rows, total), device=x.device, dtype=dtype)
+                matmul(flat, a_all.T, out=xa_all)
             da_all = torch.empty((total, flat.shape[1]), device=x.device, dtype=torch.float32)
             token_gradient(low_all, flat, da_all)
             for index, (matrix, a16, b16, signal, low) in enumerate(prepared):
@@ -410,7 +426,10 @@ class _LoRAGroup(torch.autograd.Function):
                     input_gradient(signal, matrix, a16, b16, dx[start:stop], low, add=index > 0)
                 else:
                     matmul(signal, b16, out=low)
-                matmul(flat[start:stop], a16.T, out=xa)
+                if ctx.low_rank is not None and len(states) == 1:
+                    xa = ctx.low_rank          # kept by the forward pass (untiled: one slice)
+                else:
+                    matmul(flat[start:stop], a16.T, out=xa)
                 parameter_gradients(flat[start:stop], signal, da, db, low, xa, add=start > 0)
             results.extend((None, da, db, None))
             del matrix, a16, b16, dy
@@ -448,5 +467,9 @@ def project_group(modules, x, tile=0, *, rotary=None, residual=None):
     cosine, sine, head_dim = (None, None, 0) if rotary is None else rotary
     if rotary is not None:
         cosine, sine = cosine.contiguous(), sine.contiguous()
-    return _LoRAGroup.apply(x, modules[0].compute_dtype, tile, tuple(states), cosine, sine, head_dim, residual,
-                            *parameters)
+    _policy.keep_low_rank = torch.is_grad_enabled() and all(getattr(module, "keep_low_rank", False) for module in modules)
+    try:
+        return _LoRAGroup.apply(x, modules[0].compute_dtype, tile, tuple(states), cosine, sine, head_dim, residual,
+                                *parameters)
+    finally:
+        _policy.keep_low_rank = False

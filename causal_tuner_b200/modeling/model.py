@@ -27,6 +27,9 @@ class Runtime:
     mlp_cache_budget_bytes: int | None = None
     attention_cache_budget_bytes: int | None = None
     projection_tile: int = 0
+    # Keep the low-rank inputs x @ A.T of q/k/v/o between forward and backward (2 bytes x rank per
+    # token and projection) instead of recomputing them; the reference always recomputes (False).
+    keep_low_rank: bool = False
     checkpoint: bool = True
     adaptive: bool = False
     group_size: int = 1
@@ -98,6 +101,8 @@ class Attention(nn.Module):
         self.k_proj = Projection(h, d, bias=True, **kwargs)
         self.v_proj = Projection(h, d, bias=True, **kwargs)
         self.o_proj = Projection(h, h, **kwargs)
+        for projection in (self.q_proj, self.k_proj, self.v_proj, self.o_proj):
+            projection.keep_low_rank = runtime.keep_low_rank
 
     def forward(self, x, cosine, sine, segments, spans, layout=None, *, residual=None):
         from ..kernels.attention import dense_attention, flash_dense

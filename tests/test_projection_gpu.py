@@ -268,3 +268,57 @@ def test_config2_full_size_nf4_projection():
         assert relative(left, right) < 2e-2, name
     for left, right in zip(grads, again):
         assert torch.equal(left, right)
+
+
+@pytest.mark.parametrize("ranks", [(8, 16, 8), (3, 5, 7), (256, 256, 256)])
+def test_untiled_group_shares_its_low_rank_products_and_may_keep_them(ranks):
+    # q/k/v on one input, all rows at once: stacked x.A^T and stacked dA. Keeping the low-rank inputs for
+    # backward changes what is retained, never a value; the tiled path (separate products) agrees within
+    # the accumulation-order tolerance of fp32.
+    inner = 64 if ranks[0] < 256 else 512
+    modules = [Projection(inner, out, bias=True, rank=rank, compute_dtype=torch.bfloat16, device="cuda")
+               for out, rank in zip((inner, 16, 16), ranks)]
+    for module in modules:
+        torch.nn.init.normal_(module.lora_B, std=.1)
+    x = torch.randn(3, 100, inner, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    parameters = [p for module in modules for p in (module.lora_A, module.lora_B)]
+
+    def run(tile, keep):
+        for module in modules:
+            module.keep_low_rank = keep
+        before = torch.cuda.memory_allocated()
+        outputs = project_group(modules, x, tile=tile)
+        retained = torch.cuda.memory_allocated() - before - sum(o.numel() * o.element_size() for o in outputs)
+        signals = [torch.full_like(o, .01) * (i + 1) for i, o in enumerate(outputs)]
+        first = torch.autograd.grad(outputs, (x, *parameters), signals, retain_graph=True)
+        again = torch.autograd.grad(outputs, (x, *parameters), signals)
+        assert all(torch.equal(a, b) for a, b in zip(first, again))
+        return outputs, first, retained
+
+    plain_out, plain_grads, plain_retained = run(0, False)
+    kept_out, kept_grads, kept_retained = run(0, True)
+    tiled_out, tiled_grads, _ = run(32, False)
+    assert all(torch.equal(a, b) for a, b in zip(plain_out, kept_out))
+    assert all(torch.equal(a, b) for a, b in zip(plain_grads, kept_grads))
+    assert kept_retained - plain_retained >= 300 * sum(ranks) * 2      # the stacked [rows, sum of ranks] bf16 block
+    assert all(torch.equal(a, b) for a, b in zip(plain_out, tiled_out))
+    for a, b in zip(plain_grads, tiled_grads):
+        assert relative(a, b) < (4e-3 if a.dtype == torch.bfloat16 else 1e-5)
+    assert all(g.dtype == torch.float32 for g in plain_grads[1:])
+
+
+def test_single_projection_may_keep_its_low_rank_input():
+    module = Projection(256, 128, rank=16, compute_dtype=torch.bfloat16, device="cuda")
+    torch.nn.init.normal_(module.lora_B, std=.1)
+    x = torch.randn(70, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    residual = torch.randn(70, 128, device="cuda", dtype=torch.bfloat16)
+    results = []
+    for keep in (False, True):
+        module.keep_low_rank = keep
+        out = project_group((module,), x, residual=residual)[0]
+        results.append((out, torch.autograd.grad(out, (x, module.lora_A, module.lora_B), torch.ones_like(out))))
+    assert torch.equal(results[0][0], results[1][0])
+    assert all(torch.equal(a, b) for a, b in zip(results[0][1], results[1][1]))
+    with torch.no_grad():            # nothing is kept when no graph is recorded
+        module.keep_low_rank = True
+        assert torch.equal(project_group((module,), x, residual=residual)[0], results[0][0])
