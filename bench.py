@@ -187,7 +187,7 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": name, "data": "synthetic",
-            "config": workload_config(args.gpus),
+            "config": workload_config(args.gpus, bool(args.keep_low_rank)),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": cpu_sample_text(name, args.steps)},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -195,9 +195,11 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(gpus):
+def workload_config(gpus, keep_low_rank=True):
     return {"workload": "projection_fwd_bwd_7b_gate (BASELINE.json configs[1])", "rows_per_gpu": ROWS, "in_features": INNER,
             "out_features": OUTER, "rank": RANK, "nf4_blocksize": 64, "absmax": "fp32",
+            "low_rank_input": ("x.A^T kept for backward" if keep_low_rank
+                               else "recomputed in backward (as the reference does)"),
             "parallelism": f"dp{gpus}", "l2": "inputs (134 MB X + 470 MB dY per step) are larger than the 126 MB L2"}
 
 
@@ -223,6 +225,7 @@ def run_ours(args):
     torch.manual_seed(2024)  # identical weights on every rank
     module = Projection(INNER, OUTER, rank=RANK, device=device)
     module.install_nf4(module.weight.detach().clone(), device, blocksize=64, nested=False)
+    module.keep_low_rank = bool(args.keep_low_rank)
     with torch.no_grad():
         module.lora_A.normal_(std=.02)
         module.lora_B.normal_(std=.01)
@@ -356,7 +359,7 @@ def finish(args, rank, world_size, distributed, ms_per_step, e2e_ms, e2e_steps, 
         "metric": METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world_size,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(world_size),
+        "config": workload_config(world_size, bool(args.keep_low_rank)),
         "step_tflops_per_gpu": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12,
         "step_frac_of_bf16_peak": projection_flops(ROWS) / (ms_per_step * 1e-3) / 1e12 / peak,
         "e2e": None if e2e_ms is None else {
@@ -538,7 +541,7 @@ def main():
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
     parser.add_argument("--keep-low-rank", type=int, choices=(0, 1), default=1,
-                        help="step workloads: keep x.A^T of q/k/v/o for backward (1) or recompute it as the reference does (0)")
+                        help="keep the low-rank inputs x.A^T (q/k/v/o in the step workloads) for backward (1) or recompute them as the reference does (0)")
     parser.add_argument("--no-recompute-arm", action="store_true",
                         help="skip the second measurement with every MLP recomputing its activations (profiler captures)")
     parser.add_argument("--mlp-cache-gib", type=float, default=64.0,
