@@ -59,9 +59,10 @@ rms_forward_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width, flo
 }
 
 // gx = rstd * (g - x * rstd^2 * mean(g * x)) with g = round(go * round(w)); gx may alias go.
+// With `add`: gx = round(gx) + add, the sum autograd would form when x also feeds a residual path.
 template <typename T, typename W>
 __global__ void __launch_bounds__(kThreads)
-rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, T* gx, int64_t width) {
+rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
   const int64_t row = blockIdx.x;
   const T* xr = x + row * width;
@@ -76,7 +77,9 @@ rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, T* g
   T* out = gx + row * width;
   for (int64_t c = threadIdx.x; c < width; c += kThreads) {
     const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
-    out[c] = from_float<T>(inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection)));
+    float value = inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection));
+    if (add) value = __fadd_rn(round_to<T>(value), to_float<T>(add[row * width + c]));
+    out[c] = from_float<T>(value);
   }
 }
 
@@ -160,7 +163,7 @@ rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width,
 
 template <typename T, typename W>
 __global__ void __launch_bounds__(kThreads)
-rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, T* gx, int64_t width) {
+rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
   const int64_t row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * width);
@@ -196,17 +199,22 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
   const float inverse = rstd[row];
   const float factor = inverse * inverse * projection;
   uint4* out = reinterpret_cast<uint4*>(gx + row * width);
+  const uint4* extra = add ? reinterpret_cast<const uint4*>(add + row * width) : nullptr;
   auto emit = [&](const uint4& xraw, const uint4& graw, int64_t c) {
     const T* xv = reinterpret_cast<const T*>(&xraw);
     const T* gv = reinterpret_cast<const T*>(&graw);
-    uint4 result;
+    uint4 result, other = make_uint4(0, 0, 0, 0);
+    if (extra) other = extra[c];
+    const T* av = reinterpret_cast<const T*>(&other);
     T* o = reinterpret_cast<T*>(&result);
     float weight[8];
     load_weights<T, W>(w, c, weight);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float gradient = round_to<T>(to_float<T>(gv[j]) * weight[j]);
-      o[j] = from_float<T>(inverse * (gradient - to_float<T>(xv[j]) * factor));
+      float value = inverse * (gradient - to_float<T>(xv[j]) * factor);
+      if (extra) value = __fadd_rn(round_to<T>(value), to_float<T>(av[j]));
+      o[j] = from_float<T>(value);
     }
     out[c] = result;
   };
@@ -282,8 +290,9 @@ extern "C" int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* 
   return check_launch("ct_rmsnorm_forward");
 }
 
-extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go, void* gx,
-                                   int64_t rows, int64_t width, int dtype, int weight_dtype, void* stream) {
+extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float* rstd, const void* go, const void* add,
+                                       void* gx, int64_t rows, int64_t width, int dtype, int weight_dtype,
+                                       void* stream) {
   if (rows < 0 || width <= 0) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: rows=%lld width=%lld", (long long)rows, (long long)width);
   if (rows == 0) return CT_OK;
   if (!x || !w || !rstd || !go || !gx) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: null pointer");
@@ -291,18 +300,18 @@ extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rs
   const unsigned grid = static_cast<unsigned>(rows);
   const bool vec = dtype == CT_BF16 && width % 8 == 0 &&
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(gx) |
-                     reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+                     reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(add)) & 15) == 0;
   if (vec && weight_dtype == CT_BF16) {
-    rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<__nv_bfloat16*>(gx), width);
+    rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
     count_launch(false);
     return check_launch("ct_rmsnorm_backward");
   }
   if (vec && weight_dtype == CT_F32) {
-    rms_backward_vec_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<__nv_bfloat16*>(gx), width);
+    rms_backward_vec_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
     count_launch(false);
     return check_launch("ct_rmsnorm_backward");
   }
-#define CT_RMS_BWD(T, W) rms_backward_kernel<T, W><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<const T*>(go), static_cast<T*>(gx), width)
+#define CT_RMS_BWD(T, W) rms_backward_kernel<T, W><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<const T*>(go), static_cast<const T*>(add), static_cast<T*>(gx), width)
   if (dtype == CT_BF16 && weight_dtype == CT_BF16) CT_RMS_BWD(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == CT_BF16 && weight_dtype == CT_F32) CT_RMS_BWD(__nv_bfloat16, float);
   else if (dtype == CT_F32 && weight_dtype == CT_F32) CT_RMS_BWD(float, float);
@@ -311,6 +320,11 @@ extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rs
 #undef CT_RMS_BWD
   count_launch(false);
   return check_launch("ct_rmsnorm_backward");
+}
+
+extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go, void* gx,
+                                   int64_t rows, int64_t width, int dtype, int weight_dtype, void* stream) {
+  return ct_rmsnorm_backward_add(x, w, rstd, go, nullptr, gx, rows, width, dtype, weight_dtype, stream);
 }
 
 extern "C" int ct_weighted_ce(void* logits, const int64_t* targets, const float* weights, float* loss, int64_t rows,

@@ -118,3 +118,52 @@ class RMS(torch.autograd.Function):
                 x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), result.data_ptr(),
                 x.numel() // width, width, _lib.code_of(x.dtype), _lib.code_of(weight.dtype), _lib.stream_of(x)))
         return result, None, None, None, None
+
+
+class RMSWithShortcut(torch.autograd.Function):
+    """(RMS(x), x) for a pre-norm residual block `x + block(RMS(x))`: the normalised activations and
+    the same x as the block's residual input (modeling/model.py:153-155 of the reference, where x
+    feeds both and autograd adds the two gradients with a separate kernel). Here the backward pass
+    receives both gradients and forms round(round(RMS gradient) + shortcut gradient) inside the
+    RMSNorm kernel, over the upstream gradient of the normalised branch, which the projection
+    operators hand over as a private tensor. Frozen weight only."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        _lib.require_cuda(x, weight)
+        if weight.requires_grad:
+            raise NotImplementedError("causal_tuner_b200 covers frozen RMSNorm weights (adapter training) only")
+        source = x.contiguous()
+        output = torch.empty_like(source)
+        width = source.shape[-1]
+        rows = source.numel() // width
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        weight = weight.contiguous()
+        with _lib.on_device(source):
+            _lib.check(_lib.load().ct_rmsnorm_forward(
+                source.data_ptr(), weight.data_ptr(), output.data_ptr(), rstd.data_ptr(), rows, width, float(eps),
+                _lib.code_of(source.dtype), _lib.code_of(weight.dtype), _lib.stream_of(source)))
+        ctx.save_for_backward(source, weight, rstd)
+        return output, x
+
+    @staticmethod
+    def backward(ctx, grad, shortcut_grad):
+        x, weight, rstd = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None, None
+        if grad is None:
+            return shortcut_grad, None, None
+        grad = grad.contiguous()
+        if grad.dtype != x.dtype:
+            grad = grad.to(x.dtype)
+        fused = shortcut_grad is not None and shortcut_grad.dtype == x.dtype and shortcut_grad.shape == x.shape
+        extra = shortcut_grad.contiguous() if fused else None
+        width = x.shape[-1]
+        with _lib.on_device(x):
+            _lib.check(_lib.load().ct_rmsnorm_backward_add(
+                x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), _lib.pointer(extra),
+                grad.data_ptr(), x.numel() // width, width, _lib.code_of(x.dtype), _lib.code_of(weight.dtype),
+                _lib.stream_of(x)))
+        if shortcut_grad is not None and not fused:
+            grad = grad + shortcut_grad
+        return grad, None, None

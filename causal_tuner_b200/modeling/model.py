@@ -89,6 +89,14 @@ class RMSNorm(nn.Module):
             raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
         return RMS.apply(x, self.weight, self.eps, reuse_grad, False)
 
+    def with_shortcut(self, x):
+        """(norm(x), x) for `x + block(norm(x))`; the two gradients of x are summed inside the norm's
+        backward kernel instead of by a separate add."""
+        from ..kernels.core_cuda import RMSWithShortcut
+        if not x.is_cuda:
+            raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
+        return RMSWithShortcut.apply(x, self.weight, self.eps)
+
 
 class Attention(nn.Module):
     def __init__(self, config, runtime, device):
@@ -130,9 +138,11 @@ class Layer(nn.Module):
 
     def forward(self, x, *args, mlp_tile=None, mlp_cache=None):
         # Both norms feed operators that return private input gradients, so the norm backward may
-        # write over its upstream gradient (reuse_grad).
-        x = self.self_attn(self.input_layernorm(x, reuse_grad=True), *args, residual=x)
-        return self.mlp(self.post_attention_layernorm(x, reuse_grad=True), residual=x, tile=mlp_tile, cache=mlp_cache)
+        # write over its upstream gradient, and it adds the residual path's gradient while it does.
+        normed, shortcut = self.input_layernorm.with_shortcut(x)
+        x = self.self_attn(normed, *args, residual=shortcut)
+        normed, shortcut = self.post_attention_layernorm.with_shortcut(x)
+        return self.mlp(normed, residual=shortcut, tile=mlp_tile, cache=mlp_cache)
 
 
 class Decoder(nn.Module):

@@ -279,6 +279,13 @@ CT_API int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* rstd
 CT_API int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go,
                                void* gx, int64_t rows, int64_t width, int dtype, int weight_dtype,
                                void* stream);
+/* The same input gradient plus the gradient that reaches x along the residual path it also
+ * feeds (modeling/model.py:153-155 of the reference, where autograd adds the two):
+ *   gx = round(round(rms gradient) + add), `add` [rows, width] in `dtype`, read only.
+ * add == NULL is ct_rmsnorm_backward. */
+CT_API int ct_rmsnorm_backward_add(const void* x, const void* w, const float* rstd, const void* go,
+                                   const void* add, void* gx, int64_t rows, int64_t width, int dtype,
+                                   int weight_dtype, void* stream);
 
 /* ---- weighted cross-entropy over a tile of logits -------------------------------
  * Replaces kernels/loss_cuda.py:12-72 (_statistics, _finish, weighted_ce).

@@ -170,3 +170,27 @@ def test_swiglu_and_add_index_past_two_to_the_31():
     assert torch.equal(hidden[tail], (before.float() + up[tail].float()).bfloat16())
     del gate, up, hidden
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype,width", [(torch.bfloat16, 4096), (torch.bfloat16, 8200), (torch.bfloat16, 68), (torch.float32, 96)])
+def test_norm_with_shortcut_sums_both_gradients_like_autograd(dtype, width):
+    rows = 37
+    weight = (1 + .1 * torch.randn(width, device="cuda")).to(dtype)
+    x = torch.randn(rows, width, device="cuda", dtype=dtype, requires_grad=True)
+    y = x.detach().clone().requires_grad_(True)
+    g_normed, g_shortcut = torch.randn_like(x), torch.randn_like(x)
+    # separate: RMS(x) and x used twice, autograd adds the two gradients with its own kernel
+    plain = core_cuda.RMS.apply(y, weight, 1e-6, False, False)
+    expected, = torch.autograd.grad((plain, y * 1), y, (g_normed, g_shortcut))
+    normed, shortcut = core_cuda.RMSWithShortcut.apply(x, weight, 1e-6)
+    assert torch.equal(normed, plain) and shortcut.data_ptr() == x.data_ptr()
+    keep = g_shortcut.clone()
+    actual, = torch.autograd.grad((normed, shortcut * 1), x, (g_normed.clone(), g_shortcut))
+    assert torch.equal(actual, expected) and torch.equal(g_shortcut, keep)
+    # one branch only
+    normed, shortcut = core_cuda.RMSWithShortcut.apply(x, weight, 1e-6)
+    only_norm, = torch.autograd.grad(normed, x, g_normed.clone())
+    assert torch.equal(only_norm, torch.autograd.grad(core_cuda.RMS.apply(y, weight, 1e-6, False, False), y, g_normed)[0])
+    normed, shortcut = core_cuda.RMSWithShortcut.apply(x, weight, 1e-6)
+    only_shortcut, = torch.autograd.grad(shortcut * 2, x, g_shortcut)
+    assert torch.equal(only_shortcut, 2 * g_shortcut)
