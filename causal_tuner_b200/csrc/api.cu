@@ -275,11 +275,11 @@ extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, i
                                  int64_t K, int64_t N, int64_t r, int add, int dtype, int path, void* stream) {
   if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_input_gradient: negative size");
   if (T == 0) return CT_OK;
-  if ((N > 0 && !dy) || (r > 0 && (!b || !low)) || (w && (!dx || (r > 0 && !a))))
+  if ((N > 0 && !dy) || (r > 0 && !low) || (w && (!dx || (r > 0 && !a))))
     return fail(CT_ERR_ARG, "ct_input_gradient: null pointer");
   if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_input_gradient: dtype %d", dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (r > 0) {
+  if (r > 0 && b) {   // b == NULL: low already holds dy . b (computed while the base weight was still decoding)
     GemmArgs g = blank(T, r, dtype, low, ld_low, dtype);
     g.nseg = 1;
     g.seg[0] = segment(dy, ld_dy, 1, b, r, 1, N);

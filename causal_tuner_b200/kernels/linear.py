@@ -18,6 +18,7 @@ dtype once per GEMM (the reference rounds after the base product and again after
 low-rank update), and `tile` only bounds workspaces - tile 0 runs all rows in one launch.
 """
 
+import os
 import threading
 
 import torch
@@ -118,6 +119,56 @@ def materialize(weight, state, dtype):
     return cast(weight, dtype)
 
 
+_side_streams = {}
+
+
+class _Pending:
+    """Decodes in flight on the side stream; `wait(i)` orders the current stream after the i-th
+    matrix (and everything decoded before it), `wait()` after all of them."""
+
+    def __init__(self, events, order):
+        self.events, self.order, self.done = events, order, -1
+
+    def wait(self, index=None):
+        if not self.events:
+            return
+        position = len(self.order) - 1 if index is None else self.order.index(index)
+        if position > self.done:
+            torch.cuda.current_stream().wait_event(self.events[position])
+            self.done = position
+
+
+def materialize_ahead(pairs, dtype, order=None):
+    """`materialize` for several (weight, quant_state) pairs with the NF4 decodes issued on a side
+    stream in `order`, so that they run under whatever the caller launches next that does not need the
+    dense weights (the low-rank products, which leave the decode most of the HBM bandwidth).
+    Returns (matrices, pending); call `pending.wait(i)` before the first launch that reads matrix i.
+    CT_B200_DECODE_AHEAD=0 decodes in stream order instead."""
+    order = list(range(len(pairs))) if order is None else list(order)
+    device = pairs[0][0].device
+    ahead = (device.type == "cuda" and any(state is not None for _, state in pairs)
+             and os.environ.get("CT_B200_DECODE_AHEAD", "1") != "0")
+    if not ahead:
+        return [materialize(weight, state, dtype) for weight, state in pairs], _Pending([], order)
+    with torch.cuda.device(device):
+        main = torch.cuda.current_stream()
+        side = _side_streams.get(device.index)
+        if side is None:
+            side = _side_streams[device.index] = torch.cuda.Stream(device=device)
+        side.wait_stream(main)        # everything enqueued so far (and the memory it frees) comes first
+        matrices, events = [None] * len(pairs), []
+        with torch.cuda.stream(side):
+            for index in order:
+                weight, state = pairs[index]
+                matrices[index] = materialize(weight, state, dtype)
+                if matrices[index] is not weight:
+                    matrices[index].record_stream(main)   # consumed on `main`: hold the block until that work is done
+                event = torch.cuda.Event()
+                event.record(side)
+                events.append(event)
+    return matrices, _Pending(events, order)
+
+
 def accumulate(output, left, right, *, add=True):
     """output (+)= left @ right with fp32 accumulation (kernels/linear.py:16-24). With add=False the
     previous contents of `output` are never read."""
@@ -162,6 +213,21 @@ def input_gradient(dy, weight, a, b, dx, low, *, add=False):
     with _lib.on_device(dy):
         _lib.check(_lib.load().ct_input_gradient(
             dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), b.data_ptr(),
+            dx.data_ptr(), _leading(dx), low.data_ptr(), _leading(low), rows, inner, outer, rank, int(bool(add)),
+            _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
+
+
+def input_gradient_with(dy, weight, a, low, dx, *, add=False):
+    """`input_gradient` with low = dy @ b already computed: dx = (add ? dx : 0) + dy @ weight + low @ a."""
+    _lib.require_cuda(dy, weight, dx, low)
+    dy, weight, low = _readable(dy), _readable(weight), _readable(low)
+    _writable(dx, "dx")
+    a = a.contiguous()
+    rows, outer = dy.shape
+    inner, rank = weight.shape[1], a.shape[0]
+    with _lib.on_device(dy):
+        _lib.check(_lib.load().ct_input_gradient(
+            dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), None,
             dx.data_ptr(), _leading(dx), low.data_ptr(), _leading(low), rows, inner, outer, rank, int(bool(add)),
             _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
 
@@ -317,12 +383,16 @@ class _LoRAGroup(torch.autograd.Function):
         stacked = len(states) > 1 and step >= rows > 0
         keep = bool(getattr(_policy, "keep_low_rank", False)) and step >= rows > 0
         ctx.low_rank = None
+        decoded = None
         if stacked:
-            # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x.
+            # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x,
+            # with the base weights decoding beside it.
+            decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
             a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
             xa_all = torch.empty((rows, a_all.shape[0]), device=x.device, dtype=dtype)
             matmul(flat, a_all.T, out=xa_all)
             del a_all
+            pending.wait()
             if keep:
                 ctx.low_rank = xa_all
         elif keep:
@@ -330,12 +400,13 @@ class _LoRAGroup(torch.autograd.Function):
             ctx.low_rank = workspace[:, :parameters[1].shape[0]]
         for index, state in enumerate(states):
             weight, a, b, bias = parameters[4 * index:4 * index + 4]
-            matrix = materialize(weight, state, dtype)
+            matrix = decoded[index] if decoded is not None else materialize(weight, state, dtype)
             if stacked:
                 out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
                 apply_projection(flat, matrix, cast(b, dtype), xa_all[:, offsets[index]:offsets[index] + a.shape[0]],
                                  out=out, bias=cast(bias, dtype))
                 outputs.append(out.reshape(*x.shape[:-1], matrix.shape[0]))
+                decoded[index] = None
                 del matrix
                 continue
             a16, b16, bias16 = cast(a, dtype), cast(b, dtype), cast(bias, dtype)
@@ -377,14 +448,16 @@ class _LoRAGroup(torch.autograd.Function):
             a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
             total = a_all.shape[0]
             low_all = torch.empty((rows, total), device=x.device, dtype=dtype)
+            decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
             for index, (state, grad) in enumerate(zip(states, grad_outputs)):
                 weight, a, b, _ = parameters[4 * index:4 * index + 4]
                 signal = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
                 if ctx.head_dim and index < 2:
                     signal = core_cuda.inverse_rope_tile(signal, cosine, sine, ctx.head_dim, torch.empty_like(signal))
                 span = slice(offsets[index], offsets[index] + a.shape[0])
-                prepared.append((materialize(weight, state, dtype), a_all[span], cast(b, dtype), signal,
-                                 low_all[:, span]))
+                prepared.append((decoded[index], a_all[span], cast(b, dtype), signal, low_all[:, span]))
+            del decoded
+            pending.wait()
             input_gradient_group([p[3] for p in prepared], [p[0] for p in prepared], [p[1] for p in prepared],
                                  [p[2] for p in prepared], dx, [p[4] for p in prepared])
             # One product recomputes every projection's low-rank input, one more gives the stacked dA

@@ -10,8 +10,9 @@ and its in-place backward are ct_swiglu.
 import torch
 
 from .. import _lib
-from .linear import (apply_projection, cast, materialize, forward_linear, input_gradient, input_gradient_group,
-                     parameter_gradients, projection_parameters, matmul, stack_adapters, token_gradient)
+from .linear import (apply_projection, cast, materialize, materialize_ahead, forward_linear, input_gradient,
+                     input_gradient_with, input_gradient_group, parameter_gradients, projection_parameters, matmul,
+                     stack_adapters, token_gradient)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -64,15 +65,16 @@ def silu_multiply(gate, up):
     return _SiLUMultiply.apply(gate, up)
 
 
-def _prepare(parameters, states, dtype):
-    """Decoded base weights, cast adapters, and the gate/up `a` matrices stacked row-wise (their
-    low-rank inputs come from one product over x)."""
-    matrices = [materialize(parameters[4 * i], state, dtype) for i, state in enumerate(states)]
+def _prepare(parameters, states, dtype, order=(0, 1, 2)):
+    """Base weights decoding on the side stream in `order` (wait on the returned handle before a
+    matrix is read), cast adapters, and the gate/up `a` matrices stacked row-wise (their low-rank
+    inputs come from one product over x)."""
+    matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order)
     stacked, offsets = stack_adapters([parameters[1], parameters[5]], dtype)
     ranks = [parameters[1].shape[0], parameters[5].shape[0]]
     adapters = [(stacked[offsets[i]:offsets[i] + ranks[i]], cast(parameters[4 * i + 2], dtype)) for i in range(2)]
     adapters.append((cast(parameters[9], dtype), cast(parameters[10], dtype)))
-    return matrices, adapters, stacked
+    return matrices, adapters, stacked, pending
 
 
 @torch.no_grad()
@@ -84,7 +86,7 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
     """
     flat = cast(x.reshape(-1, x.shape[-1]), dtype)
     rows = flat.shape[0]
-    matrices, adapters, stacked = _prepare(parameters, states, dtype)
+    matrices, adapters, stacked, pending = _prepare(parameters, states, dtype)
     width = matrices[0].shape[0]
     ranks = [a.shape[0] for a, _ in adapters]
     step = max(1, min(tile, rows))
@@ -109,9 +111,12 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
             gate, up = workspace[0, :count], workspace[1, :count]
             both = low[:count]
         matmul(part, stacked.T, out=both)           # low-rank inputs of gate and up, reading x once
+        pending.wait(0)
         apply_projection(part, matrices[0], adapters[0][1], both[:, :ranks[0]], out=gate)
+        pending.wait(1)
         apply_projection(part, matrices[1], adapters[1][1], both[:, ranks[0]:], out=up)
         hidden = activation(gate, up, out=workspace[0, :count] if save else gate)
+        pending.wait(2)
         forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop], xa=low_down[:count],
                        residual=None if shortcut is None else shortcut[start:stop])
     return saved
@@ -147,7 +152,9 @@ class _TiledLoRAMLP(torch.autograd.Function):
         upstream = cast(grad.reshape(rows, grad.shape[-1]), dtype).contiguous()
         want_dx = ctx.needs_input_grad[0]
         dx = torch.empty_like(flat) if want_dx else None
-        matrices, adapters, stacked = _prepare(parameters, ctx.states, dtype)
+        # Cached: the down projection's weight is needed first, gate/up only for the input gradient.
+        matrices, adapters, stacked, pending = _prepare(parameters, ctx.states, dtype,
+                                                        (2, 0, 1) if ctx.cache else (0, 1, 2))
         ranks = [a.shape[0] for a, _ in adapters]
         make = torch.empty if rows else torch.zeros
         wide = dict(device=x.device, dtype=torch.float32)
@@ -174,9 +181,13 @@ class _TiledLoRAMLP(torch.autograd.Function):
             else:
                 matmul(part, stacked.T, out=xa_both[:count])
                 xa = [xa_both[:count, :ranks[0]], xa_both[:count, ranks[0]:]]
+                pending.wait(0)
                 apply_projection(part, matrices[0], adapters[0][1], xa[0], out=gate)
+                pending.wait(1)
                 apply_projection(part, matrices[1], adapters[1][1], xa[1], out=up)
-            input_gradient(dy, matrices[2], *adapters[2], dh, low[2])
+            matmul(dy, adapters[2][1], out=low[2])      # needs no base weight: runs beside the decodes
+            pending.wait(2)
+            input_gradient_with(dy, matrices[2], adapters[2][0], low[2], dh)
             if ctx.cache:
                 # Read the saved gate/up, write (d_gate, d_up, hidden) into the tile buffers: the saved
                 # tensors stay untouched and survive a repeated backward pass, without a copy.
@@ -188,6 +199,7 @@ class _TiledLoRAMLP(torch.autograd.Function):
             parameter_gradients(hidden, dy, da_down, db[2], low[2], xa_down[:count], add=start > 0)
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
+                pending.wait()
                 input_gradient_group((gate, up), matrices[:2], [adapters[0][0], adapters[1][0]],
                                      [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
             else:

@@ -150,7 +150,9 @@ CT_API int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t 
  *   low = round(dy @ b)                                        [T, r]
  *   dx  = round((add ? dx : 0) + dy @ w + low @ a)             [T, K]
  * dy[T,N] (ld_dy), w[N,K] (ldw), a[r,K], b[N,r] contiguous. `w` may be NULL:
- * then only `low` is written (kernels/linear.py:124). */
+ * then only `low` is written (kernels/linear.py:124). `b` may be NULL with r > 0:
+ * then `low` is an INPUT that already holds round(dy @ b) (a caller that computed it
+ * while the base weight was still being decoded on another stream). */
 CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t ldw,
                       const void* a, const void* b, void* dx, int64_t ld_dx,
                       void* low, int64_t ld_low, int64_t T, int64_t K, int64_t N,
