@@ -13,6 +13,12 @@ reference work unchanged. The arithmetic runs in libct_b200.so:
 * ``accumulate``          -> ct_matmul
 * ``materialize``         -> ct_nf4_decode / ct_cast
 
+Beyond the reference's names, for projections that share their input (q/k/v, gate/up):
+``stack_adapters`` + ``matmul`` give all low-rank inputs from one product over x,
+``apply_projection`` is ``forward_linear`` with that input already computed, ``token_gradient``
+(ct_accumulate) gives the stacked dA, ``input_gradient_group`` one summed dX, and
+``materialize_ahead`` decodes the base weights on a side stream beside those products.
+
 Differences from the reference that callers can observe: outputs are rounded to the compute
 dtype once per GEMM (the reference rounds after the base product and again after the
 low-rank update), and `tile` only bounds workspaces - tile 0 runs all rows in one launch.
