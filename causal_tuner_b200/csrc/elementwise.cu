@@ -44,6 +44,48 @@ cast_f32_bf16_vec_kernel(const float4* __restrict__ src, uint4* __restrict__ dst
   }
 }
 
+// Several contiguous tensors in one launch (the per-call casts of an operator's adapters): the
+// pointer table travels as the kernel argument, a block walks 2048-element chunks of the
+// concatenation. `vec`: fp32 -> bf16 with every pointer 16-byte aligned and every size a multiple of 8.
+constexpr int kCastBatch = 32;
+constexpr int kCastChunk = 8 * kThreads;
+
+struct CastBatch {
+  const void* src[kCastBatch];
+  void* dst[kCastBatch];
+  long long size[kCastBatch];
+  int first_chunk[kCastBatch + 1];
+  int count;
+  int vec;
+};
+
+__global__ void __launch_bounds__(kThreads)
+cast_many_kernel(const __grid_constant__ CastBatch batch, int src_dtype, int dst_dtype) {
+  const int chunks = batch.first_chunk[batch.count];
+  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    int t = 0;
+    while (t + 1 < batch.count && batch.first_chunk[t + 1] <= chunk) ++t;
+    const long long begin = static_cast<long long>(chunk - batch.first_chunk[t]) * kCastChunk;
+    const long long left = batch.size[t] - begin;
+    if (batch.vec) {
+      const long long i = begin + 8ll * threadIdx.x;
+      if (8ll * threadIdx.x < left) {
+        const float4* from = reinterpret_cast<const float4*>(static_cast<const float*>(batch.src[t]) + i);
+        const float4 lo = __ldg(from), hi = __ldg(from + 1);
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, lo.y), p1 = __floats2bfloat162_rn(lo.z, lo.w);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(hi.x, hi.y), p3 = __floats2bfloat162_rn(hi.z, hi.w);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(batch.dst[t]) + i) =
+            make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                       *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+      }
+    } else {
+      const int n = static_cast<int>(left < kCastChunk ? left : kCastChunk);
+      for (int j = threadIdx.x; j < n; j += kThreads)
+        store_from_float(batch.dst[t], begin + j, dst_dtype, load_as_float(batch.src[t], begin + j, src_dtype));
+    }
+  }
+}
+
 // ---- SwiGLU ---------------------------------------------------------------------
 // One scalar element of kernels/mlp_cuda.py:10-25.
 template <typename T>
@@ -275,6 +317,40 @@ extern "C" int ct_cast(const void* src, int src_dtype, int64_t ld_src, void* dst
   }
   count_launch(false);
   return check_launch("ct_cast");
+}
+
+extern "C" int ct_cast_many(int count, const void* const* src, void* const* dst, const int64_t* sizes, int src_dtype,
+                            int dst_dtype, void* stream) {
+  if (count < 0) return fail(CT_ERR_ARG, "ct_cast_many: count=%d", count);
+  if (count == 0) return CT_OK;
+  if (!src || !dst || !sizes) return fail(CT_ERR_ARG, "ct_cast_many: null table");
+  if (src_dtype < CT_F32 || src_dtype > CT_F16 || dst_dtype < CT_F32 || dst_dtype > CT_F16)
+    return fail(CT_ERR_ARG, "ct_cast_many: dtype %d -> %d", src_dtype, dst_dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int first = 0; first < count; first += kCastBatch) {
+    CastBatch batch{};
+    batch.count = 0;
+    batch.vec = src_dtype == CT_F32 && dst_dtype == CT_BF16;
+    batch.first_chunk[0] = 0;
+    for (int i = first; i < count && i < first + kCastBatch; ++i) {
+      if (sizes[i] < 0) return fail(CT_ERR_ARG, "ct_cast_many: negative size at %d", i);
+      if (sizes[i] == 0) continue;
+      if (!src[i] || !dst[i]) return fail(CT_ERR_ARG, "ct_cast_many: null tensor at %d", i);
+      const int j = batch.count++;
+      batch.src[j] = src[i];
+      batch.dst[j] = dst[i];
+      batch.size[j] = sizes[i];
+      const long long chunks = (sizes[i] + kCastChunk - 1) / kCastChunk;
+      if (batch.first_chunk[j] + chunks > 0x7fffffffLL) return fail(CT_ERR_UNSUPPORTED, "ct_cast_many: tensor too large");
+      batch.first_chunk[j + 1] = batch.first_chunk[j] + static_cast<int>(chunks);
+      if (sizes[i] % 8 || !aligned16(src[i]) || !aligned16(dst[i])) batch.vec = 0;
+    }
+    if (batch.count == 0) continue;
+    cast_many_kernel<<<grid_for(static_cast<int64_t>(batch.first_chunk[batch.count]) * kThreads), kThreads, 0, s>>>(
+        batch, src_dtype, dst_dtype);
+    count_launch(false);
+  }
+  return check_launch("ct_cast_many");
 }
 
 extern "C" int ct_swiglu(const void* gate, const void* up, const void* grad, void* out, void* dg, void* du, int64_t n,

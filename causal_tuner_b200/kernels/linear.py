@@ -53,6 +53,37 @@ def cast(tensor, dtype, out=None):
     return output
 
 
+def cast_many(tensors, dtype, outs=None):
+    """`cast` for several tensors at once: one launch per 32 tensors that need converting instead of
+    one each. `outs[i]` (contiguous, same shape, `dtype`) receives tensor i when given; a tensor that
+    already has `dtype` and no `out` is returned as it is, None stays None."""
+    import ctypes
+    results, jobs = [], {}
+    for index, tensor in enumerate(tensors):
+        out = None if outs is None else outs[index]
+        if tensor is None or (tensor.dtype == dtype and out is None):
+            results.append(tensor)
+            continue
+        _lib.require_cuda(tensor)
+        source = tensor.contiguous()
+        if out is None:
+            out = torch.empty(source.shape, device=source.device, dtype=dtype)
+        elif out.shape != source.shape or out.dtype != dtype or not out.is_contiguous():
+            raise ValueError("cast destination must be contiguous with the source's shape")
+        results.append(out)
+        if source.numel():
+            jobs.setdefault(source.dtype, []).append((source, out))
+    for source_dtype, pairs in jobs.items():
+        count = len(pairs)
+        sources = (ctypes.c_void_p * count)(*[s.data_ptr() for s, _ in pairs])
+        targets = (ctypes.c_void_p * count)(*[o.data_ptr() for _, o in pairs])
+        sizes = (ctypes.c_int64 * count)(*[s.numel() for s, _ in pairs])
+        with _lib.on_device(pairs[0][0]):
+            _lib.check(_lib.load().ct_cast_many(count, sources, targets, sizes, _lib.code_of(source_dtype),
+                                               _lib.code_of(dtype), _lib.stream_of(pairs[0][0])))
+    return results
+
+
 def _leading(tensor):
     """Leading dimension (elements between rows) of a 2-D tensor whose rows are contiguous."""
     return tensor.stride(0) if tensor.shape[0] > 1 else max(tensor.shape[1], 1)
@@ -264,18 +295,20 @@ def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
             _lib.code_of(dx.dtype), _lib.gemm_path, _lib.stream_of(dx)))
 
 
-def stack_adapters(matrices, dtype):
+def stack_adapters(matrices, dtype, others=()):
     """Row-wise stack of the `a` matrices of projections that share their input, cast to `dtype`,
     and the row offset of each: one product x @ stack.T then yields every projection's low-rank
-    input as a column slice, reading x once."""
+    input as a column slice, reading x once. `others` (b matrices, biases; None allowed) are cast in
+    the same launch; returns (stacked, offsets, cast others)."""
     total = sum(m.shape[0] for m in matrices)
     stacked = torch.empty((total, matrices[0].shape[1]), device=matrices[0].device, dtype=dtype)
-    offsets, cursor = [], 0
+    offsets, slices, cursor = [], [], 0
     for matrix in matrices:
-        cast(matrix, dtype, out=stacked[cursor:cursor + matrix.shape[0]])
+        slices.append(stacked[cursor:cursor + matrix.shape[0]])
         offsets.append(cursor)
         cursor += matrix.shape[0]
-    return stacked, offsets
+    converted = cast_many([*matrices, *others], dtype, [*slices, *([None] * len(others))])
+    return stacked, offsets, converted[len(matrices):]
 
 
 def apply_projection(x, weight, b, xa, *, out, bias=None, residual=None):
@@ -394,7 +427,11 @@ class _LoRAGroup(torch.autograd.Function):
             # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x,
             # with the base weights decoding beside it.
             decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
-            a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
+            count = len(states)
+            a_all, offsets, others = stack_adapters(
+                [parameters[4 * i + 1] for i in range(count)], dtype,
+                [parameters[4 * i + 2] for i in range(count)] + [parameters[4 * i + 3] for i in range(count)])
+            b_cast, bias_cast = others[:count], others[count:]
             xa_all = torch.empty((rows, a_all.shape[0]), device=x.device, dtype=dtype)
             matmul(flat, a_all.T, out=xa_all)
             del a_all
@@ -409,13 +446,13 @@ class _LoRAGroup(torch.autograd.Function):
             matrix = decoded[index] if decoded is not None else materialize(weight, state, dtype)
             if stacked:
                 out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
-                apply_projection(flat, matrix, cast(b, dtype), xa_all[:, offsets[index]:offsets[index] + a.shape[0]],
-                                 out=out, bias=cast(bias, dtype))
+                apply_projection(flat, matrix, b_cast[index], xa_all[:, offsets[index]:offsets[index] + a.shape[0]],
+                                 out=out, bias=bias_cast[index])
                 outputs.append(out.reshape(*x.shape[:-1], matrix.shape[0]))
                 decoded[index] = None
                 del matrix
                 continue
-            a16, b16, bias16 = cast(a, dtype), cast(b, dtype), cast(bias, dtype)
+            a16, b16, bias16 = cast_many((a, b, bias), dtype)
             out = torch.empty((rows, matrix.shape[0]), device=x.device, dtype=dtype)
             for start in range(0, rows, step):
                 stop = min(start + step, rows)
@@ -451,7 +488,8 @@ class _LoRAGroup(torch.autograd.Function):
         if want_dx and len(states) > 1 and step >= rows > 0:
             # Untiled group (q/k/v): one GEMM sums the input gradients of all projections.
             prepared = []
-            a_all, offsets = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype)
+            a_all, offsets, b_cast = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype,
+                                                    [parameters[4 * i + 2] for i in range(len(states))])
             total = a_all.shape[0]
             low_all = torch.empty((rows, total), device=x.device, dtype=dtype)
             decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
@@ -461,7 +499,7 @@ class _LoRAGroup(torch.autograd.Function):
                 if ctx.head_dim and index < 2:
                     signal = core_cuda.inverse_rope_tile(signal, cosine, sine, ctx.head_dim, torch.empty_like(signal))
                 span = slice(offsets[index], offsets[index] + a.shape[0])
-                prepared.append((decoded[index], a_all[span], cast(b, dtype), signal, low_all[:, span]))
+                prepared.append((decoded[index], a_all[span], b_cast[index], signal, low_all[:, span]))
             del decoded
             pending.wait()
             input_gradient_group([p[3] for p in prepared], [p[0] for p in prepared], [p[1] for p in prepared],
@@ -487,7 +525,7 @@ class _LoRAGroup(torch.autograd.Function):
         for index, (state, grad) in enumerate(zip(states, grad_outputs)):
             weight, a, b, _ = parameters[4 * index:4 * index + 4]
             matrix = materialize(weight, state, dtype) if want_dx else None
-            a16, b16 = cast(a, dtype), cast(b, dtype)
+            a16, b16 = cast_many((a, b), dtype)
             dy = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
             make = torch.empty_like if rows else torch.zeros_like
             da, db = make(a), make(b)

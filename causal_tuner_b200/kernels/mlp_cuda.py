@@ -70,10 +70,11 @@ def _prepare(parameters, states, dtype, order=(0, 1, 2)):
     matrix is read), cast adapters, and the gate/up `a` matrices stacked row-wise (their low-rank
     inputs come from one product over x)."""
     matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order)
-    stacked, offsets = stack_adapters([parameters[1], parameters[5]], dtype)
+    stacked, offsets, others = stack_adapters([parameters[1], parameters[5]], dtype,
+                                              [parameters[2], parameters[6], parameters[9], parameters[10]])
     ranks = [parameters[1].shape[0], parameters[5].shape[0]]
-    adapters = [(stacked[offsets[i]:offsets[i] + ranks[i]], cast(parameters[4 * i + 2], dtype)) for i in range(2)]
-    adapters.append((cast(parameters[9], dtype), cast(parameters[10], dtype)))
+    adapters = [(stacked[offsets[i]:offsets[i] + ranks[i]], others[i]) for i in range(2)]
+    adapters.append((others[2], others[3]))
     return matrices, adapters, stacked, pending
 
 

@@ -113,6 +113,10 @@ CT_API int ct_nf4_nest(const float* absmax, int64_t blocks, int blocksize2, cons
  * -> dst[rows, cols] (ld_dst), round-to-nearest-even. */
 CT_API int ct_cast(const void* src, int src_dtype, int64_t ld_src, void* dst, int dst_dtype,
             int64_t ld_dst, int64_t rows, int64_t cols, void* stream);
+/* The same casts for `count` contiguous tensors in one launch (all the adapters an operator
+ * needs in the compute dtype). `src`, `dst` and `sizes` (elements) are HOST arrays. */
+CT_API int ct_cast_many(int count, const void* const* src, void* const* dst, const int64_t* sizes,
+                        int src_dtype, int dst_dtype, void* stream);
 
 /* ---- generic matrix product --------------------------------------------
  * Replaces kernels/linear.py:16-24 (accumulate) and the bare torch.mm calls at

@@ -194,3 +194,35 @@ def test_norm_with_shortcut_sums_both_gradients_like_autograd(dtype, width):
     normed, shortcut = core_cuda.RMSWithShortcut.apply(x, weight, 1e-6)
     only_shortcut, = torch.autograd.grad(shortcut * 2, x, g_shortcut)
     assert torch.equal(only_shortcut, 2 * g_shortcut)
+
+
+def test_cast_many_equals_one_cast_each():
+    generator = torch.Generator().manual_seed(2)
+    shapes = [(256, 4096), (5, 7), (1,), (4096,), (33, 17)] + [(16, 8)] * 40        # more than one launch carries (32)
+    sources = [torch.randn(shape, generator=generator).cuda() for shape in shapes]
+    sources[3] = None
+    sources[6] = sources[6].bfloat16()                    # already in the target dtype: returned as it is
+    before = _launches()
+    results = linear.cast_many(sources, torch.bfloat16)
+    assert _launches() - before == 2
+    for source, result in zip(sources, results):
+        if source is None:
+            assert result is None
+        elif source.dtype == torch.bfloat16:
+            assert result is source
+        else:
+            assert torch.equal(result, source.bfloat16())
+    # into caller-provided slices of one buffer, same dtype (a plain copy) and fp16
+    stacked = torch.empty(3 * 5, 7, device="cuda")
+    pieces = [torch.randn(5, 7, device="cuda") for _ in range(3)]
+    linear.cast_many(pieces, torch.float32, [stacked[0:5], stacked[5:10], stacked[10:15]])
+    assert torch.equal(stacked, torch.cat(pieces))
+    halves = linear.cast_many(pieces, torch.float16)
+    assert all(torch.equal(h, p.half()) for h, p in zip(halves, pieces))
+    with pytest.raises(ValueError):
+        linear.cast_many(pieces[:1], torch.float32, [stacked[0:4]])
+
+
+def _launches():
+    from causal_tuner_b200 import _lib
+    return _lib.launch_count()
