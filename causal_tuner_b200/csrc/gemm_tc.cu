@@ -64,6 +64,8 @@ struct Shape {
   static constexpr size_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 constexpr int GROUP_M = 16;                     // tile rasterisation: 16 row tiles share a sweep over columns
+                                                // (CT_B200_GEMM_GROUP_M overrides it for experiments; 8 and 16
+                                                // measure the same, 4, 32 and 64 are slower)
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 struct TcSegment {
@@ -78,6 +80,7 @@ struct TcParams {
   int k_blocks_total;
   int splits;
   int m_tiles, n_tiles;
+  int group_m;          // tile rasterisation: this many row tiles share a sweep over the columns
   int64_t M, N;
   void* out;
   int64_t ldo;
@@ -258,10 +261,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const TcParams& p) {
   TileCoord c;
   c.split = tile / per_split;
   const int rem = tile - c.split * per_split;
-  const int per_group = GROUP_M * p.n_tiles;
+  const int per_group = p.group_m * p.n_tiles;
   const int group = rem / per_group;
-  const int first_m = group * GROUP_M;
-  const int group_rows = min(GROUP_M, p.m_tiles - first_m);
+  const int first_m = group * p.group_m;
+  const int group_rows = min(p.group_m, p.m_tiles - first_m);
   const int in_group = rem - group * per_group;
   c.m = first_m + in_group % group_rows;
   c.n = in_group / group_rows;
@@ -770,6 +773,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   p.splits = g.split_k > 1 ? g.split_k : 1;
   p.m_tiles = static_cast<int>((g.M + tile_m - 1) / tile_m);
   p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
+  {
+    const char* text = getenv("CT_B200_GEMM_GROUP_M");
+    const int value = text ? atoi(text) : 0;
+    p.group_m = value > 0 ? value : GROUP_M;
+  }
   p.M = g.M;
   p.N = g.N;
   p.out = g.out;
