@@ -36,13 +36,28 @@ struct Nf4Params {
   int nested;
   int state_dtype;
   int vector_ok;  // packed is 4-byte aligned and out 16-byte aligned
+  int block_shift;   // log2(blocksize) when it is a power of two, else -1
+  int block2_shift;  // the same for blocksize2
 };
+
+__device__ __forceinline__ int64_t block_of(const Nf4Params& p, int64_t element) {
+  return p.block_shift >= 0 ? element >> p.block_shift : element / p.blocksize;
+}
+
+// Rounding to the quant state's dtype before the output rounding. STATE = CT_F32 means none is
+// needed: the state is fp32, or it has the output type (rounding twice to one type changes nothing).
+template <int STATE>
+__device__ __forceinline__ float round_state(float v) {
+  if constexpr (STATE == CT_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  else if constexpr (STATE == CT_F16) return __half2float(__float2half_rn(v));
+  else return v;
+}
 
 __device__ __forceinline__ float block_scale(const Nf4Params& p, int64_t group) {
   if (!p.nested) return __ldg(static_cast<const float*>(p.absmax) + group);
   const uint8_t q = __ldg(static_cast<const uint8_t*>(p.absmax) + group);
   const float decoded = __ldg(p.code2 + q);
-  const float maximum = __ldg(p.absmax2 + group / p.blocksize2);
+  const float maximum = __ldg(p.absmax2 + (p.block2_shift >= 0 ? group >> p.block2_shift : group / p.blocksize2));
   return __fadd_rn(__fmul_rn(decoded, maximum), __ldg(p.offset));
 }
 
@@ -78,7 +93,7 @@ __device__ __forceinline__ void store_group<float>(float* out, const float (&v)[
   dst[1] = make_float4(v[4], v[5], v[6], v[7]);
 }
 
-template <typename OutT>
+template <typename OutT, int STATE>
 __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p) {
   __shared__ float lut[16 * 32];
   lut[threadIdx.x] = __ldg(p.code + (threadIdx.x >> 5));
@@ -98,7 +113,7 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
     for (int step = 0; step < kSteps; ++step) {
       const int64_t first = block_first + (static_cast<int64_t>(step) * kThreads + threadIdx.x) * kGroup;
       word[step] = __ldg(reinterpret_cast<const uint32_t*>(p.packed + first / 2));
-      scale[step] = block_scale(p, first / p.blocksize);
+      scale[step] = block_scale(p, block_of(p, first));
     }
 #pragma unroll
     for (int step = 0; step < kSteps; ++step) {
@@ -107,8 +122,8 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const uint32_t byte = (word[step] >> (8 * b)) & 255u;
-        v[2 * b] = round_dtype(__fmul_rn(mine[(byte >> 4) * 32], scale[step]), p.state_dtype);
-        v[2 * b + 1] = round_dtype(__fmul_rn(mine[(byte & 15u) * 32], scale[step]), p.state_dtype);
+        v[2 * b] = round_state<STATE>(__fmul_rn(mine[(byte >> 4) * 32], scale[step]));
+        v[2 * b + 1] = round_state<STATE>(__fmul_rn(mine[(byte & 15u) * 32], scale[step]));
       }
       store_group<OutT>(out + first, v);
     }
@@ -122,13 +137,13 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
     if (first >= p.n) return;
     if (vector && first + kGroup <= p.n) {
       const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.packed + first / 2));
-      const float scale = block_scale(p, first / p.blocksize);
+      const float scale = block_scale(p, block_of(p, first));
       float v[kGroup];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const uint32_t byte = (word >> (8 * b)) & 255u;
-        v[2 * b] = round_dtype(__fmul_rn(mine[(byte >> 4) * 32], scale), p.state_dtype);
-        v[2 * b + 1] = round_dtype(__fmul_rn(mine[(byte & 15u) * 32], scale), p.state_dtype);
+        v[2 * b] = round_state<STATE>(__fmul_rn(mine[(byte >> 4) * 32], scale));
+        v[2 * b + 1] = round_state<STATE>(__fmul_rn(mine[(byte & 15u) * 32], scale));
       }
       store_group<OutT>(out + first, v);
       continue;
@@ -139,9 +154,9 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
     for (int64_t e = first; e < last; e += 2) {
       const uint8_t byte = __ldg(p.packed + e / 2);
       const float high = mine[(byte >> 4) * 32], low = mine[(byte & 15) * 32];
-      const float scale = block_scale(p, e / p.blocksize);
-      out[e] = from_float<OutT>(round_dtype(__fmul_rn(high, scale), p.state_dtype));
-      if (e + 1 < p.n) out[e + 1] = from_float<OutT>(round_dtype(__fmul_rn(low, scale), p.state_dtype));
+      const float scale = block_scale(p, block_of(p, e));
+      out[e] = from_float<OutT>(round_state<STATE>(__fmul_rn(high, scale)));
+      if (e + 1 < p.n) out[e + 1] = from_float<OutT>(round_state<STATE>(__fmul_rn(low, scale)));
     }
   }
 }
@@ -160,15 +175,31 @@ extern "C" int ct_nf4_decode(const uint8_t* packed, const void* absmax, const fl
   if (nested && (!code2 || !absmax2 || !offset || blocksize2 <= 0)) return fail(CT_ERR_ARG, "ct_nf4_decode: nested statistics missing");
   if (state_dtype < CT_F32 || state_dtype > CT_F16 || out_dtype < CT_F32 || out_dtype > CT_F16)
     return fail(CT_ERR_ARG, "ct_nf4_decode: dtype");
-  Nf4Params p{packed, absmax, code, code2, absmax2, offset, out, n, blocksize, blocksize2 > 0 ? blocksize2 : 1,
-              nested, state_dtype,
-              (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0};
+  auto log2_of = [](int value) {
+    if (value <= 0 || (value & (value - 1))) return -1;
+    int shift = 0;
+    while ((1 << shift) < value) ++shift;
+    return shift;
+  };
+  const int inner2 = blocksize2 > 0 ? blocksize2 : 1;
+  Nf4Params p{packed, absmax, code, code2, absmax2, offset, out, n, blocksize, inner2, nested, state_dtype,
+              (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+              log2_of(blocksize), log2_of(inner2)};
   const int64_t per_block = static_cast<int64_t>(kThreads) * kSteps * kGroup;
   const unsigned blocks = static_cast<unsigned>((n + per_block - 1) / per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (out_dtype == CT_BF16) nf4_decode_kernel<__nv_bfloat16><<<blocks, kThreads, 0, s>>>(p);
-  else if (out_dtype == CT_F16) nf4_decode_kernel<__half><<<blocks, kThreads, 0, s>>>(p);
-  else nf4_decode_kernel<float><<<blocks, kThreads, 0, s>>>(p);
+  // The state rounding is a separate step only when it changes something.
+  const int state = (state_dtype == CT_F32 || state_dtype == out_dtype) ? CT_F32 : state_dtype;
+#define CT_NF4_LAUNCH(OutT)                                                                    \
+  do {                                                                                         \
+    if (state == CT_BF16) nf4_decode_kernel<OutT, CT_BF16><<<blocks, kThreads, 0, s>>>(p);     \
+    else if (state == CT_F16) nf4_decode_kernel<OutT, CT_F16><<<blocks, kThreads, 0, s>>>(p);  \
+    else nf4_decode_kernel<OutT, CT_F32><<<blocks, kThreads, 0, s>>>(p);                       \
+  } while (0)
+  if (out_dtype == CT_BF16) CT_NF4_LAUNCH(__nv_bfloat16);
+  else if (out_dtype == CT_F16) CT_NF4_LAUNCH(__half);
+  else CT_NF4_LAUNCH(float);
+#undef CT_NF4_LAUNCH
   count_launch(false);
   return check_launch("ct_nf4_decode");
 }
