@@ -400,6 +400,8 @@ def step_config(name, gpus, mlp_cache_gib=0, execution=None, keep_low_rank=False
             "low_rank_inputs": (f"x.A^T of q/k/v/o kept for backward ({kept_mb:.1f} MB per layer)" if keep_low_rank
                                 else "recomputed in backward (as the reference does)"),
             "parallelism": f"dp{gpus}",
+            "rows": ("one global batch of n_gpus x rows_per_gpu packed rows (seed 1000); ranks take rows_per_gpu rows "
+                     "each from the cost-balanced assignment (tokens + document length^2 / (12 x seq_len))"),
             "l2": "per-layer operands (>= 134 MB activations + 117 MB decoded weight) exceed the 126 MB L2"}
 
 
@@ -441,7 +443,16 @@ def run_step(args):
     model = bench_step.build_model(args.workload, device, args.mlp_cache_gib, keep_low_rank=bool(args.keep_low_rank))
     optimizer = make_optimizer(model, learning_rate=2e-5)
     trainer = Trainer(model, optimizer, device=device, loss_token_budget=4096)
-    host_batch = bench_step.synthetic_batch(spec["rows"], spec["length"], spec["config"]["vocab_size"], seed=1000 + rank)
+    # One global batch of world_size x rows packed rows, the same on every rank; each rank takes the rows
+    # the cost-balanced assignment gives it (rows per rank fixed, so the per-GPU token count does not
+    # change with N, but no rank is left with all the long documents).
+    host_batch = bench_step.synthetic_batch(spec["rows"] * world_size, spec["length"], spec["config"]["vocab_size"],
+                                            seed=1000)
+    if world_size > 1:
+        from causal_tuner_b200.dp import balance_rows, row_costs
+        costs = row_costs(host_batch["attention_mask"], host_batch["segment_ids"], width=spec["length"])
+        mine = torch.tensor(balance_rows(costs, world_size)[rank])
+        host_batch = {key: value[mine].contiguous() for key, value in host_batch.items()}
     host_batch = {k: v.pin_memory() for k, v in host_batch.items()}
     device_batch = {k: v.to(device) for k, v in host_batch.items()}
     tokens_per_rank = spec["rows"] * spec["length"]
