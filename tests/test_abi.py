@@ -24,6 +24,25 @@ def test_header_declares_what_the_binding_expects():
     assert declared_symbols() == sorted(_lib.SIGNATURES)
 
 
+def test_binding_passes_as_many_arguments_as_the_header_declares():
+    with open(HEADER) as f:
+        text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
+    for name, parameters in re.findall(r"CT_API\s+[\w\s\*]+?\b(ct_[a-z0-9_]+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        parameters = parameters.strip()
+        count = 0 if parameters in ("", "void") else parameters.count(",") + 1
+        assert count == len(_lib.SIGNATURES[name][1]), name
+        # pointers are passed as void pointers, 64-bit sizes as int64, never as a narrower type
+        for declared, bound in zip(parameters.split(","), _lib.SIGNATURES[name][1]):
+            if "*" in declared:
+                assert bound is ctypes.c_void_p, (name, declared)
+            elif "int64_t" in declared:
+                assert bound is ctypes.c_int64, (name, declared)
+            elif "float" in declared:
+                assert bound is ctypes.c_float, (name, declared)
+            elif parameters not in ("", "void"):
+                assert bound is ctypes.c_int, (name, declared)
+
+
 def test_library_exports_every_declared_symbol():
     library = ctypes.CDLL(_lib.LIBRARY_PATH)
     for name in declared_symbols():
