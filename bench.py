@@ -390,14 +390,14 @@ def step_config(name, gpus, mlp_cache_gib=0, execution=None, keep_low_rank=False
     per_layer = spec["rows"] * spec["length"] * 2 * (2 * config["intermediate_size"] + 2 * bench_step.RANK)
     planned = min(config["num_hidden_layers"], int(mlp_cache_gib * 2**30) // per_layer)   # MLP.cache_bytes per layer
     cached = planned if execution is None else execution.get("mlp_cache_layers", 0)
-    kept_mb = 4 * bench_step.RANK * 2 * spec["rows"] * spec["length"] / 1e6
+    kept_mb = 5 * bench_step.RANK * 2 * spec["rows"] * spec["length"] / 1e6
     return {"workload": f"{name} ({spec['reference']})", **spec["config"], "rank": bench_step.RANK,
             "rows_per_gpu": spec["rows"], "seq_len": spec["length"], "global_batch": spec["rows"] * gpus,
             "nf4_blocksize": 64, "absmax": "fp32", "attention": "flash_attention_2 (library, as in the reference)",
             "activation_checkpointing": False,
             "mlp": (f"gate/up kept for backward in {cached} layers ({mlp_cache_gib} GiB budget, last layers first), "
                     f"recomputed in backward in the others"),
-            "low_rank_inputs": (f"x.A^T of q/k/v/o kept for backward ({kept_mb:.1f} MB per layer)" if keep_low_rank
+            "low_rank_inputs": (f"x.A^T of q/k/v/o and (with the MLP cache) down kept for backward ({kept_mb:.1f} MB per layer)" if keep_low_rank
                                 else "recomputed in backward (as the reference does)"),
             "parallelism": f"dp{gpus}",
             "rows": ("one global batch of n_gpus x rows_per_gpu packed rows (seed 1000); ranks take rows_per_gpu rows "

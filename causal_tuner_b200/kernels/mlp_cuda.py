@@ -10,7 +10,7 @@ and its in-place backward are ct_swiglu.
 import torch
 
 from .. import _lib
-from .linear import (apply_projection, cast, materialize, materialize_ahead, forward_linear, input_gradient,
+from .linear import (_policy, apply_projection, cast, materialize, materialize_ahead, forward_linear, input_gradient,
                      input_gradient_with, input_gradient_group, parameter_gradients, projection_parameters, matmul,
                      stack_adapters, token_gradient)
 
@@ -100,6 +100,9 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
         kept = torch.empty((rows, stacked.shape[0]), device=x.device, dtype=dtype)   # [xa_gate | xa_up]
         saved = (*(torch.empty((rows, width), device=x.device, dtype=dtype) for _ in range(2)),
                  kept[:, :ranks[0]], kept[:, ranks[0]:])
+        if getattr(_policy, "keep_low_rank", False):
+            # this library's option: the down projection's low-rank input joins the cache as a fifth tensor
+            saved = (*saved, torch.empty((rows, ranks[2]), device=x.device, dtype=dtype))
     destination = output.view(rows, output.shape[-1])
     shortcut = None if residual is None else residual.reshape(rows, residual.shape[-1])
     for start in range(0, rows, step):
@@ -118,7 +121,8 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
         apply_projection(part, matrices[1], adapters[1][1], both[:, ranks[0]:], out=up)
         hidden = activation(gate, up, out=workspace[0, :count] if save else gate)
         pending.wait(2)
-        forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop], xa=low_down[:count],
+        forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop],
+                       xa=saved[4][start:stop] if len(saved) > 4 else low_down[:count],
                        residual=None if shortcut is None else shortcut[start:stop])
     return saved
 
@@ -135,6 +139,7 @@ class _TiledLoRAMLP(torch.autograd.Function):
         if cache:
             output = torch.empty(x.shape, device=x.device, dtype=dtype)
             saved = _forward_into(output, x, dtype, tile, states, parameters, residual, save=True)
+            ctx.kept = len(saved)
             ctx.save_for_backward(x, *saved, *parameters)
             return output
         ctx.save_for_backward(x, *parameters)
@@ -143,9 +148,9 @@ class _TiledLoRAMLP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         x, *parameters = ctx.saved_tensors
-        saved = parameters[:4] if ctx.cache else ()
+        saved = parameters[:ctx.kept] if ctx.cache else ()
         if ctx.cache:
-            parameters = parameters[4:]
+            parameters = parameters[ctx.kept:]
         dtype = ctx.dtype
         residual_grad = grad if ctx.needs_input_grad[4] else None
         flat = cast(x.reshape(-1, x.shape[-1]), dtype)
@@ -196,8 +201,11 @@ class _TiledLoRAMLP(torch.autograd.Function):
                 hidden = dh
             else:
                 hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
-            matmul(hidden, adapters[2][0].T, out=xa_down[:count])
-            parameter_gradients(hidden, dy, da_down, db[2], low[2], xa_down[:count], add=start > 0)
+            if len(saved) > 4:
+                xa_low = saved[4][start:stop]
+            else:
+                xa_low = matmul(hidden, adapters[2][0].T, out=xa_down[:count])
+            parameter_gradients(hidden, dy, da_down, db[2], low[2], xa_low, add=start > 0)
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
                 pending.wait()
@@ -232,7 +240,11 @@ def tiled_lora_mlp(module, x, residual=None, *, tile=None, cache=None):
         states.append(state)
     tile = (module.tile if tile is None else tile) or max(1, x.numel() // x.shape[-1])
     cache = (module.cache_intermediates if cache is None else cache) and torch.is_grad_enabled()
-    output = _TiledLoRAMLP.apply(x, dtype, tile, tuple(states), residual, cache, *parameters)
+    _policy.keep_low_rank = bool(cache) and all(getattr(projection, "keep_low_rank", False) for projection in modules)
+    try:
+        output = _TiledLoRAMLP.apply(x, dtype, tile, tuple(states), residual, cache, *parameters)
+    finally:
+        _policy.keep_low_rank = False
     if not cache:
         _forward_into(output, x, dtype, tile, states, parameters, residual)
     return output

@@ -27,8 +27,9 @@ class Runtime:
     mlp_cache_budget_bytes: int | None = None
     attention_cache_budget_bytes: int | None = None
     projection_tile: int = 0
-    # Keep the low-rank inputs x @ A.T of q/k/v/o between forward and backward (2 bytes x rank per
-    # token and projection) instead of recomputing them; the reference always recomputes (False).
+    # Keep the low-rank inputs x @ A.T of q/k/v/o (and, in layers that cache their MLP activations,
+    # of the down projection) between forward and backward - 2 bytes x rank per token and
+    # projection - instead of recomputing them; the reference always recomputes (False).
     keep_low_rank: bool = False
     checkpoint: bool = True
     adaptive: bool = False
@@ -50,6 +51,8 @@ class MLP(nn.Module):
         self.gate_proj = Projection(hidden, inner, **kwargs)
         self.up_proj = Projection(hidden, inner, **kwargs)
         self.down_proj = Projection(inner, hidden, **kwargs)
+        for projection in (self.gate_proj, self.up_proj, self.down_proj):
+            projection.keep_low_rank = getattr(runtime, "keep_low_rank", False)
 
     def cache_bytes(self, rows):
         """Bytes the cache=True mode retains for `rows` tokens: gate, up and their low-rank inputs."""

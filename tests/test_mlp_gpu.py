@@ -321,3 +321,29 @@ def test_config3_recompute_versus_stored_activations(capsys):
         assert torch.equal(a, b)
     for a, b in zip(outputs["recompute"][1], outputs["stored"][1]):
         assert relative(a, b) < 3e-2
+
+
+def test_keeping_low_rank_inputs_changes_what_is_retained_not_a_value():
+    module = MLP(TinyConfig, Runtime(rank=8, mlp_tile=5), "cuda")
+    randomise_b(module, .05)
+    module.cache_intermediates = True
+    x = torch.randn(2, 7, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    signal = torch.randn_like(x)
+    params = (x, *trainable(module))
+    results = []
+    for keep in (False, True):
+        for projection in (module.gate_proj, module.up_proj, module.down_proj):
+            projection.keep_low_rank = keep
+        saved = []
+        with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t) or t, lambda t: t):
+            out = module(x, residual=x)
+        allowed = {x.data_ptr(), *(p.data_ptr() for p in module.parameters())}
+        retained = sum(t.numel() * t.element_size() for t in saved if t.data_ptr() not in allowed)
+        first = torch.autograd.grad(out, params, signal, retain_graph=True)
+        again = torch.autograd.grad(out, params, signal)
+        assert all(torch.equal(a, b) for a, b in zip(first, again))
+        results.append((out, first, retained))
+    assert torch.equal(results[0][0], results[1][0])
+    assert all(torch.equal(a, b) for a, b in zip(results[0][1], results[1][1]))
+    assert results[0][2] == module.cache_bytes(14)
+    assert results[1][2] == module.cache_bytes(14) + 14 * 8 * 2      # plus the down projection's [rows, rank] bf16
