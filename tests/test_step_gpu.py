@@ -89,6 +89,36 @@ def test_bf16_nf4_flash_step_tracks_the_fp32_reference(golden):
     assert all(p.grad.dtype == torch.float32 for p in model.adapter_parameters())
 
 
+@pytest.mark.parametrize("policy", ["reference", "kept"])
+def test_updates_are_reproducible_and_independent_of_what_is_kept(golden, policy, monkeypatch):
+    """Three updates in the production configuration, run twice from the same state: bit-identical
+    losses and adapters (fixed summation orders, side-stream decodes ordered by events). Keeping MLP
+    activations and low-rank inputs, or decoding in stream order, changes memory and time, never a value."""
+    pytest.importorskip("flash_attn")
+    g = golden("step_tiny_b1.npz")
+
+    def run(keep, ahead="1"):
+        monkeypatch.setenv("CT_B200_DECODE_AHEAD", ahead)
+        runtime = Runtime(rank=16, base_dtype=torch.bfloat16, compute_dtype=torch.bfloat16, checkpoint=False,
+                          keep_low_rank=keep, mlp_cache_budget_bytes=(1 << 30) if keep else None)
+        model = load_model(g, runtime, nf4=True)
+        with torch.no_grad():
+            for name, parameter in model.named_parameters():
+                if name.endswith("lora_B"):
+                    parameter.copy_(torch.linspace(-.02, .02, parameter.numel(), device="cuda").view_as(parameter))
+        trainer = Trainer(model, make_optimizer(model, learning_rate=1e-3), device="cuda")
+        losses = [trainer.update([batch_of(g)])["loss"] for _ in range(3)]
+        return losses, [p.detach().clone() for p in model.adapter_parameters()]
+
+    keep = policy == "kept"
+    first, again, in_order = run(keep), run(keep), run(keep, ahead="0")
+    other = run(not keep)
+    for losses, adapters in (again, in_order, other):
+        assert losses == first[0]
+        assert all(torch.equal(a, b) for a, b in zip(adapters, first[1]))
+    assert first[0][2] < first[0][0]
+
+
 def test_two_microbatches_equal_one_concatenated_batch(golden):
     g = golden("step_tiny_b1.npz")
     runtime = Runtime(rank=16, base_dtype=torch.float32, train_dtype=torch.float32, compute_dtype=torch.float32,
