@@ -201,3 +201,53 @@ def test_grouped_input_gradient_equals_the_sum_of_the_projections(path, shapes):
     before = dx.clone()
     linear.input_gradient_group(dys, weights, a_list, b_list, dx, lows, add=True)
     assert relative(dx, before.float() + expected) < 6e-3
+
+
+@pytest.mark.parametrize("tokens,rows,cols", [(4096, 768, 512), (300, 24, 520), (1024, 16, 256), (16384, 512, 128)])
+def test_token_gradient_of_stacked_low_matrices(path, tokens, rows, cols):
+    # out = left^T @ right over the tokens, fp32, fixed slice order; `left` holds several projections'
+    # low matrices side by side, so row blocks of `out` are their separate dA.
+    left = torch.randn(tokens, rows, device="cuda").bfloat16()
+    right = torch.randn(tokens, cols, device="cuda").bfloat16()
+    out = torch.full((rows, cols), float("nan"), device="cuda")
+    linear.token_gradient(left, right, out)
+    expected = left.float().T @ right.float()
+    assert relative(out, expected) < 1e-5
+    again = torch.empty_like(out)
+    linear.token_gradient(left, right, again)
+    assert torch.equal(out, again)
+    linear.token_gradient(left, right, out, add=True)
+    assert relative(out, 2 * expected) < 1e-5
+    # a column slice of a wider buffer as the left operand (leading dimension != width)
+    third = rows // 3 if rows >= 24 else rows
+    part = torch.empty(third, cols, device="cuda")
+    linear.token_gradient(left[:, :third], right, part)
+    assert relative(part, expected[:third]) < 1e-5
+    with pytest.raises(ValueError):
+        linear.token_gradient(left, right, torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,inner,outer,rank", [(300, 256, 520, 16), (1024, 512, 768, 256)])
+def test_projection_pieces_equal_the_fused_calls(path, rows, inner, outer, rank):
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    dy = torch.randn(rows, outer, device="cuda").bfloat16()
+    w = (torch.randn(outer, inner, device="cuda") * .05).bfloat16()
+    a = (torch.randn(rank, inner, device="cuda") * .05).bfloat16()
+    b = (torch.randn(outer, rank, device="cuda") * .05).bfloat16()
+    bias = torch.randn(outer, device="cuda").bfloat16()
+    out, xa = torch.empty(rows, outer, device="cuda", dtype=torch.bfloat16), torch.empty(rows, rank, device="cuda", dtype=torch.bfloat16)
+    linear.forward_linear(x, w, a, b, out=out, xa=xa, bias=bias)
+    # low-rank input computed apart, as a column slice of a stacked buffer
+    stacked = torch.full((rows, rank + 8), float("nan"), device="cuda", dtype=torch.bfloat16)
+    linear.matmul(x, a.T, out=stacked[:, 8:])
+    assert torch.equal(stacked[:, 8:], xa)
+    apart = torch.empty_like(out)
+    linear.apply_projection(x, w, b, stacked[:, 8:], out=apart, bias=bias)
+    assert torch.equal(apart, out)
+    dx, low = torch.empty(rows, inner, device="cuda", dtype=torch.bfloat16), torch.empty_like(xa)
+    linear.input_gradient(dy, w, a, b, dx, low)
+    low_apart = torch.empty_like(low)
+    linear.matmul(dy, b, out=low_apart)
+    dx_apart = torch.empty_like(dx)
+    linear.input_gradient_with(dy, w, a, low_apart, dx_apart)
+    assert torch.equal(low_apart, low) and torch.equal(dx_apart, dx)
