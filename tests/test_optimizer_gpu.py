@@ -128,3 +128,25 @@ def test_rejects_what_it_cannot_step():
     parameter.grad = torch.randn_like(parameter)
     with pytest.raises(TypeError):
         FusedAdamW([parameter]).scale_clip_step(None, 1.0)
+
+
+def test_update_of_128m_values_matches_and_leaves_the_cache_behind():
+    # 32 tensors of 4 M values: 2 GB of parameters, gradients and moments per side, far beyond the 126 MB L2.
+    sizes = [(2048, 2048)] * 32
+    ours = [torch.nn.Parameter(torch.randn(size, device="cuda")) for size in sizes]
+    theirs = [torch.nn.Parameter(p.detach().clone()) for p in ours]
+    fused = FusedAdamW(ours, lr=1e-3, weight_decay=0.01)
+    reference = torch.optim.AdamW(theirs, lr=1e-3, weight_decay=0.01, foreach=False, fused=True)
+    divisor = torch.tensor(16384.0, device="cuda")
+    for _ in range(2):
+        for a, b in zip(ours, theirs):
+            a.grad = torch.randn_like(a) * 100
+            b.grad = a.grad.clone()
+        norm = fused.scale_clip_step(divisor, 1.0)
+        torch._foreach_div_([p.grad for p in theirs], float(divisor))
+        expected_norm = torch.nn.utils.clip_grad_norm_(theirs, 1.0, error_if_nonfinite=True, foreach=True)
+        reference.step()
+        torch.testing.assert_close(norm[0], expected_norm, rtol=2e-6, atol=0)
+    for a, b in zip(ours[::8], theirs[::8]):
+        close(a, b, 2e-5)
+        close(fused.state[a]["exp_avg_sq"], reference.state[b]["exp_avg_sq"], 2e-5)
