@@ -161,7 +161,7 @@ rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width,
   }
 }
 
-template <typename T, typename W>
+template <typename T, typename W, bool ADD>
 __global__ void __launch_bounds__(kThreads)
 rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
@@ -170,7 +170,8 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
   const uint4* gr = reinterpret_cast<const uint4*>(go + row * width);
   const int64_t chunks = width / 8;
   const bool held = chunks <= kHeld * kThreads;
-  uint4 kept_x[kHeld], kept_g[kHeld];
+  const uint4* extra = ADD ? reinterpret_cast<const uint4*>(add + row * width) : nullptr;
+  uint4 kept_x[kHeld], kept_g[kHeld], kept_a[ADD ? kHeld : 1];
   float sum = 0.f;
   auto project = [&](const uint4& xraw, const uint4& graw, int64_t c) {
     const T* xv = reinterpret_cast<const T*>(&xraw);
@@ -186,6 +187,7 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
       const int64_t c = threadIdx.x + i * kThreads;
       kept_x[i] = c < chunks ? xr[c] : make_uint4(0, 0, 0, 0);
       kept_g[i] = c < chunks ? gr[c] : make_uint4(0, 0, 0, 0);
+      if constexpr (ADD) kept_a[i] = c < chunks ? extra[c] : make_uint4(0, 0, 0, 0);   // in flight with x and g
     }
 #pragma unroll
     for (int i = 0; i < kHeld; ++i) {
@@ -199,12 +201,10 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
   const float inverse = rstd[row];
   const float factor = inverse * inverse * projection;
   uint4* out = reinterpret_cast<uint4*>(gx + row * width);
-  const uint4* extra = add ? reinterpret_cast<const uint4*>(add + row * width) : nullptr;
-  auto emit = [&](const uint4& xraw, const uint4& graw, int64_t c) {
+  auto emit = [&](const uint4& xraw, const uint4& graw, const uint4& other, int64_t c) {
     const T* xv = reinterpret_cast<const T*>(&xraw);
     const T* gv = reinterpret_cast<const T*>(&graw);
-    uint4 result, other = make_uint4(0, 0, 0, 0);
-    if (extra) other = extra[c];
+    uint4 result;
     const T* av = reinterpret_cast<const T*>(&other);
     T* o = reinterpret_cast<T*>(&result);
     float weight[8];
@@ -213,7 +213,7 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
     for (int j = 0; j < 8; ++j) {
       const float gradient = round_to<T>(to_float<T>(gv[j]) * weight[j]);
       float value = inverse * (gradient - to_float<T>(xv[j]) * factor);
-      if (extra) value = __fadd_rn(round_to<T>(value), to_float<T>(av[j]));
+      if constexpr (ADD) value = __fadd_rn(round_to<T>(value), to_float<T>(av[j]));
       o[j] = from_float<T>(value);
     }
     out[c] = result;
@@ -222,10 +222,11 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
 #pragma unroll
     for (int i = 0; i < kHeld; ++i) {
       const int64_t c = threadIdx.x + i * kThreads;
-      if (c < chunks) emit(kept_x[i], kept_g[i], c);
+      if (c < chunks) emit(kept_x[i], kept_g[i], kept_a[ADD ? i : 0], c);
     }
   } else {
-    for (int64_t c = threadIdx.x; c < chunks; c += kThreads) emit(xr[c], gr[c], c);
+    for (int64_t c = threadIdx.x; c < chunks; c += kThreads)
+      emit(xr[c], gr[c], ADD ? extra[c] : make_uint4(0, 0, 0, 0), c);
   }
 }
 
@@ -302,12 +303,18 @@ extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(gx) |
                      reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(add)) & 15) == 0;
   if (vec && weight_dtype == CT_BF16) {
-    rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
+    if (add)
+      rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
+    else
+      rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16, false><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), nullptr, static_cast<__nv_bfloat16*>(gx), width);
     count_launch(false);
     return check_launch("ct_rmsnorm_backward");
   }
   if (vec && weight_dtype == CT_F32) {
-    rms_backward_vec_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
+    if (add)
+      rms_backward_vec_kernel<__nv_bfloat16, float, true><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
+    else
+      rms_backward_vec_kernel<__nv_bfloat16, float, false><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), nullptr, static_cast<__nv_bfloat16*>(gx), width);
     count_launch(false);
     return check_launch("ct_rmsnorm_backward");
   }
