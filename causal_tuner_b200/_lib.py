@@ -23,6 +23,7 @@ SIGNATURES = {
     "ct_launch_count": (_L, []),
     "ct_tcgen05_launch_count": (_L, []),
     "ct_check_device": (_I, [_P]),
+    "ct_selftest_bounded_wait": (_I, [_L, _P]),
     "ct_last_error": (ctypes.c_char_p, []),
     "ct_timing_enable": (_I, [_I]),
     "ct_timing_collect": (_I, [_P, _P, _P]),

@@ -227,8 +227,13 @@ extern "C" int ct_check_device(void* stream) {
   if (value == 0) return CT_OK;
   cudaMemset(g_error_flags[dev], 0, sizeof(int));
   static const char* roles[] = {"", "TMA producer waiting for a free stage", "MMA issuer waiting for a free accumulator",
-                                "MMA issuer waiting for a filled stage", "epilogue waiting for a finished accumulator"};
-  return fail(CT_ERR_DEVICE, "a tcgen05 GEMM CTA gave up on a bounded wait: %s", value >= 1 && value <= 4 ? roles[value] : "?");
+                                "MMA issuer waiting for a filled stage", "epilogue waiting for a finished accumulator",
+                                "the self-test's wait on a barrier that nothing completes"};
+  return fail(CT_ERR_DEVICE, "a tcgen05 GEMM CTA gave up on a bounded wait: %s", value >= 1 && value <= 5 ? roles[value] : "?");
+}
+
+extern "C" int ct_selftest_bounded_wait(int64_t limit_us, void* stream) {
+  return bounded_wait_selftest(limit_us, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,

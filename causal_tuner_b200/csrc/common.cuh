@@ -119,6 +119,8 @@ int gemm_simt(const GemmArgs& g, cudaStream_t stream);
 int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream);
 bool gemm_tcgen05_supported(const GemmArgs& g);
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream);
+// Launches one thread that waits `limit_us` on a barrier nothing completes and reports it (gemm_tc.cu).
+int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream);
 
 // out[i] = (add ? out[i] : 0) + partial[0][i] + partial[1][i] + ... in that order.
 int reduce_partials(const float* partials, int slices, int64_t rows, int64_t cols, int64_t ld_partial,

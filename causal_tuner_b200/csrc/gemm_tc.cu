@@ -127,21 +127,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait. The common case (barrier already complete) is one try_wait; the polling loop with
 // its wall-clock limit lives out of line so that the issue loops stay short. Returns false after
 // kWaitLimitNs, having raised the error flag with `code` (which names the waiting role).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
-                                            int code) {
+__device__ __forceinline__ bool mbar_wait_until(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                int* error_flag, int code, uint64_t limit_ns) {
   const uint64_t start = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - start > kWaitLimitNs) {
+      if (global_timer_ns() - start > limit_ns) {
         *abort_flag = 1;
         atomicCAS(error_flag, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
+                                            int code) {
+  return mbar_wait_until(bar, parity, abort_flag, error_flag, code, kWaitLimitNs);
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_flag,
                                           int code) {
@@ -681,7 +685,34 @@ int sm_count() {
   return count;
 }
 
+// Self-test of the bounded wait: one thread waits on an mbarrier that nothing ever completes, with the
+// GEMM's own wait routine and a short limit, gives up, raises the error flag (code 5) and returns.
+__global__ void bounded_wait_selftest_kernel(int* error_flag, uint64_t limit_ns) {
+  __shared__ uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&barrier), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_wait_until(smem_u32(&barrier), 0, &abort_flag, error_flag, 5, limit_ns);
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&barrier)) : "memory");
+  }
+}
+
 }  // namespace
+
+int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream) {
+  if (limit_us < 1 || limit_us > 100000)
+    return fail(CT_ERR_ARG, "ct_selftest_bounded_wait: limit %lld us (1 .. 100000)", (long long)limit_us);
+  int* flag = device_error_flag();
+  if (!flag) return fail(CT_ERR_CUDA, "ct_selftest_bounded_wait: no device error flag");
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(flag, static_cast<uint64_t>(limit_us) * 1000ull);
+  count_launch(false);
+  return check_launch("ct_selftest_bounded_wait");
+}
 
 bool gemm_tcgen05_supported(const GemmArgs& g) {
   if (g.in_dtype != CT_BF16) return false;

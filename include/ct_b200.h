@@ -70,6 +70,12 @@ CT_API int ct_check_device(void* stream);
  * the reference (it times whole steps only, train.py:219-223). */
 CT_API int ct_timing_enable(int on);
 CT_API int ct_timing_collect(double* total_ms, double* total_flops, int64_t* launches);
+/* Self-test of the failure path, no counterpart in the reference: enqueues one thread that waits
+ * `limit_us` microseconds (1 .. 100000) on an mbarrier that nothing ever completes, using the
+ * GEMM's bounded wait; it gives up, raises the per-device error flag and returns. The next
+ * ct_check_device on that device then returns CT_ERR_DEVICE and clears the flag; the context
+ * stays usable. Nothing faults, traps or spins without a limit. */
+CT_API int ct_selftest_bounded_wait(int64_t limit_us, void* stream);
 /* Text of the most recent CT_ERR_* on the calling thread (static storage). */
 CT_API const char* ct_last_error(void);
 
