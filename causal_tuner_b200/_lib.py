@@ -47,6 +47,9 @@ SIGNATURES = {
     "ct_rmsnorm_forward": (_I, [_P, _P, _P, _P, _L, _L, ctypes.c_float, _I, _I, _P]),
     "ct_rmsnorm_backward": (_I, [_P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
     "ct_rmsnorm_backward_add": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
+    "ct_rmsnorm_backward_from_output": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P]),
+    "ct_rmsnorm_weight_gradient": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _P]),
+    "ct_rmsnorm_weight_reduce": (_I, [_P, _L, _L, _P, _I, _P]),
     "ct_weighted_ce": (_I, [_P, _P, _P, _P, _L, _L, _I, _I, _P]),
     "ct_nf4_encode": (_I, [_P, _L, _I, _I, _P, _P, _P, _P]),
     "ct_nf4_nest": (_I, [_P, _L, _I, _P, _P, _P, _P, _P]),

@@ -60,7 +60,9 @@ rms_forward_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width, flo
 
 // gx = rstd * (g - x * rstd^2 * mean(g * x)) with g = round(go * round(w)); gx may alias go.
 // With `add`: gx = round(gx) + add, the sum autograd would form when x also feeds a residual path.
-template <typename T, typename W>
+// FROM_OUTPUT: `x` holds the norm's OUTPUT y instead of its input; the normalised row is rebuilt as
+// n = y / round(w) and gx = rstd * (g - n * mean(g * n)) (kernels/core_cuda.py:56-59).
+template <typename T, typename W, bool FROM_OUTPUT>
 __global__ void __launch_bounds__(kThreads)
 rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
@@ -69,15 +71,18 @@ rms_backward_kernel(const T* x, const W* w, const float* rstd, const T* go, cons
   const T* gr = go + row * width;
   float sum = 0.f;
   for (int64_t c = threadIdx.x; c < width; c += kThreads) {
-    const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
-    sum += gradient * to_float<T>(xr[c]);
+    const float weight = round_to<T>(to_float<W>(w[c]));
+    const float gradient = round_to<T>(to_float<T>(gr[c]) * weight);
+    sum += gradient * (FROM_OUTPUT ? __fdividef(to_float<T>(xr[c]), weight) : to_float<T>(xr[c]));
   }
   const float projection = block_sum(sum, scratch) / static_cast<float>(width);
   const float inverse = rstd[row];
   T* out = gx + row * width;
   for (int64_t c = threadIdx.x; c < width; c += kThreads) {
-    const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
-    float value = inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection));
+    const float weight = round_to<T>(to_float<W>(w[c]));
+    const float gradient = round_to<T>(to_float<T>(gr[c]) * weight);
+    float value = FROM_OUTPUT ? inverse * (gradient - __fdividef(to_float<T>(xr[c]), weight) * projection)
+                              : inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection));
     if (add) value = __fadd_rn(round_to<T>(value), to_float<T>(add[row * width + c]));
     out[c] = from_float<T>(value);
   }
@@ -161,7 +166,7 @@ rms_forward_vec_kernel(const T* x, const W* w, T* y, float* rstd, int64_t width,
   }
 }
 
-template <typename T, typename W, bool ADD>
+template <typename T, typename W, bool ADD, bool FROM_OUTPUT>
 __global__ void __launch_bounds__(kThreads, ADD ? 4 : 6)   // 40 registers without spills (plain), 64 with the add
 rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, const T* add, T* gx, int64_t width) {
   __shared__ float scratch[kThreads / 32];
@@ -179,7 +184,9 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
     float weight[8];
     load_weights<T, W>(w, c, weight);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sum += round_to<T>(to_float<T>(gv[j]) * weight[j]) * to_float<T>(xv[j]);
+    for (int j = 0; j < 8; ++j)
+      sum += round_to<T>(to_float<T>(gv[j]) * weight[j]) *
+             (FROM_OUTPUT ? __fdividef(to_float<T>(xv[j]), weight[j]) : to_float<T>(xv[j]));
   };
   if (held) {
 #pragma unroll
@@ -212,7 +219,8 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float gradient = round_to<T>(to_float<T>(gv[j]) * weight[j]);
-      float value = inverse * (gradient - to_float<T>(xv[j]) * factor);
+      float value = FROM_OUTPUT ? inverse * (gradient - __fdividef(to_float<T>(xv[j]), weight[j]) * projection)
+                                : inverse * (gradient - to_float<T>(xv[j]) * factor);
       if constexpr (ADD) value = __fadd_rn(round_to<T>(value), to_float<T>(av[j]));
       o[j] = from_float<T>(value);
     }
@@ -227,6 +235,66 @@ rms_backward_vec_kernel(const T* x, const W* w, const float* rstd, const T* go, 
   } else {
     for (int64_t c = threadIdx.x; c < chunks; c += kThreads)
       emit(xr[c], gr[c], ADD ? extra[c] : make_uint4(0, 0, 0, 0), c);
+  }
+}
+
+// Trainable norm weight (kernels/core_cuda.py:43-91): a CTA walks `rows_per_group` consecutive rows; per row it
+// optionally writes the input gradient (never in reconstruction mode, never over `go`) and adds
+// go * round(x * rstd) to one fp32 sum per column. The sums of a group go to partials[group, :];
+// rms_weight_reduce_kernel then adds the groups in index order. Rows are visited in order and every
+// column belongs to one thread, so the result does not depend on scheduling.
+constexpr size_t kWeightGradSharedLimit = 200 * 1024;
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads)
+rms_weight_gradient_kernel(const T* x, const W* w, const float* rstd, const T* go, T* gx, float* partials, int64_t rows,
+                           int64_t width, int64_t rows_per_group, int in_shared) {
+  extern __shared__ float column_sums[];
+  __shared__ float scratch[kThreads / 32];
+  const int64_t group = blockIdx.x;
+  float* sums = in_shared ? column_sums : partials + group * width;
+  for (int64_t c = threadIdx.x; c < width; c += kThreads) sums[c] = 0.f;
+  const int64_t first = group * rows_per_group;
+  const int64_t last = first + rows_per_group < rows ? first + rows_per_group : rows;
+  for (int64_t row = first; row < last; ++row) {
+    const T* xr = x + row * width;
+    const T* gr = go + row * width;
+    const float inverse = rstd[row];
+    if (gx) {
+      float sum = 0.f;
+      for (int64_t c = threadIdx.x; c < width; c += kThreads)
+        sum += round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c]))) * to_float<T>(xr[c]);
+      const float projection = block_sum(sum, scratch) / static_cast<float>(width);
+      T* out = gx + row * width;
+      for (int64_t c = threadIdx.x; c < width; c += kThreads) {
+        const float gradient = round_to<T>(to_float<T>(gr[c]) * round_to<T>(to_float<W>(w[c])));
+        out[c] = from_float<T>(inverse * (gradient - to_float<T>(xr[c]) * (inverse * inverse * projection)));
+      }
+    }
+    for (int64_t c = threadIdx.x; c < width; c += kThreads)
+      sums[c] += to_float<T>(gr[c]) * round_to<T>(to_float<T>(xr[c]) * inverse);
+  }
+  if (in_shared) {
+    float* out = partials + group * width;
+    for (int64_t c = threadIdx.x; c < width; c += kThreads) out[c] = sums[c];
+  }
+}
+
+// dw[c] = sum over groups (in index order within each of 8 interleaved lanes, lanes then added in order).
+template <typename W>
+__global__ void rms_weight_reduce_kernel(const float* partials, int64_t groups, int64_t width, W* dw) {
+  __shared__ float lanes[8][33];
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
+  float sum = 0.f;
+  if (c < width)
+    for (int64_t g = threadIdx.y; g < groups; g += 8) sum += partials[g * width + c];
+  lanes[threadIdx.y][threadIdx.x] = sum;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < width) {
+    float total = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) total += lanes[l][threadIdx.x];
+    dw[c] = from_float<W>(total);
   }
 }
 
@@ -246,12 +314,14 @@ weighted_ce_kernel(T* logits, const int64_t* targets, const float* weights, floa
   const float lse = maximum + logf(block_sum(sum, scratch));
   const int64_t target = targets[row];
   const float weight = weights[row];
-  const float selected = to_float<T>(lr[target]);
+  // A target outside [0, vocab) (an ignore index on a zero-weight row) selects nothing: no read, no one-hot term.
+  const bool target_ok = target >= 0 && target < vocab;
+  const float selected = target_ok ? to_float<T>(lr[target]) : 0.f;
   __syncthreads();  // every thread has read the target logit before anyone overwrites it
   if (threadIdx.x == 0) loss[row] = weight * (lse - selected);
   if (gradient) {
     for (int64_t c = threadIdx.x; c < vocab; c += kThreads) {
-      const float derivative = (expf(to_float<T>(lr[c]) - lse) - (c == target ? 1.f : 0.f)) * weight;
+      const float derivative = (expf(to_float<T>(lr[c]) - lse) - (target_ok && c == target ? 1.f : 0.f)) * weight;
       lr[c] = from_float<T>(derivative);
     }
   }
@@ -291,9 +361,10 @@ extern "C" int ct_rmsnorm_forward(const void* x, const void* w, void* y, float* 
   return check_launch("ct_rmsnorm_forward");
 }
 
-extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float* rstd, const void* go, const void* add,
-                                       void* gx, int64_t rows, int64_t width, int dtype, int weight_dtype,
-                                       void* stream) {
+namespace {
+
+int rms_backward_launch(const void* x, const void* w, const float* rstd, const void* go, const void* add, void* gx,
+                        int64_t rows, int64_t width, int dtype, int weight_dtype, bool from_output, void* stream) {
   if (rows < 0 || width <= 0) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: rows=%lld width=%lld", (long long)rows, (long long)width);
   if (rows == 0) return CT_OK;
   if (!x || !w || !rstd || !go || !gx) return fail(CT_ERR_ARG, "ct_rmsnorm_backward: null pointer");
@@ -302,23 +373,30 @@ extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float
   const bool vec = dtype == CT_BF16 && width % 8 == 0 &&
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(gx) |
                      reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(add)) & 15) == 0;
-  if (vec && weight_dtype == CT_BF16) {
-    if (add)
-      rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16, true><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
-    else
-      rms_backward_vec_kernel<__nv_bfloat16, __nv_bfloat16, false><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(go), nullptr, static_cast<__nv_bfloat16*>(gx), width);
+  using bf16 = __nv_bfloat16;
+#define CT_RMS_BWD_VEC(W, ADD, OUT)                                                                                   \
+  rms_backward_vec_kernel<bf16, W, ADD, OUT><<<grid, kThreads, 0, s>>>(                                               \
+      static_cast<const bf16*>(x), static_cast<const W*>(w), rstd, static_cast<const bf16*>(go),                      \
+      static_cast<const bf16*>(add), static_cast<bf16*>(gx), width)
+  if (vec && (weight_dtype == CT_BF16 || weight_dtype == CT_F32)) {
+    const bool narrow = weight_dtype == CT_BF16;
+    if (from_output && add) { if (narrow) CT_RMS_BWD_VEC(bf16, true, true); else CT_RMS_BWD_VEC(float, true, true); }
+    else if (from_output) { if (narrow) CT_RMS_BWD_VEC(bf16, false, true); else CT_RMS_BWD_VEC(float, false, true); }
+    else if (add)    { if (narrow) CT_RMS_BWD_VEC(bf16, true, false); else CT_RMS_BWD_VEC(float, true, false); }
+    else             { if (narrow) CT_RMS_BWD_VEC(bf16, false, false); else CT_RMS_BWD_VEC(float, false, false); }
     count_launch(false);
     return check_launch("ct_rmsnorm_backward");
   }
-  if (vec && weight_dtype == CT_F32) {
-    if (add)
-      rms_backward_vec_kernel<__nv_bfloat16, float, true><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), static_cast<const __nv_bfloat16*>(add), static_cast<__nv_bfloat16*>(gx), width);
-    else
-      rms_backward_vec_kernel<__nv_bfloat16, float, false><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(w), rstd, static_cast<const __nv_bfloat16*>(go), nullptr, static_cast<__nv_bfloat16*>(gx), width);
-    count_launch(false);
-    return check_launch("ct_rmsnorm_backward");
-  }
-#define CT_RMS_BWD(T, W) rms_backward_kernel<T, W><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<const T*>(go), static_cast<const T*>(add), static_cast<T*>(gx), width)
+#undef CT_RMS_BWD_VEC
+#define CT_RMS_BWD(T, W)                                                                                              \
+  do {                                                                                                                \
+    if (from_output)                                                                                                  \
+      rms_backward_kernel<T, W, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w),   \
+          rstd, static_cast<const T*>(go), static_cast<const T*>(add), static_cast<T*>(gx), width);                   \
+    else                                                                                                              \
+      rms_backward_kernel<T, W, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<const W*>(w),  \
+          rstd, static_cast<const T*>(go), static_cast<const T*>(add), static_cast<T*>(gx), width);                   \
+  } while (0)
   if (dtype == CT_BF16 && weight_dtype == CT_BF16) CT_RMS_BWD(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == CT_BF16 && weight_dtype == CT_F32) CT_RMS_BWD(__nv_bfloat16, float);
   else if (dtype == CT_F32 && weight_dtype == CT_F32) CT_RMS_BWD(float, float);
@@ -329,9 +407,77 @@ extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float
   return check_launch("ct_rmsnorm_backward");
 }
 
+}  // namespace
+
+extern "C" int ct_rmsnorm_backward_add(const void* x, const void* w, const float* rstd, const void* go, const void* add,
+                                       void* gx, int64_t rows, int64_t width, int dtype, int weight_dtype,
+                                       void* stream) {
+  return rms_backward_launch(x, w, rstd, go, add, gx, rows, width, dtype, weight_dtype, false, stream);
+}
+
 extern "C" int ct_rmsnorm_backward(const void* x, const void* w, const float* rstd, const void* go, void* gx,
                                    int64_t rows, int64_t width, int dtype, int weight_dtype, void* stream) {
-  return ct_rmsnorm_backward_add(x, w, rstd, go, nullptr, gx, rows, width, dtype, weight_dtype, stream);
+  return rms_backward_launch(x, w, rstd, go, nullptr, gx, rows, width, dtype, weight_dtype, false, stream);
+}
+
+extern "C" int ct_rmsnorm_backward_from_output(const void* y, const void* w, const float* rstd, const void* go,
+                                               const void* add, void* gx, int64_t rows, int64_t width, int dtype,
+                                               int weight_dtype, void* stream) {
+  return rms_backward_launch(y, w, rstd, go, add, gx, rows, width, dtype, weight_dtype, true, stream);
+}
+
+extern "C" int ct_rmsnorm_weight_gradient(const void* x, const void* w, const float* rstd, const void* go, void* gx,
+                                          float* partials, int64_t rows, int64_t width, int64_t rows_per_group,
+                                          int dtype, int weight_dtype, void* stream) {
+  if (rows < 0 || width <= 0 || rows_per_group <= 0)
+    return fail(CT_ERR_ARG, "ct_rmsnorm_weight_gradient: rows=%lld width=%lld rows_per_group=%lld", (long long)rows,
+                (long long)width, (long long)rows_per_group);
+  if (rows == 0) return CT_OK;
+  if (!x || !w || !rstd || !go || !partials) return fail(CT_ERR_ARG, "ct_rmsnorm_weight_gradient: null pointer");
+  if (gx && gx == go) return fail(CT_ERR_ARG, "ct_rmsnorm_weight_gradient: gx must not alias go (go is read after gx is written)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t groups = (rows + rows_per_group - 1) / rows_per_group;
+  if (groups > 0x7fffffff) return fail(CT_ERR_ARG, "ct_rmsnorm_weight_gradient: %lld groups", (long long)groups);
+  // Column sums live in shared memory when the row fits (any hidden width in practice), else in the
+  // global partial row itself; either way every column has exactly one owner thread.
+  const size_t wanted = static_cast<size_t>(width) * sizeof(float);
+  const bool in_shared = wanted <= kWeightGradSharedLimit;
+  const size_t smem = in_shared ? wanted : 0;
+#define CT_RMS_WG(T, W)                                                                                               \
+  do {                                                                                                                \
+    auto kernel = rms_weight_gradient_kernel<T, W>;                                                                   \
+    if (smem > 48 * 1024 &&                                                                                           \
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) \
+      return fail(CT_ERR_CUDA, "ct_rmsnorm_weight_gradient: cannot opt in to %zu bytes of shared memory", smem);      \
+    kernel<<<static_cast<unsigned>(groups), kThreads, smem, s>>>(static_cast<const T*>(x), static_cast<const W*>(w), \
+        rstd, static_cast<const T*>(go), static_cast<T*>(gx), partials, rows, width, rows_per_group, in_shared ? 1 : 0); \
+  } while (0)
+  if (dtype == CT_BF16 && weight_dtype == CT_BF16) CT_RMS_WG(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == CT_BF16 && weight_dtype == CT_F32) CT_RMS_WG(__nv_bfloat16, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_F32) CT_RMS_WG(float, float);
+  else if (dtype == CT_F32 && weight_dtype == CT_BF16) CT_RMS_WG(float, __nv_bfloat16);
+  else return fail(CT_ERR_ARG, "ct_rmsnorm_weight_gradient: dtype %d / %d", dtype, weight_dtype);
+#undef CT_RMS_WG
+  count_launch(false);
+  return check_launch("ct_rmsnorm_weight_gradient");
+}
+
+extern "C" int ct_rmsnorm_weight_reduce(const float* partials, int64_t groups, int64_t width, void* dw, int weight_dtype,
+                                        void* stream) {
+  if (groups < 0 || width <= 0) return fail(CT_ERR_ARG, "ct_rmsnorm_weight_reduce: groups=%lld width=%lld", (long long)groups, (long long)width);
+  if (!dw || (groups > 0 && !partials)) return fail(CT_ERR_ARG, "ct_rmsnorm_weight_reduce: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((width + 31) / 32);
+  if (weight_dtype == CT_F32)
+    rms_weight_reduce_kernel<float><<<grid, dim3(32, 8), 0, s>>>(partials, groups, width, static_cast<float*>(dw));
+  else if (weight_dtype == CT_BF16)
+    rms_weight_reduce_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, s>>>(partials, groups, width, static_cast<__nv_bfloat16*>(dw));
+  else if (weight_dtype == CT_F16)
+    rms_weight_reduce_kernel<__half><<<grid, dim3(32, 8), 0, s>>>(partials, groups, width, static_cast<__half*>(dw));
+  else
+    return fail(CT_ERR_ARG, "ct_rmsnorm_weight_reduce: dtype %d", weight_dtype);
+  count_launch(false);
+  return check_launch("ct_rmsnorm_weight_reduce");
 }
 
 extern "C" int ct_weighted_ce(void* logits, const int64_t* targets, const float* weights, float* loss, int64_t rows,

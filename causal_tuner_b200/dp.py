@@ -73,6 +73,83 @@ class GradientExchange:
         self._inflight = []
 
 
+class BucketPlan:
+    """Fixed assignment of a trainer's gradient tensors to flat fp32 buckets.
+
+    Tensors are taken in REVERSE parameter order - the order in which a backward pass finishes
+    them - and packed into buckets of at least `bucket_bytes`. The plan depends on the shapes
+    only, so every rank builds the same one, and because `PlannedExchange` launches buckets
+    strictly in plan order the sequence of collectives is the same on every rank whatever
+    happens to one of them. The flat buffers are allocated once and reused by every update."""
+
+    def __init__(self, shapes, device, bucket_bytes=64 << 20):
+        if bucket_bytes <= 0:
+            raise ValueError("bucket_bytes must be positive")
+        self.shapes = [tuple(shape) for shape in shapes]
+        self.slot = [None] * len(self.shapes)          # tensor index -> (bucket, offset, count)
+        self.members, sizes = [[]], [0]
+        for index in reversed(range(len(self.shapes))):
+            count = 1
+            for extent in self.shapes[index]:
+                count *= extent
+            if sizes[-1] * 4 >= bucket_bytes:
+                self.members.append([])
+                sizes.append(0)
+            self.slot[index] = (len(self.members) - 1, sizes[-1], count)
+            self.members[-1].append(index)
+            sizes[-1] += count
+        self.buffers = [torch.empty(size, device=device, dtype=torch.float32) for size in sizes]
+
+    def view(self, index):
+        bucket, offset, count = self.slot[index]
+        return self.buffers[bucket][offset:offset + count].view(self.shapes[index])
+
+
+class PlannedExchange:
+    """One update's SUM all-reduce over a `BucketPlan`.
+
+    `add(index, gradient)` copies a finished gradient into its slot; a bucket is all-reduced
+    (asynchronously) as soon as it is complete AND every earlier bucket has been launched.
+    `finish(extra)` launches what is left, all-reduces the small `extra` tensor last (loss,
+    weight and a failure flag travel there), waits, and returns the views that now hold the sums.
+    `flush()` is for a rank whose update failed: it launches every bucket not yet launched,
+    whatever it contains, so that the peers' collectives complete and they can read the flag."""
+
+    def __init__(self, plan, group=None):
+        self.plan, self.group = plan, group
+        self._missing = [len(members) for members in plan.members]
+        self._next, self._inflight = 0, []
+        self.collectives = 0
+
+    def add(self, index, gradient):
+        bucket = self.plan.slot[index][0]
+        self.plan.view(index).copy_(gradient)
+        self._missing[bucket] -= 1
+        self._advance()
+
+    def _advance(self, force=False):
+        while self._next < len(self._missing) and (force or self._missing[self._next] <= 0):
+            work = dist.all_reduce(self.plan.buffers[self._next], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            self._inflight.append(work)
+            self.collectives += 1
+            self._next += 1
+
+    def flush(self):
+        self._advance(force=True)
+
+    def finish(self, extra=None):
+        if any(self._missing[self._next:]):
+            raise RuntimeError("gradient exchange finished before every gradient was added")
+        self._advance()
+        if extra is not None:
+            self._inflight.append(dist.all_reduce(extra, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            self.collectives += 1
+        for work in self._inflight:
+            work.wait()
+        self._inflight = []
+        return [self.plan.view(index) for index in range(len(self.plan.shapes))]
+
+
 def exchange_gradients(gradients, group=None, bucket_bytes=64 << 20):
     """In-place SUM all-reduce of `gradients` across the ranks of `group`; returns the number of collectives."""
     exchange = GradientExchange(group, bucket_bytes)

@@ -75,49 +75,71 @@ def position_values(positions, inverse, dtype):
     return cosine, sine
 
 
+def _sm_count(device):
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
 class RMS(torch.autograd.Function):
-    """y = round(x * rstd) * round(w) for a FROZEN weight (kernels/core_cuda.py:94-131).
+    """y = round(x * rstd) * round(w) (kernels/core_cuda.py:94-131).
 
     `reuse_grad=True` writes the input gradient over the upstream gradient, which the caller
     guarantees to be a private tensor (the projection operators return fresh input gradients).
-    The output-reconstruction mode of the reference is a memory option and is not implemented:
-    `reconstruct` is accepted and ignored, the input is saved.
+    `reconstruct=True` saves the OUTPUT instead of the input - the projection that follows keeps it
+    anyway - and the backward pass rebuilds the normalised row as y / w. Both belong to frozen
+    pre-norms and are ignored for a trainable weight, whose fp32 gradient is summed over at most
+    4 x SM-count row groups in a fixed order.
     """
 
     @staticmethod
     def forward(ctx, x, weight, eps, reuse_grad=False, reconstruct=False):
         _lib.require_cuda(x, weight)
-        if weight.requires_grad:
-            raise NotImplementedError("causal_tuner_b200 covers frozen RMSNorm weights (adapter training) only")
-        ctx.reuse_grad = reuse_grad
+        ctx.reuse_grad = reuse_grad and not weight.requires_grad
+        ctx.reconstruct = reconstruct and not weight.requires_grad
         x = x.contiguous()
         output = torch.empty_like(x)
         width = x.shape[-1]
         rows = x.numel() // width
         rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
-        weight = weight.contiguous()
+        weight_values = weight.contiguous()
         with _lib.on_device(x):
             _lib.check(_lib.load().ct_rmsnorm_forward(
-                x.data_ptr(), weight.data_ptr(), output.data_ptr(), rstd.data_ptr(), rows, width, float(eps),
+                x.data_ptr(), weight_values.data_ptr(), output.data_ptr(), rstd.data_ptr(), rows, width, float(eps),
                 _lib.code_of(x.dtype), _lib.code_of(weight.dtype), _lib.stream_of(x)))
-        ctx.save_for_backward(x, weight, rstd)
+        ctx.save_for_backward(output if ctx.reconstruct else x, weight, rstd)
         return output
 
     @staticmethod
     def backward(ctx, grad):
         x, weight, rstd = ctx.saved_tensors
-        if not ctx.needs_input_grad[0]:
-            return None, None, None, None, None
         grad = grad.contiguous()
         if grad.dtype != x.dtype:
             grad = grad.to(x.dtype)
-        result = grad if ctx.reuse_grad else torch.empty_like(x)
-        width = x.shape[-1]
+        want_dx, want_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        result = (grad if ctx.reuse_grad else torch.empty_like(x)) if want_dx else None
+        width, rows = x.shape[-1], rstd.numel()
+        library = _lib.load()
+        codes = (_lib.code_of(x.dtype), _lib.code_of(weight.dtype))
+        weight_values = weight.contiguous()
+        dw = None
         with _lib.on_device(x):
-            _lib.check(_lib.load().ct_rmsnorm_backward(
-                x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), result.data_ptr(),
-                x.numel() // width, width, _lib.code_of(x.dtype), _lib.code_of(weight.dtype), _lib.stream_of(x)))
-        return result, None, None, None, None
+            stream = _lib.stream_of(x)
+            if want_dw:
+                dw = torch.empty_like(weight_values)
+                groups = min(rows, 4 * _sm_count(x.device))
+                per_group = -(-rows // groups) if groups else 1
+                groups = -(-rows // per_group)
+                partials = torch.empty((groups, width), device=x.device, dtype=torch.float32)
+                if rows:
+                    _lib.check(library.ct_rmsnorm_weight_gradient(
+                        x.data_ptr(), weight_values.data_ptr(), rstd.data_ptr(), grad.data_ptr(), _lib.pointer(result),
+                        partials.data_ptr(), rows, width, per_group, *codes, stream))
+                _lib.check(library.ct_rmsnorm_weight_reduce(partials.data_ptr(), groups, width, dw.data_ptr(), codes[1],
+                                                            stream))
+            elif want_dx and rows:
+                entry = library.ct_rmsnorm_backward_from_output if ctx.reconstruct else library.ct_rmsnorm_backward_add
+                _lib.check(entry(x.data_ptr(), weight_values.data_ptr(), rstd.data_ptr(), grad.data_ptr(), None,
+                                 result.data_ptr(), rows, width, *codes, stream))
+        return result, dw, None, None, None
 
 
 class RMSWithShortcut(torch.autograd.Function):
@@ -126,13 +148,14 @@ class RMSWithShortcut(torch.autograd.Function):
     feeds both and autograd adds the two gradients with a separate kernel). Here the backward pass
     receives both gradients and forms round(round(RMS gradient) + shortcut gradient) inside the
     RMSNorm kernel, over the upstream gradient of the normalised branch, which the projection
-    operators hand over as a private tensor. Frozen weight only."""
+    operators hand over as a private tensor. Frozen weight only; `reconstruct` saves the output
+    instead of x, as in `RMS`."""
 
     @staticmethod
-    def forward(ctx, x, weight, eps):
+    def forward(ctx, x, weight, eps, reconstruct=False):
         _lib.require_cuda(x, weight)
         if weight.requires_grad:
-            raise NotImplementedError("causal_tuner_b200 covers frozen RMSNorm weights (adapter training) only")
+            raise ValueError("RMSWithShortcut is for frozen norm weights; use RMS for a trainable one")
         source = x.contiguous()
         output = torch.empty_like(source)
         width = source.shape[-1]
@@ -143,27 +166,29 @@ class RMSWithShortcut(torch.autograd.Function):
             _lib.check(_lib.load().ct_rmsnorm_forward(
                 source.data_ptr(), weight.data_ptr(), output.data_ptr(), rstd.data_ptr(), rows, width, float(eps),
                 _lib.code_of(source.dtype), _lib.code_of(weight.dtype), _lib.stream_of(source)))
-        ctx.save_for_backward(source, weight, rstd)
+        ctx.reconstruct = bool(reconstruct)
+        ctx.save_for_backward(output if ctx.reconstruct else source, weight, rstd)
         return output, x
 
     @staticmethod
     def backward(ctx, grad, shortcut_grad):
         x, weight, rstd = ctx.saved_tensors
         if not ctx.needs_input_grad[0]:
-            return None, None, None
+            return None, None, None, None
         if grad is None:
-            return shortcut_grad, None, None
+            return shortcut_grad, None, None, None
         grad = grad.contiguous()
         if grad.dtype != x.dtype:
             grad = grad.to(x.dtype)
         fused = shortcut_grad is not None and shortcut_grad.dtype == x.dtype and shortcut_grad.shape == x.shape
         extra = shortcut_grad.contiguous() if fused else None
         width = x.shape[-1]
+        library = _lib.load()
+        entry = library.ct_rmsnorm_backward_from_output if ctx.reconstruct else library.ct_rmsnorm_backward_add
         with _lib.on_device(x):
-            _lib.check(_lib.load().ct_rmsnorm_backward_add(
-                x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), _lib.pointer(extra),
-                grad.data_ptr(), x.numel() // width, width, _lib.code_of(x.dtype), _lib.code_of(weight.dtype),
-                _lib.stream_of(x)))
+            _lib.check(entry(x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), grad.data_ptr(), _lib.pointer(extra),
+                             grad.data_ptr(), x.numel() // width, width, _lib.code_of(x.dtype),
+                             _lib.code_of(weight.dtype), _lib.stream_of(x)))
         if shortcut_grad is not None and not fused:
             grad = grad + shortcut_grad
-        return grad, None, None
+        return grad, None, None, None

@@ -1,8 +1,11 @@
-"""`Runtime` and the SwiGLU `MLP` block of the decoder (the callers of the two fused operators).
+"""The decoder around the two fused operators: `Runtime`, `RMSNorm`, `Attention`, `MLP`, `Layer`,
+`CausalLM`.
 
-Drop-in for the parts of the reference's modeling/model.py that sit on the projection / MLP
-path: `Runtime` (:18-36) and `MLP` (:111-139). The decoder around them (attention, norms,
-embedding, checkpoint policy) is outside this package.
+Class names, constructor arguments and attributes are those of the reference's modeling/model.py
+(:18-279) because callers and checkpoints address them by name; the bodies call this package's
+operators only. Adapter training is covered (rank > 0, frozen base weights); the execution policy
+is explicit in `Runtime` (layer checkpointing on or off, an MLP activation-cache byte budget, kept
+low-rank inputs) instead of being derived from free memory, and nothing is offloaded.
 """
 
 from dataclasses import dataclass
@@ -81,24 +84,50 @@ class MLP(nn.Module):
 # always recomputes gate/up unless `layer.mlp.cache_intermediates` is set, nothing is offloaded.
 
 class RMSNorm(nn.Module):
+    """RMS normalisation with a weight per channel (modeling/model.py:39-66 of the reference).
+
+    A frozen bf16 norm that hands its input gradient buffer back (`reuse_grad`) also uses the
+    output-reconstruction mode when every weight magnitude lies in [1/256, 256]: the backward pass
+    then needs the output only, which the following projection keeps anyway."""
+
     def __init__(self, size, eps, dtype, device):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(size, dtype=dtype, device=device))
         self.eps = eps
+        self._reconstruction_cache = None
+
+    def _can_reconstruct(self, dtype):
+        weight = self.weight
+        if dtype != torch.bfloat16 or weight.requires_grad or torch.is_inference(weight):
+            return False
+        key = (weight.data_ptr(), weight._version, dtype)
+        cached = self._reconstruction_cache
+        if cached is None or cached[0] != key:
+            if torch.cuda.is_current_stream_capturing():
+                return False            # the check below reads a value back to the host
+            magnitude = weight.detach().to(dtype).abs()
+            cached = self._reconstruction_cache = (key, bool(((magnitude >= 1 / 256) & (magnitude <= 256)).all()))
+        return cached[1]
+
+    def _require_cuda(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
 
     def forward(self, x, *, reuse_grad=False):
         from ..kernels.core_cuda import RMS
-        if not x.is_cuda:
-            raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
-        return RMS.apply(x, self.weight, self.eps, reuse_grad, False)
+        self._require_cuda(x)
+        reconstruct = reuse_grad and torch.is_grad_enabled() and self._can_reconstruct(x.dtype)
+        return RMS.apply(x, self.weight, self.eps, reuse_grad, reconstruct)
 
     def with_shortcut(self, x):
-        """(norm(x), x) for `x + block(norm(x))`; the two gradients of x are summed inside the norm's
-        backward kernel instead of by a separate add."""
-        from ..kernels.core_cuda import RMSWithShortcut
-        if not x.is_cuda:
-            raise RuntimeError("causal_tuner_b200.RMSNorm runs on CUDA tensors only; there is no CPU path")
-        return RMSWithShortcut.apply(x, self.weight, self.eps)
+        """(norm(x), x) for `x + block(norm(x))`; with a frozen weight the two gradients of x are summed
+        inside the norm's backward kernel instead of by a separate add."""
+        from ..kernels.core_cuda import RMS, RMSWithShortcut
+        self._require_cuda(x)
+        if self.weight.requires_grad:
+            return RMS.apply(x, self.weight, self.eps, False, False), x
+        reconstruct = torch.is_grad_enabled() and self._can_reconstruct(x.dtype)
+        return RMSWithShortcut.apply(x, self.weight, self.eps, reconstruct)
 
 
 class Attention(nn.Module):
@@ -158,8 +187,10 @@ class Decoder(nn.Module):
 
 
 class CausalLM(nn.Module):
-    """Adapter-training decoder: every base weight, bias, norm, embedding and the head are frozen;
-    lora_A / lora_B of the seven projections per layer train in `runtime.train_dtype`."""
+    """Adapter-training decoder: base weights, biases and norms are frozen; lora_A / lora_B of the
+    seven projections per layer train in `runtime.train_dtype`, and so do the embedding and the head
+    when `runtime.train_embed` / `runtime.train_head` ask for it (modeling/model.py:185-193 of the
+    reference)."""
 
     def __init__(self, config, runtime, device=None):
         super().__init__()
@@ -171,7 +202,8 @@ class CausalLM(nn.Module):
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=runtime.base_dtype,
                                  device=device)
         for name, param in self.named_parameters():
-            trainable = "lora_" in name
+            trainable = ("lora_" in name or ("embed_tokens" in name and runtime.train_embed)
+                         or (name.startswith("lm_head") and runtime.train_head))
             param.requires_grad_(trainable)
             if trainable:
                 param.data = param.data.to(runtime.train_dtype)

@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .dp import GradientExchange
+from .dp import BucketPlan, PlannedExchange
 from .optim import FusedAdamW
 from .kernels.loss import active_rows, projection_loss
 from .segments import prediction_targets
@@ -37,6 +37,7 @@ class Trainer:
         self.model, self.optimizer, self.device = model, optimizer, device
         self.max_grad_norm, self.loss_token_budget = max_grad_norm, loss_token_budget
         self.group, self.bucket_bytes = group, bucket_bytes
+        self._plan = None
 
     def update(self, batches, *, learning_rate=None):
         self.model.train()
@@ -47,53 +48,70 @@ class Trainer:
         batches = list(batches)
         parameters = [p for group in self.optimizer.param_groups for p in group["params"]]
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
-        exchange, hooks = None, []
-        for index, batch in enumerate(batches):
-            if distributed and index == len(batches) - 1:
-                # Last micro-batch: every gradient is final as soon as autograd has accumulated it, so
-                # it joins a bucket right away and full buckets are all-reduced under the rest of the
-                # backward pass.
-                exchange = GradientExchange(self.group, self.bucket_bytes)
-                wide = {}
-
-                def ready(param, exchange=exchange, wide=wide):
-                    if param.grad.dtype == torch.float32:
-                        exchange.add(param.grad)
-                    else:                              # 16-bit training dtype: exchange in fp32, round once
-                        wide[param] = param.grad.float()
-                        exchange.add(wide[param])
-                hooks = [p.register_post_accumulate_grad_hook(ready) for p in parameters]
-            microbatches += 1
-            valid_tokens += int(batch["attention_mask"].sum())
-            targets, weights = prediction_targets(batch)
-            rows = active_rows(weights, self.device)
-            targets, weights = targets.to(self.device), weights.to(self.device)
-            batch = {k: v.to(self.device) if torch.is_tensor(v) else v for k, v in batch.items()}
-            hidden = self.model(batch)
-            loss = projection_loss(hidden, self.model.lm_head.weight, targets, weights,
-                                   token_budget=self.loss_token_budget,
-                                   compute_dtype=self.model.runtime.compute_dtype, reuse_hidden=True, rows=rows)
-            del hidden
-            loss.backward()
-            total_loss.add_(loss.detach())
-            total_weight.add_(weights.sum())
-            del loss, batch
-        if microbatches == 0:
-            raise ValueError("An optimizer update requires at least one microbatch")
-        for hook in hooks:
-            hook.remove()
-        for param in parameters:
-            if param.grad is None:
-                raise RuntimeError("A trainable parameter has no gradient; the graph is disconnected")
+        exchange, hooks, failure = None, [], None
+        if distributed:
+            shapes = [tuple(p.shape) for p in parameters]
+            if self._plan is None or self._plan.shapes != shapes:
+                self._plan = BucketPlan(shapes, self.device, self.bucket_bytes)
+            position = {param: index for index, param in enumerate(parameters)}
+        try:
+            for index, batch in enumerate(batches):
+                if distributed and index == len(batches) - 1:
+                    # Last micro-batch: every gradient is final as soon as autograd has accumulated it, so it
+                    # is copied into its bucket right away and complete buckets are all-reduced under the rest
+                    # of the backward pass (a 16-bit gradient is widened by that copy and rounded once after).
+                    exchange = PlannedExchange(self._plan, self.group)
+                    hooks = [p.register_post_accumulate_grad_hook(
+                        lambda param, exchange=exchange: exchange.add(position[param], param.grad)) for p in parameters]
+                microbatches += 1
+                valid_tokens += int(batch["attention_mask"].sum())
+                targets, weights = prediction_targets(batch)
+                rows = active_rows(weights, self.device)
+                targets, weights = targets.to(self.device), weights.to(self.device)
+                batch = {k: v.to(self.device) if torch.is_tensor(v) else v for k, v in batch.items()}
+                hidden = self.model(batch)
+                loss = projection_loss(hidden, self.model.lm_head.weight, targets, weights,
+                                       token_budget=self.loss_token_budget,
+                                       compute_dtype=self.model.runtime.compute_dtype,
+                                       reuse_hidden=not self.model.model.norm.weight.requires_grad, rows=rows)
+                del hidden
+                loss.backward()
+                total_loss.add_(loss.detach())
+                total_weight.add_(weights.sum())
+                del loss, batch
+            if microbatches == 0:
+                raise ValueError("An optimizer update requires at least one microbatch")
+            for param in parameters:
+                if param.grad is None:
+                    raise RuntimeError("A trainable parameter has no gradient; the graph is disconnected")
+        except Exception as error:      # told to the other ranks below, then raised again
+            failure = error
+        finally:
+            for hook in hooks:          # never leave hooks behind: the next update builds its own exchange
+                hook.remove()
         collectives = 0
-        if exchange is not None:
-            scalars = torch.stack((total_loss, total_weight))
-            exchange.add(scalars)
-            exchange.finish()
-            for param, value in wide.items():
-                param.grad.copy_(value)
-            total_loss, total_weight = scalars[0], scalars[1]
+        if distributed:
+            # The loss, the weight and a failure flag travel in the last, small all-reduce. A rank whose
+            # forward or backward raised still launches every bucket (contents irrelevant) so that the
+            # collectives of its peers complete; every rank then sees the flag and raises before stepping.
+            scalars = torch.stack((total_loss, total_weight, torch.full_like(total_loss, 0.0 if failure is None else 1.0)))
+            if exchange is None:
+                exchange = PlannedExchange(self._plan, self.group)
+            if failure is not None:
+                exchange.flush()
+            summed = exchange.finish(scalars)
             collectives = exchange.collectives
+            if failure is None and scalars[2].item() > 0:
+                failure = RuntimeError("Another rank failed during this update; no optimizer step was taken")
+            if failure is None:
+                for param, value in zip(parameters, summed):
+                    if param.grad.dtype == torch.float32:
+                        param.grad = value            # a view of the persistent bucket: no copy back
+                    else:
+                        param.grad.copy_(value)
+                total_loss, total_weight = scalars[0], scalars[1]
+        if failure is not None:
+            raise failure
         denominator = total_weight.clamp_min(1.0)
         if learning_rate is not None:
             for group in self.optimizer.param_groups:

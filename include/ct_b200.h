@@ -299,6 +299,29 @@ CT_API int ct_rmsnorm_backward_add(const void* x, const void* w, const float* rs
                                    const void* add, void* gx, int64_t rows, int64_t width, int dtype,
                                    int weight_dtype, void* stream);
 
+/* Output-reconstruction mode of a frozen pre-norm (kernels/core_cuda.py:56-59, FROM_OUTPUT): the
+ * backward pass is given the norm's OUTPUT y instead of its input (the caller keeps y anyway as the
+ * input of the projection that follows, so x need not be retained):
+ *   n = y / round(w);  gx = rstd * (g - n * mean(g * n)),  g = round(go * round(w))
+ * Only meaningful where no weight is near zero; the caller decides (modeling/model.py:46-58 of the
+ * reference allows 1/256 <= |w| <= 256 in bf16). gx may alias go; `add` (may be NULL) is the
+ * residual-path gradient of ct_rmsnorm_backward_add. */
+CT_API int ct_rmsnorm_backward_from_output(const void* y, const void* w, const float* rstd,
+                                           const void* go, const void* add, void* gx, int64_t rows,
+                                           int64_t width, int dtype, int weight_dtype, void* stream);
+/* Trainable norm weight (kernels/core_cuda.py:60-91, _rms_gradient_row with WEIGHT_GRAD, _rms_backward,
+ * _rms_weight_reduce): group `i` of `rows_per_group` consecutive rows writes
+ *   partials[i, c] = sum over its rows of go[row, c] * round(x[row, c] * rstd[row])      fp32
+ * (rows added in order) and, when gx != NULL, the input gradient of ct_rmsnorm_backward for those rows
+ * (gx must not alias go here). partials is [ceil(rows / rows_per_group), width] fp32.
+ * ct_rmsnorm_weight_reduce then writes dw[c] = sum over groups of partials[group, c] (fixed order) in
+ * `weight_dtype`; groups == 0 gives zeros. */
+CT_API int ct_rmsnorm_weight_gradient(const void* x, const void* w, const float* rstd, const void* go,
+                                      void* gx, float* partials, int64_t rows, int64_t width,
+                                      int64_t rows_per_group, int dtype, int weight_dtype, void* stream);
+CT_API int ct_rmsnorm_weight_reduce(const float* partials, int64_t groups, int64_t width, void* dw,
+                                    int weight_dtype, void* stream);
+
 /* ---- weighted cross-entropy over a tile of logits -------------------------------
  * Replaces kernels/loss_cuda.py:12-72 (_statistics, _finish, weighted_ce).
  *   loss[row] = weights[row] * (logsumexp(logits[row]) - logits[row, targets[row]])

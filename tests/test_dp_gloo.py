@@ -72,6 +72,86 @@ def test_missing_rank_surfaces_as_an_error_on_the_survivor():
     assert results[0] != "no error"
 
 
+class _ToyDecoder(torch.nn.Module):
+    """Stands in for CausalLM on CPU ranks: a few trainable matrices between the batch and the 'hidden'
+    output, with the attributes Trainer.update reads."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(7)
+        self.first = torch.nn.Parameter(torch.randn(6, 8))
+        self.second = torch.nn.Parameter(torch.randn(8, 3))
+        self.third = torch.nn.Parameter(torch.randn(3, 5))
+        self.lm_head = torch.nn.Linear(5, 11, bias=False).requires_grad_(False)
+        self.runtime = type("R", (), {"compute_dtype": torch.float32})()
+        self.model = type("M", (), {"norm": type("N", (), {"weight": torch.zeros(1)})()})()
+        self.fail = False
+
+    def forward(self, batch):
+        if self.fail:
+            raise MemoryError("injected on the host")
+        x = torch.nn.functional.one_hot(batch["input_ids"] % 6, 6).float()
+        return x @ self.first @ self.second @ self.third
+
+
+def trainer_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    from causal_tuner_b200 import _lib, training
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        # CPU ranks: the CUDA-only loss and the device check are replaced; the exchange logic is what runs.
+        training.projection_loss = lambda hidden, head, targets, weights, **kw: (hidden @ head.T).square().sum()
+        _lib.check_device = lambda *a, **k: None
+        model = _ToyDecoder()
+        optimizer = torch.optim.AdamW([p for p in model.parameters() if p.requires_grad], lr=1e-3)
+        trainer = training.Trainer(model, optimizer, device="cpu", bucket_bytes=64)   # several buckets
+        ids = torch.arange(12).reshape(2, 6) + rank
+        batch = {"input_ids": ids, "attention_mask": torch.ones_like(ids)}
+        first = trainer.update([batch])
+        grads = [p.grad.clone() for p in model.parameters() if p.requires_grad]
+        model.fail = rank == 1                      # rank 1 raises inside its forward pass
+        try:
+            trainer.update([batch])
+            outcome = "no error"
+        except Exception as error:
+            outcome = f"{type(error).__name__}: {error}"
+        model.fail = False
+        again = trainer.update([batch])             # the ranks are still in step: the next update works
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [g.tolist() for g in grads])
+        same = all(torch.equal(torch.tensor(gathered[0][i]), torch.tensor(gathered[r][i]))
+                   for r in range(world) for i in range(len(grads)))
+        results[rank] = (first["collectives"], outcome, again["collectives"], same, first["loss"] == first["loss"])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_rank_that_raises_mid_update_stops_every_rank_and_the_next_update_still_works():
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(trainer_worker, args=(2, free_port(), results), nprocs=2, join=True)
+    for rank in (0, 1):
+        collectives, outcome, again, same, finite = results[rank]
+        assert collectives == again and collectives >= 3        # buckets + the scalar all-reduce, every update
+        assert same and finite                                  # both ranks hold the same summed gradients
+    assert results[1][1].startswith("MemoryError")
+    assert results[0][1].startswith("RuntimeError: Another rank failed")
+
+
+def test_bucket_plan_is_a_function_of_the_shapes():
+    from causal_tuner_b200.dp import BucketPlan
+    shapes = [(4, 8), (8, 4), (2, 2), (16,), (3, 5)]
+    plan = BucketPlan(shapes, "cpu", bucket_bytes=64)
+    assert [plan.slot[i][0] for i in range(5)] == [2, 1, 1, 0, 0]       # reverse parameter order, >= 64 bytes each
+    assert sum(b.numel() for b in plan.buffers) == sum(torch.Size(s).numel() for s in shapes)
+    assert all(plan.view(i).shape == torch.Size(s) for i, s in enumerate(shapes))
+    other = BucketPlan(shapes, "cpu", bucket_bytes=64)
+    assert plan.slot == other.slot and plan.members == other.members
+    with pytest.raises(ValueError):
+        BucketPlan(shapes, "cpu", bucket_bytes=0)
+
+
 def test_single_process_is_a_no_op():
     gradient = torch.randn(4, 4)
     before = gradient.clone()

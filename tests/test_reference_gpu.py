@@ -1,0 +1,234 @@
+"""This library against the REFERENCE'S OWN CUDA path (Triton kernels + cuBLAS + FlashAttention-2,
+installed unmodified in oracle/_ref by oracle/make_ref.py) on the same seeded inputs and the same
+packed NF4 bytes:
+
+* NF4 decode bit-exact with the reference's Triton `_decode` (kernels/nf4_cuda.py:9-43), on the grid of
+  its own tests and at 14336 x 4096, plain and nested statistics;
+* `project_group` at the size of BASELINE.json configs[1] and `tiled_lora_mlp` at configs[2]
+  (32768 tokens, with and without the activation cache) within 2e-2 relative Frobenius error of the
+  reference's `project_group` / `tiled_lora_mlp` for outputs and every gradient;
+* five optimizer updates of the 1.3B and of the 7B-class decoder (configs[3], configs[4]) with identical
+  weights and batch: every per-step loss within 1e-3 relative of the reference's `Trainer.update`
+  (training/engine.py:41-111).
+"""
+
+import gc
+
+import pytest
+import torch
+
+from causal_tuner_b200.kernels.linear import project_group
+from causal_tuner_b200.kernels.mlp_cuda import tiled_lora_mlp
+from causal_tuner_b200.kernels.nf4_cuda import dequantize_nf4
+from causal_tuner_b200.modeling.lora import Projection
+from causal_tuner_b200.quant import quantize_nf4
+from oracle import ref_bridge
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
+
+
+@pytest.fixture(scope="module")
+def reference():
+    if not ref_bridge.available():
+        pytest.skip("oracle/_ref is not installed (python oracle/make_ref.py needs the reference checkout)")
+    pytest.importorskip("triton")
+    return ref_bridge.load()
+
+
+def relative(actual, expected):
+    actual, expected = actual.float(), expected.float()
+    return ((actual - expected).norm() / expected.norm().clamp_min(1e-30)).item()
+
+
+def release():
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+# ---- NF4 decode ------------------------------------------------------------------------------------
+
+GRID = [((71, 96), bs, nested, dtype) for bs in (64, 128, 4096) for nested in (False, True)
+        for dtype in (torch.bfloat16, torch.float16, torch.float32)]
+GRID += [((17, 19), 64, nested, torch.bfloat16) for nested in (False, True)]
+
+
+@pytest.mark.parametrize("shape,blocksize,nested,source", GRID)
+def test_decode_equals_reference_triton_kernel_on_its_own_test_grid(reference, shape, blocksize, nested, source):
+    """The case grid of the reference's tests/test_kernel_workspaces.py:256-266,422-430 (nested x source dtype x
+    block size, plus the odd tail), with the reference's Triton kernel as the comparator instead of bitsandbytes."""
+    from causal_tuner.kernels.nf4_cuda import dequantize_nf4 as reference_decode
+    torch.manual_seed(300)
+    weight = torch.randn(*shape, device="cuda").to(source)
+    packed, state = quantize_nf4(weight, blocksize=blocksize, nested=nested)
+    for target in (torch.bfloat16, torch.float16, torch.float32):
+        expected = reference_decode(packed, state, target)
+        actual = dequantize_nf4(packed, state, target)
+        assert actual.dtype == expected.dtype and actual.shape == expected.shape
+        assert torch.equal(actual, expected), (shape, blocksize, nested, source, target)
+
+
+@pytest.mark.parametrize("nested", [False, True])
+def test_decode_equals_reference_triton_kernel_at_full_size(reference, nested):
+    from causal_tuner.kernels.nf4_cuda import dequantize_nf4 as reference_decode
+    torch.manual_seed(301)
+    weight = (torch.randn(14336, 4096, device="cuda") * .02).bfloat16()
+    packed, state = quantize_nf4(weight, blocksize=64, nested=nested)
+    expected = reference_decode(packed, state, torch.bfloat16)
+    actual = dequantize_nf4(packed, state, torch.bfloat16)
+    assert torch.equal(actual, expected)
+    release()
+
+
+# ---- projection operator -----------------------------------------------------------------------------
+
+def make_projection(inner, outer, rank, *, bias=False, nested=False, seed=0):
+    torch.manual_seed(seed)
+    module = Projection(inner, outer, bias=bias, rank=rank, device="cuda")
+    module.install_nf4(module.weight.detach().clone(), "cuda", blocksize=64, nested=nested)
+    with torch.no_grad():
+        module.lora_A.normal_(std=.02)
+        module.lora_B.normal_(std=.01)
+        if bias:
+            module.bias.normal_(std=.05)
+    return module
+
+
+def test_projection_config2_against_reference_cuda_path(reference):
+    """BASELINE.json configs[1]: M = 16384, K = 4096, N = 14336, rank 256, NF4 64-element blocks, fp32 absmax;
+    X ~ N(0,1), W ~ N(0,.02), A ~ N(0,.02), B ~ N(0,.01), dY ~ N(0,1). Tolerance 2e-2 relative Frobenius."""
+    from causal_tuner.kernels.linear import project_group as reference_group
+    ours = make_projection(4096, 14336, 256, seed=11)
+    theirs = ref_bridge.mirror_projection(ours)
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    x = torch.randn(16384, 4096, device="cuda", generator=generator).bfloat16()
+    dy = torch.randn(16384, 14336, device="cuda", generator=generator).bfloat16()
+    results = []
+    for module, operator in ((ours, project_group), (theirs, reference_group)):
+        leaf = x.clone().requires_grad_(True)
+        y = operator((module,), leaf)[0]
+        grads = torch.autograd.grad(y, (leaf, module.lora_A, module.lora_B), dy)
+        results.append((y.detach(), *grads))
+        del y, grads, leaf
+    for name, actual, expected in zip(("y", "dx", "da", "db"), *results):
+        assert actual.dtype == expected.dtype and actual.shape == expected.shape, name
+        assert relative(actual, expected) < 2e-2, (name, relative(actual, expected))
+    del results
+    release()
+
+
+def test_qkv_group_with_rotary_and_output_projection_against_reference(reference):
+    """The attention-side call sites (modeling/model.py:87-89,105-106): q/k/v sharing x with biases and the
+    in-place q/k rotation, and the o projection with its fused residual; 7B widths, 4096 tokens."""
+    from causal_tuner.kernels.linear import project_group as reference_group
+    from causal_tuner_b200.kernels.core_cuda import position_values
+    rows, hidden, head = 4096, 4096, 128
+    ours = [make_projection(hidden, hidden, 256, bias=True, seed=21), make_projection(hidden, head, 256, bias=True, seed=22),
+            make_projection(hidden, head, 256, bias=True, seed=23)]
+    theirs = [ref_bridge.mirror_projection(m) for m in ours]
+    positions = torch.arange(rows, device="cuda").reshape(1, rows)
+    inverse = 1.0 / (1e6 ** (torch.arange(0, 64, 2, device="cuda", dtype=torch.float32) / 64))
+    cosine, sine = position_values(positions, inverse, torch.bfloat16)
+    generator = torch.Generator(device="cuda").manual_seed(24)
+    x = torch.randn(1, rows, hidden, device="cuda", generator=generator).bfloat16()
+    signals = [torch.randn(1, rows, m.lora_B.shape[0], device="cuda", generator=generator).bfloat16() for m in ours]
+    results = []
+    for modules, operator in ((ours, project_group), (theirs, reference_group)):
+        leaf = x.clone().requires_grad_(True)
+        outputs = operator(tuple(modules), leaf, 0, rotary=(cosine, sine, head))
+        parameters = [p for m in modules for p in (m.lora_A, m.lora_B)]
+        grads = torch.autograd.grad(outputs, (leaf, *parameters), signals)
+        results.append([o.detach() for o in outputs] + list(grads))
+    for index, (actual, expected) in enumerate(zip(*results)):
+        assert relative(actual, expected) < 2e-2, (index, relative(actual, expected))
+    # o projection: residual fused into the single-output group
+    ours_o = make_projection(hidden, hidden, 256, seed=25)
+    theirs_o = ref_bridge.mirror_projection(ours_o)
+    residual = torch.randn(1, rows, hidden, device="cuda", generator=generator).bfloat16()
+    results = []
+    for module, operator in ((ours_o, project_group), (theirs_o, reference_group)):
+        leaf, shortcut = x.clone().requires_grad_(True), residual.clone().requires_grad_(True)
+        y = operator((module,), leaf, 0, residual=shortcut)[0]
+        grads = torch.autograd.grad(y, (leaf, shortcut, module.lora_A, module.lora_B), signals[0])
+        results.append([y.detach(), *grads])
+    for index, (actual, expected) in enumerate(zip(*results)):
+        assert relative(actual, expected) < 2e-2, (index, relative(actual, expected))
+    release()
+
+
+# ---- MLP operator ----------------------------------------------------------------------------------
+
+class _Block(torch.nn.Module):
+    def __init__(self, gate, up, down):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate, up, down
+        self.tile, self.cache_intermediates = None, False
+
+
+@pytest.mark.parametrize("cache", [False, True])
+def test_mlp_config3_against_reference_cuda_path(reference, cache):
+    """BASELINE.json configs[2]: hidden 4096, intermediate 14336, rank 256, NF4, 8 x 4096 tokens ~ N(0,1);
+    recompute-in-backward (cache=False) and stored activations (cache=True) against the reference's
+    `tiled_lora_mlp` in the same mode. Tolerance 2e-2 relative Frobenius for the output and all seven gradients."""
+    from causal_tuner.kernels.mlp_cuda import tiled_lora_mlp as reference_mlp
+    hidden, inner = 4096, 14336
+    ours = _Block(make_projection(hidden, inner, 256, seed=31), make_projection(hidden, inner, 256, seed=32),
+                  make_projection(inner, hidden, 256, seed=33))
+    theirs = _Block(*(ref_bridge.mirror_projection(m) for m in (ours.gate_proj, ours.up_proj, ours.down_proj)))
+    generator = torch.Generator(device="cuda").manual_seed(34)
+    x = torch.randn(8, 4096, hidden, device="cuda", generator=generator).bfloat16()
+    dy = torch.randn(8, 4096, hidden, device="cuda", generator=generator).bfloat16()
+    results = []
+    for block, operator in ((ours, tiled_lora_mlp), (theirs, reference_mlp)):
+        leaf = x.clone().requires_grad_(True)
+        y = operator(block, leaf, None, tile=4096, cache=cache)
+        parameters = [p for m in (block.gate_proj, block.up_proj, block.down_proj) for p in (m.lora_A, m.lora_B)]
+        grads = torch.autograd.grad(y, (leaf, *parameters), dy)
+        results.append([y.detach(), *grads])
+        del y, grads, leaf
+        release()
+    names = ("y", "dx", "da_gate", "db_gate", "da_up", "db_up", "da_down", "db_down")
+    for name, actual, expected in zip(names, *results):
+        assert actual.dtype == expected.dtype, name
+        assert relative(actual, expected) < 2e-2, (name, relative(actual, expected))
+    del results
+    release()
+
+
+# ---- whole optimizer updates ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("workload", ["step1b", "step7b"])
+def test_five_updates_track_the_reference_trainer(reference, workload):
+    """configs[3] / configs[4]: identical frozen weights (shared packed NF4 bytes), identical adapter
+    initialisation, identical batch of packed documents; five `Trainer.update` calls on each side.
+    north_star's bound: every per-step loss within 1e-3 relative. The clipped gradient norm is compared
+    at 2e-2 (it sums bf16 gradients of every layer)."""
+    pytest.importorskip("flash_attn")
+    import bench_step
+    from causal_tuner_b200.training import Trainer, make_optimizer
+    spec = bench_step.WORKLOADS[workload]
+    device = torch.device("cuda", 0)
+    ours = bench_step.build_model(workload, device, mlp_cache_gib=0)
+    theirs = ref_bridge.mirror_model(ours)
+    batch = bench_step.synthetic_batch(spec["rows"], spec["length"], spec["config"]["vocab_size"], seed=4242)
+    rate = 1e-4
+
+    their_trainer = ref_bridge.reference_trainer(theirs, device, learning_rate=rate, loss_token_budget=4096)
+    expected = [their_trainer.update([dict(batch)], step=index, total_steps=5) for index in range(5)]
+    policy = expected[0]["execution"][0]
+    del their_trainer, theirs
+    release()
+
+    our_trainer = Trainer(ours, make_optimizer(ours, learning_rate=rate), device=device, loss_token_budget=4096)
+    actual = [our_trainer.update([dict(batch)]) for _ in range(5)]
+    print(f"\n{workload}: reference policy {policy}")
+    for step, (mine, reference_metrics) in enumerate(zip(actual, expected)):
+        print(f"  step {step}: loss {mine['loss']:.6f} vs {reference_metrics['loss']:.6f}, "
+              f"norm {mine['grad_norm']:.5f} vs {reference_metrics['grad_norm']:.5f}")
+    for step, (mine, reference_metrics) in enumerate(zip(actual, expected)):
+        assert mine["valid_tokens"] == reference_metrics["valid_tokens"]
+        assert mine["effective_weight"] == reference_metrics["effective_weight"]
+        assert abs(mine["loss"] - reference_metrics["loss"]) / reference_metrics["loss"] < 1e-3, step
+        assert abs(mine["grad_norm"] - reference_metrics["grad_norm"]) / reference_metrics["grad_norm"] < 2e-2, step
+    assert actual[-1]["loss"] < actual[0]["loss"]
+    del our_trainer, ours
+    release()
