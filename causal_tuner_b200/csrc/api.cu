@@ -16,7 +16,11 @@ namespace {
 thread_local char g_error_text[512] = "";
 std::atomic<int64_t> g_launches{0}, g_tc_launches{0};
 constexpr int kMaxDevices = 64;
+// Per-device error flag (device memory, or a device symbol when the no-allocation entry point came
+// first). Installed on first use under g_device_mutex, so that two host threads that make their first
+// calls on a device at the same moment agree on one flag.
 int* g_error_flags[kMaxDevices] = {};
+std::mutex g_device_mutex;
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -92,6 +96,7 @@ bool dependent_launch_enabled() {
 int* device_error_flag() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
   if (!g_error_flags[dev]) {
     int* flag = nullptr;
     if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return nullptr;
@@ -220,12 +225,17 @@ extern "C" int ct_check_device(void* stream) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(CT_ERR_CUDA, "ct_check_device: no current device");
-  if (!g_error_flags[dev]) return CT_OK;
+  int* flag = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    flag = g_error_flags[dev];
+  }
+  if (!flag) return CT_OK;
   int value = 0;
-  err = cudaMemcpy(&value, g_error_flags[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  err = cudaMemcpy(&value, flag, sizeof(int), cudaMemcpyDeviceToHost);
   if (err != cudaSuccess) return fail(CT_ERR_CUDA, "ct_check_device: %s", cudaGetErrorString(err));
   if (value == 0) return CT_OK;
-  cudaMemset(g_error_flags[dev], 0, sizeof(int));
+  cudaMemset(flag, 0, sizeof(int));
   static const char* roles[] = {"", "TMA producer waiting for a free stage", "MMA issuer waiting for a free accumulator",
                                 "MMA issuer waiting for a filled stage", "epilogue waiting for a finished accumulator",
                                 "the self-test's wait on a barrier that nothing completes"};
@@ -368,23 +378,25 @@ extern "C" int ct_accumulate(const void* left, int64_t ld_left, const void* righ
 }
 
 // ---- parameter gradients without any allocation ----------------------------------------------
-// Slice-partial scratch that lives in the library image itself. Every GPU that loads the library
-// holds these bytes until the process exits. In HOST code the array's name is only a stand-in for
+// Slice-partial scratch that lives in the library image itself. Every GPU on which this entry point
+// has been called holds these bytes until the process exits. In HOST code the array's name is only a stand-in for
 // the symbol; the device address comes from cudaGetSymbolAddress, once per device.
 namespace {
 constexpr int64_t kNoAllocScratchBytes = 16ll << 20;  // e.g. 4 slices of a 256 x 4096 fp32 gradient
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 static __device__ int g_noalloc_error_flag;
 void* g_noalloc_scratch_address[kMaxDevices] = {};
-std::mutex g_noalloc_mutex;
 
-// First use on a device: resolve the device addresses of the two symbols above (no allocation).
+// First use on a device: resolve the device addresses of the two symbols above. The call itself asks for no
+// memory, but CUDA loads a module's image lazily: the module that holds these symbols (and with it the
+// 16 MiB array) reaches the device here, on the first call, and the GEMM's module on its first launch.
+// A host that must not allocate later makes one warm-up call per device at start-up.
 int noalloc_setup(void** scratch) {
   int dev = -1;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(CT_ERR_CUDA, "ct_parameter_gradients_noalloc: no current device");
-  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  std::lock_guard<std::mutex> lock(g_device_mutex);
   if (!g_noalloc_scratch_address[dev]) {
     void* address = nullptr;
     err = cudaGetSymbolAddress(&address, g_noalloc_scratch);

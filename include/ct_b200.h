@@ -224,12 +224,18 @@ CT_API int ct_accumulate(const void* left, int64_t ld_left, const void* right, i
  * (a raw cudaMalloc would then fail), or a step loop that cannot accept the
  * device-wide synchronisation a cudaMalloc or cudaFree implies.
  *   - Capacity: ct_parameter_gradients_noalloc_capacity() bytes (16 MiB, e.g. the
- *     four slices of a rank-256 gradient over 4096 columns). Every GPU that loads
- *     the library holds that array until the process exits. A problem whose
+ *     four slices of a rank-256 gradient over 4096 columns). A problem whose
  *     ct_parameter_gradients_workspace(...) exceeds it is refused with
  *     CT_ERR_UNSUPPORTED and nothing is launched.
- *   - The first call on a device resolves the array's device address
- *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - The FIRST call on a device is a set-up call: it resolves the array's device
+ *     address (cudaGetSymbolAddress), and because CUDA loads code lazily it is also
+ *     the moment the driver places the library's image - the 16 MiB array and the
+ *     GEMM kernels - on that device, which takes device memory once and can fail with
+ *     CT_ERR_CUDA if none is left. Make one warm-up call per device at start-up
+ *     (any small problem; r = 0 resolves the addresses and launches nothing), before
+ *     the host's pool takes the rest of the memory and before any stream capture.
+ *     From then on the device holds the array until the process exits and later
+ *     calls change neither free nor allocated device memory.
  *   - All calls share the one array and it keeps the previous call's partial
  *     sums; nothing in it needs clearing (every slice is fully overwritten before
  *     it is read), but two calls whose kernels overlap on the GPU (different

@@ -139,6 +139,74 @@ def test_segments_positions_and_targets_never_cross_documents():
     assert targets[0, :2].tolist() == [1, 2] and targets[weights == 0].eq(0).all()
 
 
+def test_segment_helpers_equal_the_installed_reference_on_random_packs():
+    """Randomised packs (gaps, repeated raw labels, label 0, explicit weights, -100 targets) through the
+    reference's own data/segments.py, installed in oracle/_ref, and through this package's functions."""
+    from oracle import ref_bridge
+    if not ref_bridge.available():
+        pytest.skip("oracle/_ref is not installed")
+    ref_bridge.load()
+    from causal_tuner.data import segments as theirs
+    from causal_tuner_b200 import segments as ours
+    generator = torch.Generator().manual_seed(99)
+    for trial in range(40):
+        rows, width = int(torch.randint(1, 5, (), generator=generator)), int(torch.randint(1, 40, (), generator=generator))
+        mask = (torch.rand(rows, width, generator=generator) > .2).long()
+        labels = torch.randint(0, 3, (rows, width), generator=generator).sort(dim=1).values if trial % 2 else \
+            torch.randint(0, 3, (rows, width), generator=generator)
+        a, b = ours.canonical_segments(mask, labels), theirs.canonical_segments(mask, labels)
+        assert a.dtype == b.dtype and torch.equal(a, b)
+        assert torch.equal(ours.canonical_segments(mask), theirs.canonical_segments(mask))
+        assert torch.equal(ours.position_ids(a), theirs.position_ids(b))
+        assert ours.runs(a) == theirs.runs(b)
+        ids = torch.randint(0, 50, (rows, width), generator=generator)
+        batch = {"input_ids": ids, "attention_mask": mask, "segment_ids": labels}
+        if trial % 3 == 0:
+            batch["loss_weights"] = torch.rand(rows, width, generator=generator)
+        if trial % 3 == 1:
+            batch["assistant_masks"] = (torch.rand(rows, width, generator=generator) > .5).long()
+        if trial % 4 == 0:
+            batch["labels"] = torch.where(torch.rand(rows, width, generator=generator) > .8, -100, ids)
+        if trial % 7 == 0:
+            batch["prediction_targets"] = torch.randint(0, 50, (rows, width), generator=generator)
+            batch["prediction_weights"] = torch.rand(rows, width, generator=generator)
+        for mine, reference_value in zip(ours.prediction_targets(batch), theirs.prediction_targets(batch)):
+            assert mine.dtype == reference_value.dtype and torch.equal(mine, reference_value)
+    assert ours.runs(torch.zeros(2, 0, dtype=torch.int32)) == () and ours.runs(torch.zeros(2, 5, dtype=torch.int32)) == ()
+    with pytest.raises(ValueError):
+        ours.canonical_segments(torch.ones(3))
+    with pytest.raises(ValueError):
+        ours.canonical_segments(torch.ones(2, 3), torch.ones(2, 4))
+
+
+def test_attention_layout_classification_equals_the_installed_reference():
+    from oracle import ref_bridge
+    if not ref_bridge.available():
+        pytest.skip("oracle/_ref is not installed")
+    ref_bridge.load()
+    from causal_tuner.kernels.attention import prepare_dense_layout as theirs
+    from causal_tuner_b200.kernels.attention import prepare_dense_layout as ours
+    from causal_tuner_b200 import segments as seg
+    generator = torch.Generator().manual_seed(5)
+    seen = set()
+    for trial in range(60):
+        rows, width = int(torch.randint(1, 4, (), generator=generator)), int(torch.randint(1, 24, (), generator=generator))
+        kind = trial % 4
+        mask = torch.ones(rows, width, dtype=torch.long) if kind < 2 else (torch.rand(rows, width, generator=generator) > .3).long()
+        labels = torch.zeros(rows, width, dtype=torch.long) if kind == 0 else \
+            torch.randint(0, 3, (rows, width), generator=generator).sort(dim=1).values
+        if kind == 3 and trial % 8 == 3:
+            mask.zero_()
+        spans = seg.runs(seg.canonical_segments(mask, labels))
+        a, b = ours((rows, width), spans, "cpu"), theirs((rows, width), spans, "cpu")
+        assert (a.spans, a.mode, a.maximum) == (b.spans, b.mode, b.maximum)
+        assert (a.offsets is None) == (b.offsets is None) and (a.offsets is None or torch.equal(a.offsets, b.offsets))
+        seen.add(a.mode)
+    assert seen == {"empty", "full", "packed", "gaps"}
+    with pytest.raises(NotImplementedError):
+        ours((1, 2), ((0, 0, 2),), "cpu", torch.zeros(1, 2))
+
+
 def test_active_rows_prefers_slices():
     from causal_tuner_b200.kernels.loss import active_rows, row_count
     assert active_rows(torch.tensor([0., 1, 2, 0])) == slice(1, 3)

@@ -71,17 +71,19 @@ def test_fp32_step_matches_the_reference_fixture(golden, variant, checkpoint):
             torch.testing.assert_close(parameter.detach().cpu(), expected_value, rtol=0, atol=2.5e-5, msg=name)
 
 
-def test_bf16_nf4_flash_step_tracks_the_fp32_reference(golden):
-    """Same step in the production configuration (NF4 base, bf16 compute, FlashAttention-2, layer
-    checkpointing). bf16 arithmetic against the fp32 fixture: loss within 2e-3 relative, gradients within
-    5e-2 relative Frobenius error over all adapters."""
+def test_bf16_nf4_flash_step_tracks_the_bf16_reference_fixture(golden):
+    """Same step in the production arithmetic (NF4 base decoded to bf16, bf16 compute, FlashAttention-2, layer
+    checkpointing) against the fixture the reference produced with ITS bf16 arithmetic on the CPU
+    (make_golden_step.py --dtype bfloat16): loss within 1e-3 relative - the bound stated for per-step losses -
+    and gradients within 5e-2 relative Frobenius error over all adapters (every layer's bf16 rounding adds up)."""
     pytest.importorskip("flash_attn")
-    g = golden("step_tiny_b1.npz")
-    runtime = Runtime(rank=16, base_dtype=torch.bfloat16, compute_dtype=torch.bfloat16, checkpoint=True)
-    model = load_model(g, runtime, nf4=True)
+    g = golden("step_tiny_bf16.npz")
+    runtime = Runtime(rank=16, base_dtype=torch.float32, compute_dtype=torch.bfloat16, checkpoint=True)
+    model = load_model(g, runtime, nf4=True)       # fp32 NF4 values re-pack without loss; decode rounds to bf16 once
     optimizer = make_optimizer(model, learning_rate=1e-4)
     metrics = Trainer(model, optimizer, device="cuda").update([batch_of(g)])
-    assert abs(metrics["loss"] - float(g["loss"])) / float(g["loss"]) < 2e-3
+    assert abs(metrics["loss"] - float(g["loss"])) / float(g["loss"]) < 1e-3
+    assert abs(metrics["grad_norm"] - float(g["grad_norm"])) / float(g["grad_norm"]) < 2e-2
     actual = torch.cat([p.grad.flatten().cpu() for n, p in model.named_parameters() if p.requires_grad])
     expected = torch.cat([torch.from_numpy(g["g__" + n.replace(".", "__")]).flatten()
                           for n, p in model.named_parameters() if p.requires_grad])

@@ -39,16 +39,16 @@ def reference_gradients(x, dy, low, xa, add, seed_values):
     return da, db, need
 
 
-def noalloc_gradients(x, dy, low, xa, add, seed_values):
+def noalloc_gradients(x, dy, low, xa, add, da, db):
+    """The call under test; `da` / `db` are made by the caller so that nothing is allocated in here."""
     library = _lib.load()
     rows, inner = x.shape
     outer, rank = dy.shape[1], low.shape[1]
-    da, db = seed_values[0].clone(), seed_values[1].clone()
     code = library.ct_parameter_gradients_noalloc(
         x.data_ptr(), inner, dy.data_ptr(), outer, low.data_ptr(), rank, xa.data_ptr(), rank, da.data_ptr(),
         db.data_ptr(), rows, inner, outer, rank, int(add), _lib.BF16, _lib.PATH_AUTO,
         torch.cuda.current_stream().cuda_stream)
-    return code, da, db
+    return code
 
 
 def test_matches_the_workspace_entry_point_on_two_calls_in_a_row():
@@ -61,9 +61,17 @@ def test_matches_the_workspace_entry_point_on_two_calls_in_a_row():
         start = (torch.randn(rank, inner, device="cuda"), torch.randn(outer, rank, device="cuda"))
         expected_da, expected_db, need = reference_gradients(x, dy, low, xa, add, start)
         assert 0 < need <= library.ct_parameter_gradients_noalloc_capacity()
-        code, da, db = noalloc_gradients(x, dy, low, xa, add, start)
-        _lib.check(code)
+        da, db = start[0].clone(), start[1].clone()
+        torch.cuda.synchronize()
+        free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        _lib.check(noalloc_gradients(x, dy, low, xa, add, da, db))
         _lib.check_device()
+        if call:
+            # The property in the entry point's name. The first call on a device is the documented set-up
+            # call (the driver places the library's image, scratch array included, on the device then);
+            # from the second call on, neither the device's free memory nor torch's own count may move.
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_allocated() == allocated_before
         assert torch.equal(da, expected_da) and torch.equal(db, expected_db)
         # and both agree with a plain fp32 product of the same operands
         plain_da = low.float().T @ x.float() + (start[0] if add else 0)
