@@ -1,21 +1,25 @@
-"""Throughput of the fused NF4 + LoRA projection (forward Y, backward dX, dA, dB).
+"""Throughput of the NF4 + LoRA training hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
-    python bench.py --impl reference --gpus N --steps K ...   # the reference's CPU composition
+    python bench.py --gpus N --steps K --warmup W              # this repository's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...     # the reference's own CPU implementation
 
-Workload ("projection_fwd_bwd_7b_gate"): one decoder projection of the 7B configuration -
-M = 16384 packed tokens, K = 4096, N = 14336, rank 256, NF4 base weight in 64-element blocks
-with fp32 absmax, bf16 activations, fp32 adapter weights and gradients. X ~ N(0,1),
-W ~ N(0,0.02), A ~ N(0,0.02), B ~ N(0,0.01), dY ~ N(0,1), all synthetic and seeded. A step
-is one forward plus one backward through the public operator (`project_group` + autograd);
-with N > 1 every rank works on its own 16384 tokens (weak scaling) and the fp32 adapter
-gradients are summed across ranks with one NCCL all-reduce inside the step.
+Default workload `step7b` (BASELINE.json configs[4]): one optimizer update of the 7B-class MQA decoder -
+32 layers, hidden 4096, 32 + 1 heads of 128, SwiGLU MLP 14336, vocab 49152, NF4 base weights in 64-element
+blocks with fp32 absmax, rank-256 adapters on all seven projections, bf16 compute, fp32 adapters / gradients
+/ Adam state, 4 packed rows of 4096 tokens per GPU with document lengths log-uniform in [64, 4096] - through
+`Trainer.update`: batch to the device, forward, tiled lm_head loss, backward, (N > 1) NCCL all-reduce of
+the adapter gradients, clip, AdamW, loss back to the host. `--workload step1b` is configs[3], `--workload
+projection` is configs[1] (one gate/up-shaped projection, forward + backward). All data is synthetic and
+seeded.
 
-One JSON line is printed by rank 0. `value` is whole-job tokens/s with inputs resident in
-HBM; `e2e` is the same step fed from pinned host buffers with every result copied back to
-the host inside the timed region; `roofline` is the tcgen05 GEMM's algorithmic FLOP/s over
-its own CUDA-event time against the measured cuBLAS bf16 peak; `cpu_baseline` times the CPU
-restatement of the reference composition on a bounded sample of rows.
+Rank 0 prints ONE JSON line. `value` is whole-job tokens/s with the batch resident in HBM; `e2e` is the same
+update fed from pinned host memory with the loss read back; `roofline` is the tcgen05 GEMM kernels'
+algorithmic FLOP/s over their own CUDA-event time against the measured cuBLAS bf16 peak, with the DRAM
+traffic of those kernels from an ncu capture of one decoder layer scaled to the step; `projection_op` is
+configs[1] timed in the same process (the "projection TFLOP/s vs peak" half of the metric);
+`reference_gpu` is the unmodified reference (oracle/_ref: cuBLAS + Triton + FlashAttention-2) timed on the
+same GPU with the same weights and batch - reported beside the line, never used in it; `cpu_baseline` and
+`--impl reference` time the unmodified reference's CPU branch on the host cores on a bounded sample.
 """
 
 import argparse
@@ -120,21 +124,39 @@ def physical_gpu_index(local_rank):
 
 # ---------------------------------------------------------------------------------------------
 class CpuProjection:
-    """The reference's CPU composition (modeling/lora.py:29-39 + torch autograd) on `rows` tokens of the workload."""
+    """The reference's CPU branch of one projection (modeling/lora.py:29-39 + torch autograd) on `rows` tokens of the
+    workload: the unmodified `Projection` from oracle/_ref when it is installed (kind "reference"), else the oracle's
+    restatement of that branch (kind "port")."""
 
     def __init__(self, rows, dtype, threads):
+        from oracle import ref_bridge
         torch.set_num_threads(threads)
         generator = torch.Generator().manual_seed(1234)
         self.rows, self.dtype = rows, dtype
-        self.weight = (torch.randn(OUTER, INNER, generator=generator) * .02).to(dtype)
-        self.a = (torch.randn(RANK, INNER, generator=generator) * .02).requires_grad_(True)
-        self.b = (torch.randn(OUTER, RANK, generator=generator) * .01).requires_grad_(True)
+        weight = (torch.randn(OUTER, INNER, generator=generator) * .02).to(dtype)
+        a = torch.randn(RANK, INNER, generator=generator) * .02
+        b = torch.randn(OUTER, RANK, generator=generator) * .01
         self.x = torch.randn(rows, INNER, generator=generator).to(dtype).requires_grad_(True)
         self.dy = torch.randn(rows, OUTER, generator=generator).to(dtype)
+        self.kind = "reference" if ref_bridge.available() else "port"
+        if self.kind == "reference":
+            ref_bridge.load()
+            from causal_tuner.modeling.lora import Projection
+            self.module = Projection(INNER, OUTER, rank=RANK, base_dtype=dtype, compute_dtype=dtype, device="cpu")
+            with torch.no_grad():
+                self.module.weight.copy_(weight)
+                self.module.lora_A.copy_(a)
+                self.module.lora_B.copy_(b)
+            self.a, self.b = self.module.lora_A, self.module.lora_B
+        else:
+            self.weight, self.a, self.b = weight, a.requires_grad_(True), b.requires_grad_(True)
 
     def step(self):
-        from oracle import ops
-        y = ops.projection(self.x, self.weight, self.a, self.b, None, self.dtype)
+        if self.kind == "reference":
+            y = self.module(self.x)
+        else:
+            from oracle import ops
+            y = ops.projection(self.x, self.weight, self.a, self.b, None, self.dtype)
         return torch.autograd.grad(y, (self.x, self.a, self.b), self.dy)
 
     def seconds_per_step(self, steps):
@@ -156,9 +178,11 @@ def faster_cpu_projection(threads):
     return best[1], best[2]
 
 
-def cpu_sample_text(name, steps):
+def cpu_sample_text(name, steps, kind="port"):
+    source = ("the reference's own Projection (oracle/_ref, unmodified), CPU branch modeling/lora.py:29-39 + autograd"
+              if kind == "reference" else "oracle/ops.py restating the reference CPU branch modeling/lora.py:29-39 + autograd")
     return (f"{steps} steps of {CPU_SAMPLE_ROWS} of the {ROWS} rows (full K, N, rank; cost is linear in rows), "
-            f"{name} compute, oracle/ops.py restating the reference CPU branch modeling/lora.py:29-39 + autograd")
+            f"{name} compute, {source}")
 
 
 def cpu_baseline(seconds=12.0):
@@ -167,14 +191,13 @@ def cpu_baseline(seconds=12.0):
     one = problem.seconds_per_step(1)
     steps = max(3, min(200, int(seconds / max(one, 1e-3))))
     per_step = problem.seconds_per_step(steps)
-    return {"value": CPU_SAMPLE_ROWS / per_step, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": cpu_sample_text(name, steps)}
+    return {"value": CPU_SAMPLE_ROWS / per_step, "unit": "tokens/s", "cores": threads, "kind": problem.kind,
+            "sample": cpu_sample_text(name, steps, problem.kind)}
 
 
 def run_reference(args):
-    """The reference arm: its CPU composition on this machine's host cores, all threads. The reference
-    is a Python package that does not travel to the GPU machine, so the timed code is its restatement in
-    oracle/ops.py; each step is one pass over a bounded sample of the workload's rows."""
+    """The reference arm of the projection workload: the reference's CPU branch on this machine's host cores,
+    all threads; each step is one pass over a bounded sample of the workload's rows."""
     rank, _, _ = world()
     if rank != 0:
         return
@@ -188,8 +211,8 @@ def run_reference(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": name, "data": "synthetic",
             "config": workload_config(args.gpus, bool(args.keep_low_rank)),
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
-                             "sample": cpu_sample_text(name, args.steps)},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": problem.kind,
+                             "sample": cpu_sample_text(name, args.steps, problem.kind)},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -405,21 +428,167 @@ def step_config(name, gpus, mlp_cache_gib=0, execution=None, keep_low_rank=False
             "l2": "per-layer operands (>= 134 MB activations + 117 MB decoded weight) exceed the 126 MB L2"}
 
 
-def run_step_reference(args):
+def reference_cpu_line(workload, steps, warmup):
+    """Times `steps` whole updates of the unmodified reference on the host cores (after `warmup`). Returns
+    (tokens/s, seconds per update, cpu_baseline record). Falls back to the oracle's restatement of one layer
+    + head (kind "port") on a machine where oracle/_ref was never installed."""
     import bench_step
+    threads = os.cpu_count() or 1
+    if not bench_step.reference_cpu_available():
+        estimate = bench_step.cpu_estimate(workload, passes=max(1, min(steps, 5)))
+        return estimate["value"], bench_step.CPU_SAMPLE_TOKENS / estimate["value"], estimate
+    problem = bench_step.ReferenceCpuStep(workload, threads)
+    started = time.perf_counter()
+    problem.step()
+    first = time.perf_counter() - started
+    # A host on which steps + warm-up would take more than about five minutes gets a smaller sample.
+    while problem.tokens > 128 and first * (steps + warmup) > 300:
+        problem.resize(problem.tokens // 2)
+        first /= 2
+    for _ in range(max(warmup - 1, 0) if problem.tokens == bench_step.CPU_SAMPLE_TOKENS else warmup):
+        problem.step()
+    start = time.perf_counter()
+    for _ in range(steps):
+        metrics = problem.step()
+    seconds = (time.perf_counter() - start) / steps
+    rate = metrics["valid_tokens"] / seconds
+    record = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "reference",
+              "sample": problem.sample_text(steps), "seconds_per_update": seconds, "loss": metrics["loss"]}
+    return rate, seconds, record
+
+
+def run_step_reference(args):
+    """The reference arm: rank 0 alone runs the reference's CPU implementation; each step is one whole
+    optimizer update on a bounded sample (one 512-token packed row) of the workload's batch."""
     rank, _, _ = world()
     if rank != 0:
         return
-    estimate = bench_step.cpu_estimate(args.workload, passes=max(1, min(args.steps, 5)))
-    line = {"impl": "reference", "metric": STEP_METRIC, "value": estimate["value"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1000.0 * bench_step.CPU_SAMPLE_TOKENS / estimate["value"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": step_config(args.workload, args.gpus, args.mlp_cache_gib, None, bool(args.keep_low_rank)),
-            "cpu_baseline": estimate,
-            "e2e": {"value": estimate["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    rate, seconds, record = reference_cpu_line(args.workload, args.steps, max(args.warmup, 1))
+    config = step_config(args.workload, args.gpus, args.mlp_cache_gib, None, bool(args.keep_low_rank))
+    config["reference_step"] = ("ms_per_step is one update on a 512-token sample of the per-GPU batch, not on the whole "
+                                "batch; tokens/s is what compares")
+    line = {"impl": "reference", "metric": STEP_METRIC, "value": rate, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1),
+            "ms_per_step": 1000.0 * seconds, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+            "cpu_baseline": record,
+            "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def projection_op_record(device, steps=20):
+    """BASELINE.json configs[1] inside the same process: one fused NF4 + LoRA projection (M = 16384, K = 4096,
+    N = 14336, rank 256), forward Y and backward dX, dA, dB through `project_group`, CUDA events, inputs larger
+    than L2. Algorithmic FLOP 4TKN + 6TKr + 6TNr against the measured cuBLAS burst peak (a kernel timed alone)."""
+    from causal_tuner_b200.kernels.linear import project_group
+    from causal_tuner_b200.modeling.lora import Projection
+    torch.manual_seed(2024)
+    module = Projection(INNER, OUTER, rank=RANK, device=device)
+    module.install_nf4(module.weight.detach().clone(), device, blocksize=64, nested=False)
+    module.keep_low_rank = True
+    with torch.no_grad():
+        module.lora_A.normal_(std=.02)
+        module.lora_B.normal_(std=.01)
+    generator = torch.Generator(device=device).manual_seed(77)
+    x = torch.randn(16384, INNER, device=device, generator=generator).bfloat16().requires_grad_(True)
+    dy = torch.randn(16384, OUTER, device=device, generator=generator).bfloat16()
+
+    def step():
+        y = project_group((module,), x)[0]
+        torch.autograd.grad(y, (x, module.lora_A, module.lora_B), dy)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize(device)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(stop) / steps
+    peaks, kind = measured_peaks()
+    tflops = projection_flops(16384) / (ms * 1e-3) / 1e12
+    record = {"workload": "projection_fwd_bwd_7b_gate (BASELINE.json configs[1])", "ms": ms, "tflops": tflops,
+              "frac_of_bf16_burst_peak": tflops / float(peaks["bf16_tflops"]), "peak_source": kind,
+              "tokens_per_s": 16384 / (ms * 1e-3), "steps": steps}
+    return record, module, x, dy
+
+
+def reference_gpu_record(model, device, batch, tokens, projection=None):
+    """The unmodified reference (oracle/_ref) on this GPU: its Triton kernels, cuBLAS and FlashAttention-2 through
+    its own `Trainer.update`, on a replica that shares this model's packed NF4 weights and starts from copies of
+    its adapters, same batch; and its `project_group` on configs[1]. A reported comparison only."""
+    from oracle import ref_bridge
+    if not ref_bridge.available():
+        return {"unavailable": "oracle/_ref is not installed on this machine"}
+    try:
+        import triton  # noqa: F401
+    except ImportError:
+        return {"unavailable": "triton is not importable; the reference's CUDA path needs it"}
+    record = {}
+    ref_bridge.load()
+    if projection is not None:
+        from causal_tuner.kernels.linear import project_group as reference_group
+        module, x, dy = projection
+        theirs = ref_bridge.mirror_projection(module)
+
+        def step():
+            y = reference_group((theirs,), x)[0]
+            torch.autograd.grad(y, (x, theirs.lora_A, theirs.lora_B), dy)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(10):
+            step()
+        stop.record()
+        torch.cuda.synchronize(device)
+        ms = start.elapsed_time(stop) / 10
+        record["projection_op"] = {"ms": ms, "tflops": projection_flops(16384) / (ms * 1e-3) / 1e12}
+        del theirs
+    # Policy pinned to this arm's: no layer checkpointing, the same MLP activation-cache budget.
+    theirs = ref_bridge.mirror_model(model)
+    trainer = ref_bridge.reference_trainer(theirs, device, loss_token_budget=4096)
+    for index in range(2):              # Triton compiles its kernels in the first update
+        metrics = trainer.update([dict(batch)], step=index, total_steps=1 << 20)
+    torch.cuda.synchronize(device)
+    steps = 3
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for index in range(steps):
+        metrics = trainer.update([dict(batch)], step=2 + index, total_steps=1 << 20)
+    stop.record()
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(stop) / steps
+    record.update({"value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
+                   "loss": metrics["loss"], "execution": {k: v for k, v in metrics["execution"][0].items()},
+                   "what": "reference CausalLM + Trainer.update from oracle/_ref (Triton + cuBLAS + FlashAttention-2), "
+                           "same packed NF4 weights, adapters and batch, same GPU, 1 GPU"})
+    return record
+
+
+# DRAM traffic of the tcgen05 GEMM kernels, from the ncu capture summarised in
+# profiles/step7b_one_layer_gemm_dram_traffic.md: one decoder layer of this workload (16384 tokens, forward +
+# backward, MLP activations kept), `dram__bytes_read.sum + dram__bytes_write.sum` summed over that layer's
+# GEMM launches. Every layer launches the same GEMMs on the same shapes, so a step is `layers` times this.
+LAYER_GEMM_DRAM_BYTES = {"step7b": None, "step1b": None}
+LAYER_GEMM_LAUNCHES = {"step7b": None, "step1b": None}
+
+
+def gemm_traffic(workload, config, launches_per_step):
+    """`traffic` (DRAM bytes per GEMM launch, averaged over the launches of a step) and the operand bytes the
+    same launches need at least, for the roofline record; None while no capture of this workload is on file."""
+    per_layer = LAYER_GEMM_DRAM_BYTES.get(workload)
+    if not per_layer or not launches_per_step:
+        return {"traffic": None}
+    layers = config["num_hidden_layers"]
+    return {"traffic": per_layer * layers / launches_per_step,
+            "traffic_note": (f"ncu dram__bytes_read.sum + dram__bytes_write.sum over the GEMM launches of ONE decoder layer "
+                             f"(forward + backward, this workload's token count) x {layers} layers / GEMM launches per step; "
+                             f"the head's two GEMMs per loss tile are not in the capture")}
 
 
 def run_step(args):
@@ -440,6 +609,9 @@ def run_step(args):
         dist.init_process_group("nccl", device_id=device)
     _lib.load()
     spec = bench_step.WORKLOADS[args.workload]
+    if args.layers:        # profiler-sized case: fewer layers of the same shapes (not a bench value)
+        spec = dict(spec, config=dict(spec["config"], num_hidden_layers=args.layers))
+        bench_step.WORKLOADS[args.workload] = spec
     model = bench_step.build_model(args.workload, device, args.mlp_cache_gib, keep_low_rank=bool(args.keep_low_rank))
     optimizer = make_optimizer(model, learning_rate=2e-5)
     trainer = Trainer(model, optimizer, device=device, loss_token_budget=4096)
@@ -505,10 +677,25 @@ def run_step(args):
         recompute = {"value": tokens_per_rank * world_size / (recompute_ms * 1e-3), "unit": "tokens/s",
                      "ms_per_step": recompute_ms, "peak_memory_gb": torch.cuda.max_memory_allocated(device) / 1e9}
         model.last_execution = execution
+        model.runtime.mlp_cache_budget_bytes = int(args.mlp_cache_gib * 2**30) or None
+        for module in model.modules():
+            if hasattr(module, "keep_low_rank"):
+                module.keep_low_rank = bool(args.keep_low_rank)
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
         return
+    # Reported beside the line, measured after it (N = 1 only): configs[1] in this process, and the unmodified
+    # reference's CUDA path on the same GPU, weights and batch.
+    projection_op, reference_gpu = None, None
+    if world_size == 1 and not args.no_extras:
+        trainer.optimizer.zero_grad(set_to_none=True)
+        projection_op, module, x, dy = projection_op_record(device)
+        try:
+            reference_gpu = reference_gpu_record(model, device, device_batch, tokens_per_rank, (module, x, dy))
+        except Exception as error:      # a reported extra must not take the bench line down with it
+            reference_gpu = {"unavailable": f"{type(error).__name__}: {error}"[:300]}
+        del module, x, dy
     peaks, peak_kind = measured_peaks()
     peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
     tokens = tokens_per_rank * world_size
@@ -529,12 +716,14 @@ def run_step(args):
         "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel / gemm_tcgen05_pair_kernel",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
                      "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
-                     "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps, "traffic": None},
+                     "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps,
+                     **gemm_traffic(args.workload, spec["config"], kernel_launches / args.steps)},
         "clocks": clocks, "loss_first": losses[0], "loss_last": losses[-1],
         "peak_memory_gb": peak_memory / 1e9, "mlp_recompute_everywhere": recompute,
+        "projection_op": projection_op, "reference_gpu": reference_gpu,
     }
     if world_size == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = bench_step.cpu_estimate(args.workload)
+        line["cpu_baseline"] = reference_cpu_line(args.workload, steps=3, warmup=1)[2]
     print(json.dumps(line), flush=True)
     if distributed:
         dist.destroy_process_group()
@@ -551,6 +740,10 @@ def main():
                         help="tokens per GPU; anything but the default is a profiler-sized case, not a bench value")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiler captures)")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the projection_op and reference_gpu records (profiler captures)")
+    parser.add_argument("--layers", type=int, default=0,
+                        help="decoder layers of a step workload; anything but the default is a profiler-sized case")
     parser.add_argument("--keep-low-rank", type=int, choices=(0, 1), default=1,
                         help="keep the low-rank inputs x.A^T (q/k/v/o in the step workloads) for backward (1) or recompute them as the reference does (0)")
     parser.add_argument("--no-recompute-arm", action="store_true",

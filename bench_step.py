@@ -69,7 +69,71 @@ def build_model(name, device, mlp_cache_gib=0, keep_low_rank=False):
     return model
 
 
-# ---- CPU leg: the reference composition on a bounded sample -------------------------------------
+# ---- CPU leg: the unmodified reference (oracle/_ref) on its own CPU branch ---------------------------
+class ReferenceCpuStep:
+    """The reference's `CausalLM` + `Trainer.update` (training/engine.py:41-111), installed unmodified in
+    oracle/_ref, on the host cores: the workload's full architecture (all layers, head, AdamW over every
+    adapter), its non-CUDA branch (dense bf16 base weights because its NF4 path refuses non-CUDA devices,
+    modeling/lora.py:44-45; "vanilla" attention, kernels/reference.py:19-27, which caps a call at
+    batch x heads x length^2 <= 2^23 scores). A step is one whole optimizer update on ONE packed row of
+    CPU_SAMPLE_TOKENS tokens - a bounded sample of the workload's rows; per-token cost is what scales."""
+
+    def __init__(self, name, threads):
+        from oracle import ref_bridge
+        ref_bridge.load()
+        from causal_tuner.modeling.config import ModelConfig
+        from causal_tuner.modeling.model import CausalLM, Runtime
+        torch.set_num_threads(threads)
+        self.spec = WORKLOADS[name]
+        config = ModelConfig(pad_token_id=0, eos_token_id=1, **self.spec["config"])
+        runtime = Runtime(rank=RANK, attention="vanilla", checkpoint=False)
+        torch.manual_seed(2024)
+        started = time.perf_counter()
+        # Built on the meta device and filled from one random block per parameter: drawing 7e9 normal
+        # samples on the host would take minutes and the timed arithmetic does not depend on the values.
+        self.model = CausalLM(config, runtime, "meta").to_empty(device="cpu")
+        block = torch.randn(1 << 20)
+        with torch.no_grad():
+            for parameter_name, parameter in self.model.named_parameters():
+                scale = 1.0 if "norm" in parameter_name else (.01 if parameter_name.endswith("lora_B") else .02)
+                flat = parameter.view(-1)
+                source = (block * scale).to(parameter.dtype)
+                if "norm" in parameter_name:
+                    source = source.abs() + .5
+                for start in range(0, flat.numel(), source.numel()):
+                    stop = min(start + source.numel(), flat.numel())
+                    flat[start:stop] = source[:stop - start]
+        self.build_seconds = time.perf_counter() - started
+        self.trainer = ref_bridge.reference_trainer(self.model, "cpu", loss_token_budget=128)
+        self.updates = 0
+        self.resize(CPU_SAMPLE_TOKENS)
+
+    def resize(self, tokens):
+        """Use one packed row of `tokens` tokens per update (a slow host gets a smaller sample)."""
+        self.tokens = tokens
+        self.batch = synthetic_batch(1, tokens, self.spec["config"]["vocab_size"], seed=1000)
+
+    def step(self):
+        metrics = self.trainer.update([dict(self.batch)], step=self.updates, total_steps=1 << 20)
+        self.updates += 1
+        return metrics
+
+    def sample_text(self, steps):
+        c = self.spec["config"]
+        return (f"{steps} whole optimizer updates of the reference's own CausalLM/Trainer (oracle/_ref, unmodified) on the host "
+                f"cores: all {c['num_hidden_layers']} layers + head + AdamW, bf16 compute with dense base weights and "
+                f"'vanilla' attention (its non-CUDA branch), one packed row of {self.tokens} of the workload's "
+                f"{self.spec['rows'] * self.spec['length']} tokens per update (so AdamW's per-update cost is spread over "
+                f"{self.tokens} tokens instead of {self.spec['rows'] * self.spec['length']}); model built in "
+                f"{self.build_seconds:.0f} s")
+
+
+def reference_cpu_available():
+    from oracle import ref_bridge
+    return ref_bridge.available()
+
+
+# ---- CPU leg when oracle/_ref is absent: the oracle's restatement on a bounded sample -------------------
 class CpuLayerSample:
     """One decoder layer and the head of the workload on CPU_SAMPLE_TOKENS tokens, forward and backward
     through oracle/model.py (the restatement of the reference's CPU branch). A whole step costs

@@ -39,6 +39,8 @@
 #include <cudaTypedefs.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -654,7 +656,39 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 // Tensor map over a bf16 matrix whose contiguous dimension has `inner` elements and
 // whose rows are `ld` elements apart; tiles are `box_rows` rows of 64 elements.
+// Encoding a map is a driver call of a microsecond or two and a training step asks for the same few
+// hundred (pointer, shape) combinations over and over (the caching allocator hands the same blocks back),
+// so encoded maps are kept in a small direct-mapped table. A map depends on nothing but its key.
+struct MapKey {
+  const void* base;
+  int64_t inner, outer, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 4096;
+MapSlot g_map_table[kMapSlots];
+std::mutex g_map_mutex;
+
 int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_rows) {
+  const MapKey key{base, inner, outer, ld, box_rows};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h = (h ^ static_cast<uint64_t>(inner) * 0x9E3779B97F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
+  h = (h ^ static_cast<uint64_t>(outer) * 0x94D049BB133111EBull ^ static_cast<uint64_t>(ld) << 7 ^ static_cast<uint64_t>(box_rows)) * 0x9E3779B97F4A7C15ull;
+  MapSlot& slot = g_map_table[(h >> 32) % kMapSlots];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (slot.used && slot.key == key) {
+      std::memcpy(map, &slot.map, sizeof(CUtensorMap));
+      return CT_OK;
+    }
+  }
   auto fn = encode_fn();
   if (!fn) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
@@ -665,6 +699,12 @@ int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, i
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    slot.key = key;
+    std::memcpy(&slot.map, map, sizeof(CUtensorMap));
+    slot.used = true;
+  }
   return CT_OK;
 }
 
@@ -740,9 +780,13 @@ bool gemm_tcgen05_supported(const GemmArgs& g) {
 // CTA pairs pay off once a tile's 256 rows are real rows; products with fewer than 256 rows stay
 // on the single-CTA kernel.
 // The environment variable CT_B200_GEMM_CTAS (1 or 2) pins the choice for experiments and tests.
+int env_int(const char* name, int fallback) {
+  const char* text = getenv(name);
+  return text ? atoi(text) : fallback;
+}
+
 int ctas_for(const GemmArgs& g) {
-  const char* text = getenv("CT_B200_GEMM_CTAS");
-  const int pinned = text ? atoi(text) : 0;
+  const int pinned = env_int("CT_B200_GEMM_CTAS", 0);   // read per call: tests and comparison runs switch it in-process
   if (pinned == 1 || pinned == 2) return pinned;
   return g.M >= 2 * BM ? 2 : 1;
 }
@@ -806,8 +850,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   p.m_tiles = static_cast<int>((g.M + tile_m - 1) / tile_m);
   p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
   {
-    const char* text = getenv("CT_B200_GEMM_GROUP_M");
-    const int value = text ? atoi(text) : 0;
+    const int value = env_int("CT_B200_GEMM_GROUP_M", 0);
     p.group_m = value > 0 ? value : GROUP_M;
   }
   p.M = g.M;
@@ -835,8 +878,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   if (ctas == 2) {
     // Default: 3 stages of two 64-wide k-blocks (one barrier round per 8 MMAs). CT_B200_GEMM_KSUB=1
     // selects 6 stages of one k-block (one round per 4 MMAs) for comparison runs.
-    const char* ksub_text = getenv("CT_B200_GEMM_KSUB");
-    const int ksub = ksub_text ? atoi(ksub_text) : 2;
+    const int ksub = env_int("CT_B200_GEMM_KSUB", 2);
     rc = ksub == 1 ? launch_pair<6, 1>(p, grid, device, stream) : launch_pair<3, 2>(p, grid, device, stream);
   } else {
     rc = launch_single(p, grid, device, stream);

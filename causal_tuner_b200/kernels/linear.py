@@ -408,7 +408,6 @@ class _LoRAGroup(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dtype, tile, states, cosine, sine, head_dim, residual, *parameters):
         _lib.require_cuda(x)
-        ctx.save_for_backward(x, cosine, sine, *parameters)
         ctx.dtype, ctx.states, ctx.head_dim = dtype, states, head_dim
         flat = cast(x.reshape(-1, x.shape[-1]), dtype)
         rows = flat.shape[0]
@@ -421,7 +420,7 @@ class _LoRAGroup(torch.autograd.Function):
         outputs = []
         stacked = len(states) > 1 and step >= rows > 0
         keep = bool(getattr(_policy, "keep_low_rank", False)) and step >= rows > 0
-        ctx.low_rank = None
+        kept = ()         # with `keep`: (low-rank inputs, cast a [stacked], cast b per projection) for backward
         decoded = None
         if stacked:
             # Untiled group (q/k/v): the low-rank inputs of all projections in one product over x,
@@ -434,13 +433,12 @@ class _LoRAGroup(torch.autograd.Function):
             b_cast, bias_cast = others[:count], others[count:]
             xa_all = torch.empty((rows, a_all.shape[0]), device=x.device, dtype=dtype)
             matmul(flat, a_all.T, out=xa_all)
+            if keep:
+                kept = (xa_all, a_all, *b_cast)
             del a_all
             pending.wait()
-            if keep:
-                ctx.low_rank = xa_all
         elif keep:
             workspace = torch.empty((rows, widest), device=x.device, dtype=dtype)   # its own buffer: it outlives the call
-            ctx.low_rank = workspace[:, :parameters[1].shape[0]]
         for index, state in enumerate(states):
             weight, a, b, bias = parameters[4 * index:4 * index + 4]
             matrix = decoded[index] if decoded is not None else materialize(weight, state, dtype)
@@ -460,7 +458,12 @@ class _LoRAGroup(torch.autograd.Function):
                                xa=workspace[:stop - start, :a.shape[0]],
                                residual=shortcut[start:stop] if fuse_residual and index == 0 else None)
             outputs.append(out.reshape(*x.shape[:-1], matrix.shape[0]))
+            if keep and len(states) == 1:
+                kept = (workspace[:, :a.shape[0]], a16, b16)
             del matrix, a16, b16
+        # Saved through autograd (not as attributes) so that checkpointing and saved-tensor hooks see them.
+        ctx.kept = len(kept)
+        ctx.save_for_backward(x, cosine, sine, *parameters, *kept)
         if head_dim:
             core_cuda.rotate_owned_qk(outputs[0], outputs[1], cosine, sine, head_dim)
         if residual is not None and not fuse_residual:
@@ -470,6 +473,9 @@ class _LoRAGroup(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grad_outputs):
         x, cosine, sine, *parameters = ctx.saved_tensors
+        kept = tuple(parameters[len(parameters) - ctx.kept:]) if ctx.kept else ()
+        if ctx.kept:
+            parameters = parameters[:len(parameters) - ctx.kept]
         dtype, states = ctx.dtype, ctx.states
         flat = cast(x.reshape(-1, x.shape[-1]), dtype)
         rows = flat.shape[0]
@@ -488,8 +494,16 @@ class _LoRAGroup(torch.autograd.Function):
         if want_dx and len(states) > 1 and step >= rows > 0:
             # Untiled group (q/k/v): one GEMM sums the input gradients of all projections.
             prepared = []
-            a_all, offsets, b_cast = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype,
-                                                    [parameters[4 * i + 2] for i in range(len(states))])
+            if kept:
+                xa_kept, a_all, b_cast = kept[0], kept[1], list(kept[2:])
+                offsets, cursor = [], 0
+                for i in range(len(states)):
+                    offsets.append(cursor)
+                    cursor += parameters[4 * i + 1].shape[0]
+            else:
+                xa_kept = None
+                a_all, offsets, b_cast = stack_adapters([parameters[4 * i + 1] for i in range(len(states))], dtype,
+                                                        [parameters[4 * i + 2] for i in range(len(states))])
             total = a_all.shape[0]
             low_all = torch.empty((rows, total), device=x.device, dtype=dtype)
             decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
@@ -506,7 +520,7 @@ class _LoRAGroup(torch.autograd.Function):
                                  [p[2] for p in prepared], dx, [p[4] for p in prepared])
             # One product recomputes every projection's low-rank input, one more gives the stacked dA
             # (each reads x once); dB is per projection.
-            xa_all = ctx.low_rank
+            xa_all = xa_kept
             if xa_all is None:
                 xa_all = torch.empty((rows, total), device=x.device, dtype=dtype)
                 matmul(flat, a_all.T, out=xa_all)
@@ -525,7 +539,7 @@ class _LoRAGroup(torch.autograd.Function):
         for index, (state, grad) in enumerate(zip(states, grad_outputs)):
             weight, a, b, _ = parameters[4 * index:4 * index + 4]
             matrix = materialize(weight, state, dtype) if want_dx else None
-            a16, b16 = cast_many((a, b), dtype)
+            a16, b16 = (kept[1], kept[2]) if kept and len(states) == 1 else cast_many((a, b), dtype)
             dy = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
             make = torch.empty_like if rows else torch.zeros_like
             da, db = make(a), make(b)
@@ -543,8 +557,8 @@ class _LoRAGroup(torch.autograd.Function):
                     input_gradient(signal, matrix, a16, b16, dx[start:stop], low, add=index > 0)
                 else:
                     matmul(signal, b16, out=low)
-                if ctx.low_rank is not None and len(states) == 1:
-                    xa = ctx.low_rank          # kept by the forward pass (untiled: one slice)
+                if kept and len(states) == 1:
+                    xa = kept[0]               # kept by the forward pass (untiled: one slice)
                 else:
                     matmul(flat[start:stop], a16.T, out=xa)
                 parameter_gradients(flat[start:stop], signal, da, db, low, xa, add=start > 0)

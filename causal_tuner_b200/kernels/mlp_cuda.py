@@ -65,14 +65,18 @@ def silu_multiply(gate, up):
     return _SiLUMultiply.apply(gate, up)
 
 
-def _prepare(parameters, states, dtype, order=(0, 1, 2)):
+def _prepare(parameters, states, dtype, order=(0, 1, 2), casts=None):
     """Base weights decoding on the side stream in `order` (wait on the returned handle before a
     matrix is read), cast adapters, and the gate/up `a` matrices stacked row-wise (their low-rank
-    inputs come from one product over x)."""
+    inputs come from one product over x). `casts` = (stacked, b_gate, b_up, a_down, b_down) already in
+    `dtype` (kept by the forward pass) skips the conversion."""
     matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order)
-    stacked, offsets, others = stack_adapters([parameters[1], parameters[5]], dtype,
-                                              [parameters[2], parameters[6], parameters[9], parameters[10]])
     ranks = [parameters[1].shape[0], parameters[5].shape[0]]
+    if casts is not None:
+        stacked, others, offsets = casts[0], list(casts[1:]), [0, ranks[0]]
+    else:
+        stacked, offsets, others = stack_adapters([parameters[1], parameters[5]], dtype,
+                                                  [parameters[2], parameters[6], parameters[9], parameters[10]])
     adapters = [(stacked[offsets[i]:offsets[i] + ranks[i]], others[i]) for i in range(2)]
     adapters.append((others[2], others[3]))
     return matrices, adapters, stacked, pending
@@ -101,8 +105,10 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
         saved = (*(torch.empty((rows, width), device=x.device, dtype=dtype) for _ in range(2)),
                  kept[:, :ranks[0]], kept[:, ranks[0]:])
         if getattr(_policy, "keep_low_rank", False):
-            # this library's option: the down projection's low-rank input joins the cache as a fifth tensor
-            saved = (*saved, torch.empty((rows, ranks[2]), device=x.device, dtype=dtype))
+            # this library's option: the down projection's low-rank input joins the cache as a fifth tensor,
+            # followed by the adapters in the compute dtype (so that backward does not convert them again)
+            saved = (*saved, torch.empty((rows, ranks[2]), device=x.device, dtype=dtype),
+                     stacked, adapters[0][1], adapters[1][1], adapters[2][0], adapters[2][1])
     destination = output.view(rows, output.shape[-1])
     shortcut = None if residual is None else residual.reshape(rows, residual.shape[-1])
     for start in range(0, rows, step):
@@ -160,7 +166,8 @@ class _TiledLoRAMLP(torch.autograd.Function):
         dx = torch.empty_like(flat) if want_dx else None
         # Cached: the down projection's weight is needed first, gate/up only for the input gradient.
         matrices, adapters, stacked, pending = _prepare(parameters, ctx.states, dtype,
-                                                        (2, 0, 1) if ctx.cache else (0, 1, 2))
+                                                        (2, 0, 1) if ctx.cache else (0, 1, 2),
+                                                        casts=saved[5:10] if len(saved) >= 10 else None)
         ranks = [a.shape[0] for a, _ in adapters]
         make = torch.empty if rows else torch.zeros
         wide = dict(device=x.device, dtype=torch.float32)
