@@ -3,6 +3,9 @@
 // RoPE, the residual add and the ordered reduction of split-contraction
 // partial sums. All are grid-stride loops over 16-byte vectors where the
 // buffers allow it.
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace ct {
@@ -10,10 +13,33 @@ namespace {
 
 constexpr int kThreads = 256;
 
-inline unsigned grid_for(int64_t work_items) {
-  // Enough CTAs to fill 148 SMs eight times over, never more than the work.
+// Grid of a grid-stride kernel: exactly as many CTAs as are resident at once (SM count x CTAs per SM at this
+// kernel's register use), never more than the work. Every CTA then carries the same share of the work from
+// the first cycle to the last; a larger grid would run its surplus CTAs as a second, mostly empty wave.
+template <typename Kernel>
+unsigned grid_for(Kernel kernel, int64_t work_items) {
+  static std::mutex mutex;
+  static std::unordered_map<const void*, int> resident;      // kernel -> resident CTAs on the current device type
+  int64_t cap = 0;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    const void* key = reinterpret_cast<const void*>(kernel);
+    auto found = resident.find(key);
+    if (found == resident.end()) {
+      int device = 0, sms = 0, per_sm = 0;
+      if (cudaGetDevice(&device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || sms <= 0 ||
+          per_sm <= 0) {
+        cudaGetLastError();
+        sms = 148;
+        per_sm = 4;
+      }
+      found = resident.emplace(key, sms * per_sm).first;
+    }
+    cap = found->second;
+  }
   int64_t blocks = (work_items + kThreads - 1) / kThreads;
-  const int64_t cap = 148 * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<unsigned>(blocks);
@@ -124,38 +150,64 @@ swiglu_kernel(const T* gate, const T* up, const T* grad, T* out, T* dg, T* du, i
   }
 }
 
-// bf16, 8 elements (16 bytes) per thread per step; every buffer 16-byte aligned, n % 8 == 0.
+// bf16, 8 elements (16 bytes) per vector; every buffer 16-byte aligned, n % 8 == 0. A thread handles kSwigluUnroll
+// vectors per step and issues all of their loads before the first use: the outputs may alias the inputs
+// element for element (the in-place backward), so the compiler cannot move the next vector's loads above
+// this vector's stores by itself, and one vector in flight per thread leaves HBM latency exposed.
+constexpr int kSwigluUnroll = 2;
+
+__device__ __forceinline__ void swiglu_vector(const uint4& gv, const uint4& uv, const uint4& rv, bool backward,
+                                              bool reconstruct, uint4& hv, uint4& av, uint4& bv) {
+  const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+  uint32_t hw[4], aw[4], bw[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[j]));
+    const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[j]));
+    const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+    float h0 = 0.f, h1 = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+    swiglu_element<__nv_bfloat16>(g.x, u.x, r.x, backward, reconstruct, h0, a0, b0);
+    swiglu_element<__nv_bfloat16>(g.y, u.y, r.y, backward, reconstruct, h1, a1, b1);
+    __nv_bfloat162 hp = __floats2bfloat162_rn(h0, h1), ap = __floats2bfloat162_rn(a0, a1),
+                   bp = __floats2bfloat162_rn(b0, b1);
+    hw[j] = *reinterpret_cast<uint32_t*>(&hp);
+    aw[j] = *reinterpret_cast<uint32_t*>(&ap);
+    bw[j] = *reinterpret_cast<uint32_t*>(&bp);
+  }
+  hv = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+  av = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+  bv = make_uint4(bw[0], bw[1], bw[2], bw[3]);
+}
+
+template <bool BACKWARD>
 __global__ void __launch_bounds__(kThreads)
 swiglu_bf16_vec_kernel(const uint4* gate, const uint4* up, const uint4* grad, uint4* out, uint4* dg, uint4* du,
                        int64_t groups, int reconstruct) {
-  const bool backward = grad != nullptr;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < groups;
-       i += static_cast<int64_t>(gridDim.x) * kThreads) {
-    const uint4 gv = gate[i], uv = up[i];
-    uint4 rv = make_uint4(0, 0, 0, 0);
-    if (backward) rv = grad[i];
-    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-    uint32_t hw[4], aw[4], bw[4];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; base < groups;
+       base += stride * kSwigluUnroll) {
+    uint4 gv[kSwigluUnroll], uv[kSwigluUnroll], rv[kSwigluUnroll];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[j]));
-      const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[j]));
-      const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
-      float h0 = 0.f, h1 = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-      swiglu_element<__nv_bfloat16>(g.x, u.x, r.x, backward, reconstruct != 0, h0, a0, b0);
-      swiglu_element<__nv_bfloat16>(g.y, u.y, r.y, backward, reconstruct != 0, h1, a1, b1);
-      __nv_bfloat162 hp = __floats2bfloat162_rn(h0, h1), ap = __floats2bfloat162_rn(a0, a1),
-                     bp = __floats2bfloat162_rn(b0, b1);
-      hw[j] = *reinterpret_cast<uint32_t*>(&hp);
-      aw[j] = *reinterpret_cast<uint32_t*>(&ap);
-      bw[j] = *reinterpret_cast<uint32_t*>(&bp);
+    for (int k = 0; k < kSwigluUnroll; ++k) {
+      const int64_t i = base + k * stride;
+      const bool live = i < groups;
+      gv[k] = live ? gate[i] : make_uint4(0, 0, 0, 0);
+      uv[k] = live ? up[i] : make_uint4(0, 0, 0, 0);
+      rv[k] = (BACKWARD && live) ? grad[i] : make_uint4(0, 0, 0, 0);
     }
-    if (backward) {
-      dg[i] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
-      du[i] = make_uint4(bw[0], bw[1], bw[2], bw[3]);
+#pragma unroll
+    for (int k = 0; k < kSwigluUnroll; ++k) {
+      const int64_t i = base + k * stride;
+      if (i >= groups) break;
+      uint4 hv, av, bv;
+      swiglu_vector(gv[k], uv[k], rv[k], BACKWARD, reconstruct != 0, hv, av, bv);
+      if (BACKWARD) {
+        dg[i] = av;
+        du[i] = bv;
+      }
+      if (reconstruct) out[i] = hv;
     }
-    if (reconstruct) out[i] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
   }
 }
 
@@ -291,7 +343,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int reduce_partials(const float* partials, int slices, int64_t rows, int64_t cols, int64_t ld_partial, float* out,
                     int64_t ld_out, int add, cudaStream_t stream) {
   if (rows * cols == 0) return CT_OK;
-  reduce_partials_kernel<<<grid_for(rows * cols), kThreads, 0, stream>>>(partials, slices, rows, cols, ld_partial, out,
+  reduce_partials_kernel<<<grid_for(reduce_partials_kernel, rows * cols), kThreads, 0, stream>>>(partials, slices, rows, cols, ld_partial, out,
                                                                         ld_out, add);
   count_launch(false);
   return check_launch("reduce_partials");
@@ -310,10 +362,10 @@ extern "C" int ct_cast(const void* src, int src_dtype, int64_t ld_src, void* dst
   const int64_t total = rows * cols;
   if (src_dtype == CT_F32 && dst_dtype == CT_BF16 && ld_src == cols && ld_dst == cols && total % 8 == 0 &&
       aligned16(src) && aligned16(dst)) {
-    cast_f32_bf16_vec_kernel<<<grid_for(total / 8), kThreads, 0, s>>>(static_cast<const float4*>(src),
+    cast_f32_bf16_vec_kernel<<<grid_for(cast_f32_bf16_vec_kernel, total / 8), kThreads, 0, s>>>(static_cast<const float4*>(src),
                                                                      static_cast<uint4*>(dst), total / 8);
   } else {
-    cast_kernel<<<grid_for(total), kThreads, 0, s>>>(src, src_dtype, ld_src, dst, dst_dtype, ld_dst, rows, cols);
+    cast_kernel<<<grid_for(cast_kernel, total), kThreads, 0, s>>>(src, src_dtype, ld_src, dst, dst_dtype, ld_dst, rows, cols);
   }
   count_launch(false);
   return check_launch("ct_cast");
@@ -346,7 +398,7 @@ extern "C" int ct_cast_many(int count, const void* const* src, void* const* dst,
       if (sizes[i] % 8 || !aligned16(src[i]) || !aligned16(dst[i])) batch.vec = 0;
     }
     if (batch.count == 0) continue;
-    cast_many_kernel<<<grid_for(static_cast<int64_t>(batch.first_chunk[batch.count]) * kThreads), kThreads, 0, s>>>(
+    cast_many_kernel<<<grid_for(cast_many_kernel, static_cast<int64_t>(batch.first_chunk[batch.count]) * kThreads), kThreads, 0, s>>>(
         batch, src_dtype, dst_dtype);
     count_launch(false);
   }
@@ -364,21 +416,22 @@ extern "C" int ct_swiglu(const void* gate, const void* up, const void* grad, voi
     const bool vec = n % 8 == 0 && aligned16(gate) && aligned16(up) && (!grad || aligned16(grad)) &&
                      (!reconstruct || aligned16(out)) && (!grad || (aligned16(dg) && aligned16(du)));
     if (vec)
-      swiglu_bf16_vec_kernel<<<grid_for(n / 8), kThreads, 0, s>>>(
+      (grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>)<<<
+          grid_for(grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>, n / 8), kThreads, 0, s>>>(
           static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<const uint4*>(grad),
           static_cast<uint4*>(out), static_cast<uint4*>(dg), static_cast<uint4*>(du), n / 8, reconstruct);
     else
-      swiglu_kernel<__nv_bfloat16><<<grid_for(n), kThreads, 0, s>>>(
+      swiglu_kernel<__nv_bfloat16><<<grid_for(swiglu_kernel<__nv_bfloat16>, n), kThreads, 0, s>>>(
           static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
           static_cast<const __nv_bfloat16*>(grad), static_cast<__nv_bfloat16*>(out),
           static_cast<__nv_bfloat16*>(dg), static_cast<__nv_bfloat16*>(du), n, reconstruct);
   } else if (dtype == CT_F32) {
-    swiglu_kernel<float><<<grid_for(n), kThreads, 0, s>>>(static_cast<const float*>(gate), static_cast<const float*>(up),
+    swiglu_kernel<float><<<grid_for(swiglu_kernel<float>, n), kThreads, 0, s>>>(static_cast<const float*>(gate), static_cast<const float*>(up),
                                                           static_cast<const float*>(grad), static_cast<float*>(out),
                                                           static_cast<float*>(dg), static_cast<float*>(du), n,
                                                           reconstruct);
   } else if (dtype == CT_F16) {
-    swiglu_kernel<__half><<<grid_for(n), kThreads, 0, s>>>(static_cast<const __half*>(gate),
+    swiglu_kernel<__half><<<grid_for(swiglu_kernel<__half>, n), kThreads, 0, s>>>(static_cast<const __half*>(gate),
                                                            static_cast<const __half*>(up),
                                                            static_cast<const __half*>(grad), static_cast<__half*>(out),
                                                            static_cast<__half*>(dg), static_cast<__half*>(du), n,
@@ -404,28 +457,28 @@ extern "C" int ct_rope(const void* x, const void* cosine, const void* sine, void
     const int rotated_only = x == y;
     const int64_t work = rows * heads * (rotated_only ? half / 4 : head_dim / 8);
     if (dtype == CT_BF16)
-      rope_vec_kernel<__nv_bfloat16><<<grid_for(work), kThreads, 0, s>>>(
+      rope_vec_kernel<__nv_bfloat16><<<grid_for(rope_vec_kernel<__nv_bfloat16>, work), kThreads, 0, s>>>(
           static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cosine),
           static_cast<const __nv_bfloat16*>(sine), static_cast<__nv_bfloat16*>(y), rows, heads, head_dim, half, inverse,
           rotated_only);
     else
-      rope_vec_kernel<__half><<<grid_for(work), kThreads, 0, s>>>(
+      rope_vec_kernel<__half><<<grid_for(rope_vec_kernel<__half>, work), kThreads, 0, s>>>(
           static_cast<const __half*>(x), static_cast<const __half*>(cosine), static_cast<const __half*>(sine),
           static_cast<__half*>(y), rows, heads, head_dim, half, inverse, rotated_only);
     count_launch(false);
     return check_launch("ct_rope");
   }
   if (dtype == CT_BF16)
-    rope_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+    rope_kernel<__nv_bfloat16><<<grid_for(rope_kernel<__nv_bfloat16>, total), kThreads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cosine),
         static_cast<const __nv_bfloat16*>(sine), static_cast<__nv_bfloat16*>(y), rows, heads, head_dim, half, inverse);
   else if (dtype == CT_F32)
-    rope_kernel<float><<<grid_for(total), kThreads, 0, s>>>(static_cast<const float*>(x),
+    rope_kernel<float><<<grid_for(rope_kernel<float>, total), kThreads, 0, s>>>(static_cast<const float*>(x),
                                                             static_cast<const float*>(cosine),
                                                             static_cast<const float*>(sine), static_cast<float*>(y),
                                                             rows, heads, head_dim, half, inverse);
   else if (dtype == CT_F16)
-    rope_kernel<__half><<<grid_for(total), kThreads, 0, s>>>(static_cast<const __half*>(x),
+    rope_kernel<__half><<<grid_for(rope_kernel<__half>, total), kThreads, 0, s>>>(static_cast<const __half*>(x),
                                                              static_cast<const __half*>(cosine),
                                                              static_cast<const __half*>(sine), static_cast<__half*>(y),
                                                              rows, heads, head_dim, half, inverse);
@@ -442,15 +495,15 @@ extern "C" int ct_add_inplace(void* y, const void* r, int64_t n, int dtype, void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == CT_BF16) {
     if (n % 8 == 0 && aligned16(y) && aligned16(r))
-      add_bf16_vec_kernel<<<grid_for(n / 8), kThreads, 0, s>>>(static_cast<uint4*>(y), static_cast<const uint4*>(r),
+      add_bf16_vec_kernel<<<grid_for(add_bf16_vec_kernel, n / 8), kThreads, 0, s>>>(static_cast<uint4*>(y), static_cast<const uint4*>(r),
                                                                n / 8);
     else
-      add_kernel<__nv_bfloat16><<<grid_for(n), kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(y),
+      add_kernel<__nv_bfloat16><<<grid_for(add_kernel<__nv_bfloat16>, n), kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(y),
                                                                  static_cast<const __nv_bfloat16*>(r), n);
   } else if (dtype == CT_F32) {
-    add_kernel<float><<<grid_for(n), kThreads, 0, s>>>(static_cast<float*>(y), static_cast<const float*>(r), n);
+    add_kernel<float><<<grid_for(add_kernel<float>, n), kThreads, 0, s>>>(static_cast<float*>(y), static_cast<const float*>(r), n);
   } else if (dtype == CT_F16) {
-    add_kernel<__half><<<grid_for(n), kThreads, 0, s>>>(static_cast<__half*>(y), static_cast<const __half*>(r), n);
+    add_kernel<__half><<<grid_for(add_kernel<__half>, n), kThreads, 0, s>>>(static_cast<__half*>(y), static_cast<const __half*>(r), n);
   } else {
     return fail(CT_ERR_ARG, "ct_add_inplace: dtype %d", dtype);
   }
@@ -466,13 +519,13 @@ extern "C" int ct_position_values(const int64_t* positions, const float* inverse
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = count * half;
   if (dtype == CT_BF16)
-    position_values_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+    position_values_kernel<__nv_bfloat16><<<grid_for(position_values_kernel<__nv_bfloat16>, total), kThreads, 0, s>>>(
         positions, inverse, static_cast<__nv_bfloat16*>(cosine), static_cast<__nv_bfloat16*>(sine), total, half);
   else if (dtype == CT_F16)
-    position_values_kernel<__half><<<grid_for(total), kThreads, 0, s>>>(
+    position_values_kernel<__half><<<grid_for(position_values_kernel<__half>, total), kThreads, 0, s>>>(
         positions, inverse, static_cast<__half*>(cosine), static_cast<__half*>(sine), total, half);
   else if (dtype == CT_F32)
-    position_values_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
+    position_values_kernel<float><<<grid_for(position_values_kernel<float>, total), kThreads, 0, s>>>(
         positions, inverse, static_cast<float*>(cosine), static_cast<float*>(sine), total, half);
   else
     return fail(CT_ERR_ARG, "ct_position_values: dtype %d", dtype);

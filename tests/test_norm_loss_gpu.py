@@ -154,7 +154,7 @@ def test_trainable_head_gradients_for_every_row_layout(dtype, reuse, layout):
     for mine, reference in zip(first, torch.autograd.grad(expected, (oracle_x, oracle_head))):
         torch.testing.assert_close(mine, reference, rtol=bound, atol=bound)
     assert first[1].dtype == torch.float32
-    for mine, again in zip(first, torch.autograd.grad(actual, (leaf, head))):
+    for mine, again in zip(first, torch.autograd.grad(actual, (leaf, head), retain_graph=True)):
         assert torch.equal(mine, again)
     assert torch.equal(leaf.detach(), values)
     doubled = torch.autograd.grad(actual * 2, (leaf, head))
