@@ -516,7 +516,7 @@ def projection_op_record(device, steps=20):
     return record, module, x, dy
 
 
-def reference_gpu_record(model, device, batch, tokens, projection=None):
+def reference_gpu_record(model, device, batch, tokens, projection=None, table=None):
     """The unmodified reference (oracle/_ref) on this GPU: its Triton kernels, cuBLAS and FlashAttention-2 through
     its own `Trainer.update`, on a replica that shares this model's packed NF4 weights and starts from copies of
     its adapters, same batch; and its `project_group` on configs[1]. A reported comparison only."""
@@ -563,11 +563,95 @@ def reference_gpu_record(model, device, batch, tokens, projection=None):
     stop.record()
     torch.cuda.synchronize(device)
     ms = start.elapsed_time(stop) / steps
+    if table:
+        kernel_table(lambda: trainer.update([dict(batch)], step=5, total_steps=1 << 20), table,
+                     "one update of the unmodified reference (oracle/_ref: Triton + cuBLAS + FlashAttention-2), same weights and batch")
     record.update({"value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
                    "loss": metrics["loss"], "execution": {k: v for k, v in metrics["execution"][0].items()},
                    "what": "reference CausalLM + Trainer.update from oracle/_ref (Triton + cuBLAS + FlashAttention-2), "
                            "same packed NF4 weights, adapters and batch, same GPU, 1 GPU"})
     return record
+
+
+def kernel_table(update, path, title):
+    """Device time per kernel of ONE update under torch.profiler (CUPTI), written to `path` as a text table.
+    Diagnostic: kernels run serialised and slightly slower under the profiler; compare rows, not the total
+    with a bench value."""
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as session:
+        update()
+        torch.cuda.synchronize()
+    rows = []
+    for event in session.key_averages():
+        total = getattr(event, "device_time_total", None)
+        if total is None:
+            total = getattr(event, "cuda_time_total", 0)
+        if total > 0:
+            rows.append((total, event.count, event.key))
+    rows.sort(reverse=True)
+    grand = sum(row[0] for row in rows) or 1
+    with open(path, "w") as handle:
+        handle.write(f"{title}\ntotal device time {grand / 1000:.2f} ms in {sum(r[1] for r in rows)} launches\n")
+        for total, count, name in rows[:60]:
+            handle.write(f"{total / 1000:10.2f} ms {100 * total / grand:5.1f} %  n={count:5d}  {name[:140]}\n")
+
+
+# The GEMM shapes of one decoder layer of step7b (16384 tokens): (name, M, N, K, layout). NT: B given as [N, K]
+# (forward products); NN: B given as [K, N] (input gradients, dy . W); TN: both operands token-major, fp32 output
+# (adapter gradients).
+STEP_SHAPES = [("fwd gate/up", 16384, 14336, 4352, "NT"), ("fwd q/o", 16384, 4096, 4352, "NT"),
+               ("fwd down", 16384, 4096, 14592, "NT"), ("dx down", 16384, 14336, 4352, "NN"),
+               ("dx gate+up", 16384, 4096, 29184, "NN"), ("dx o", 16384, 4096, 4352, "NN"),
+               ("x.A^T", 16384, 256, 4096, "NT"), ("x.A^T q/k/v", 16384, 768, 4096, "NT"),
+               ("dy.B gate", 16384, 256, 14336, "NN"), ("k/v forward", 16384, 128, 4352, "NT"),
+               ("dB gate", 14336, 256, 16384, "TN"), ("dA down", 256, 14336, 16384, "TN"),
+               ("dB q", 4096, 256, 16384, "TN"), ("dA q/k/v", 768, 4096, 16384, "TN")]
+
+
+def run_shapes(args):
+    """`--workload shapes`: every GEMM shape of a step7b layer through this library's tcgen05 kernels and through
+    torch.matmul (cuBLAS) on the same operands, alternating bursts of about 60 ms, best of two; one JSON line.
+    A same-device yardstick for the kernels, not a bench line."""
+    from causal_tuner_b200.kernels import linear
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    device = torch.device("cuda", 0)
+    make = lambda *shape: (torch.randn(*shape, device=device) * .1).bfloat16()
+
+    def burst(function, count):
+        function()
+        function()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            function()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count * 1000
+
+    table = {}
+    for name, m, n, k, layout in STEP_SHAPES:
+        if layout == "TN":
+            left, right = make(k, m), make(k, n)
+            ours_out, library_out = (torch.empty(m, n, device=device) for _ in range(2))
+            ours = lambda: linear.token_gradient(left, right, ours_out)
+            library = lambda: torch.mm(left.T, right, out_dtype=torch.float32, out=library_out)
+        else:
+            left = make(m, k)
+            right = make(n, k).T if layout == "NT" else make(k, n)
+            ours_out, library_out = (torch.empty(m, n, device=device, dtype=torch.bfloat16) for _ in range(2))
+            ours = lambda: linear.matmul(left, right, out=ours_out)
+            library = lambda: torch.mm(left, right, out=library_out)
+        flop = 2 * m * n * k
+        count = max(20, int(6e4 / (flop / 1.3e15 * 1e6)))
+        best = [min(burst(f, count) for _ in range(2)) for f in (ours, library)]
+        table[name] = {"M": m, "N": n, "K": k, "layout": layout, "ours_us": best[0], "cublas_us": best[1],
+                       "ours_tflops": flop / best[0] / 1e6, "cublas_tflops": flop / best[1] / 1e6,
+                       "rel_diff": ((ours_out.float() - library_out.float()).norm() / library_out.float().norm()).item()}
+        del left, right, ours_out, library_out
+    print(json.dumps({"workload": "shapes (GEMMs of one step7b layer, ours vs torch.matmul on the same GPU)", "shapes": table}),
+          flush=True)
 
 
 # DRAM traffic of the tcgen05 GEMM kernels, from the ncu capture summarised in
@@ -687,12 +771,16 @@ def run_step(args):
         return
     # Reported beside the line, measured after it (N = 1 only): configs[1] in this process, and the unmodified
     # reference's CUDA path on the same GPU, weights and batch.
+    if args.kernel_table:
+        kernel_table(lambda: trainer.update([device_batch]), args.kernel_table + "_ours.txt",
+                     f"{args.workload}: one update of this library (MLP cache budget {args.mlp_cache_gib} GiB)")
     projection_op, reference_gpu = None, None
     if world_size == 1 and not args.no_extras:
         trainer.optimizer.zero_grad(set_to_none=True)
         projection_op, module, x, dy = projection_op_record(device)
         try:
-            reference_gpu = reference_gpu_record(model, device, device_batch, tokens_per_rank, (module, x, dy))
+            reference_gpu = reference_gpu_record(model, device, device_batch, tokens_per_rank, (module, x, dy),
+                                                 table=args.kernel_table and args.kernel_table + "_reference_gpu.txt")
         except Exception as error:      # a reported extra must not take the bench line down with it
             reference_gpu = {"unavailable": f"{type(error).__name__}: {error}"[:300]}
         del module, x, dy
@@ -751,12 +839,18 @@ def main():
     parser.add_argument("--mlp-cache-gib", type=float, default=64.0,
                         help="per-GPU byte budget for keeping MLP gate/up activations instead of recomputing them "
                              "(0: always recompute)")
-    parser.add_argument("--workload", choices=("step7b", "step1b", "projection"), default="step7b",
+    parser.add_argument("--workload", choices=("step7b", "step1b", "projection", "shapes"), default="step7b",
                         help="step7b: 7B-class decoder update (the headline metric); step1b: the 1.3B decoder; "
-                             "projection: one fused NF4+LoRA projection, forward+backward")
+                             "projection: one fused NF4+LoRA projection, forward+backward; shapes: the GEMM shapes of a "
+                             "step7b layer against torch.matmul (a diagnostic table, not a bench line)")
+    parser.add_argument("--kernel-table", default=None, metavar="PREFIX",
+                        help="also write per-kernel device-time tables of one update (torch.profiler) to PREFIX_ours.txt "
+                             "and, with the reference_gpu record, PREFIX_reference_gpu.txt")
     args = parser.parse_args()
     ROWS = args.rows
-    if args.workload == "projection":
+    if args.workload == "shapes":
+        run_shapes(args)
+    elif args.workload == "projection":
         run_reference(args) if args.impl == "reference" else run_ours(args)
     else:
         run_step_reference(args) if args.impl == "reference" else run_step(args)

@@ -41,6 +41,8 @@ SIGNATURES = {
     "ct_rope": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "ct_accumulate_workspace": (_L, [_L, _L, _L, _I, _I]),
     "ct_accumulate": (_I, [_P, _L, _P, _L, _P, _L, _L, _L, _I, _I, _P, _I, _P]),
+    "ct_token_gradients_group_workspace": (_L, [_I, _P, _P, _L, _I, _I]),
+    "ct_token_gradients_group": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _P, _I, _P]),
     "ct_cast_many": (_I, [_I, _P, _P, _P, _I, _I, _P]),
     "ct_position_values": (_I, [_P, _P, _P, _P, _L, _I, _I, _P]),
     "ct_add_inplace": (_I, [_P, _P, _L, _I, _P]),

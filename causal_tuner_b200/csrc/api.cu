@@ -377,6 +377,113 @@ extern "C" int ct_accumulate(const void* left, int64_t ld_left, const void* righ
                            static_cast<cudaStream_t>(stream));
 }
 
+// ---- several token contractions in one launch ---------------------------------------------------
+namespace {
+constexpr int kMaxTokenGroup = 6;
+
+// One slice count for the whole group (every product contracts over the same T): the cheapest of 1..16 by the
+// cost model of gradient_splits applied to the group's tile total. A function of the shapes alone.
+int group_splits(int count, const int64_t* rows, const int64_t* cols, int64_t T) {
+  int64_t tiles = 0;
+  for (int i = 0; i < count; ++i) tiles += ((rows[i] + 255) / 256) * ((cols[i] + 255) / 256);
+  const int64_t k_blocks = (T + 63) / 64, slots = 74;
+  if (tiles <= 0) return 1;
+  int64_t best = 1, best_cost = -1;
+  for (int64_t s = 1; s <= 16 && s * 8 <= (k_blocks > 8 ? k_blocks : 8); ++s) {
+    const int64_t rounds = (tiles * s + slots - 1) / slots;
+    const int64_t cost = rounds * ((k_blocks + s - 1) / s + 16) + (s > 1 ? 4 * s : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return static_cast<int>(best);
+}
+
+bool group_on_tensor_cores(int count, const void* const* left, const int64_t* ld_left, const void* const* right,
+                           const int64_t* ld_right, float* const* out, const int64_t* rows, const int64_t* cols,
+                           int64_t T, int dtype, int path) {
+  if (path == CT_PATH_SIMT || dtype != CT_BF16 || count < 2 || count > kMaxTokenGroup) return false;
+  for (int i = 0; i < count; ++i) {
+    GemmArgs g = blank(rows[i], cols[i], dtype, out[i], cols[i], CT_F32);
+    g.nseg = 1;
+    g.seg[0] = segment(left[i], 1, ld_left[i], right[i], ld_right[i], 1, T);
+    if (!gemm_tcgen05_supported(g)) return false;
+  }
+  return true;
+}
+}  // namespace
+
+extern "C" int64_t ct_token_gradients_group_workspace(int count, const int64_t* rows, const int64_t* cols, int64_t T,
+                                                      int dtype, int path) {
+  if (count < 1 || !rows || !cols || T <= 0 || dtype != CT_BF16 || path == CT_PATH_SIMT) return 0;
+  int64_t bytes = 0, single = 0;
+  const int s = count >= 2 && count <= kMaxTokenGroup ? group_splits(count, rows, cols, T) : 1;
+  for (int i = 0; i < count; ++i) {
+    bytes += static_cast<int64_t>(s) * rows[i] * cols[i] * 4;
+    const int64_t alone = ct_accumulate_workspace(rows[i], cols[i], T, dtype, path);   // the one-by-one route
+    single = alone > single ? alone : single;
+  }
+  if (s <= 1) bytes = 0;
+  return bytes > single ? bytes : single;
+}
+
+extern "C" int ct_token_gradients_group(int count, const void* const* left, const int64_t* ld_left,
+                                        const void* const* right, const int64_t* ld_right, float* const* out,
+                                        const int64_t* rows, const int64_t* cols, int64_t T, const int* add, int dtype,
+                                        void* workspace, int path, void* stream) {
+  if (count < 1) return fail(CT_ERR_ARG, "ct_token_gradients_group: count %d", count);
+  if (!left || !ld_left || !right || !ld_right || !out || !rows || !cols || !add)
+    return fail(CT_ERR_ARG, "ct_token_gradients_group: null pointer");
+  if (T < 0) return fail(CT_ERR_ARG, "ct_token_gradients_group: negative size");
+  if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_token_gradients_group: dtype %d", dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < count; ++i) {
+    if (rows[i] < 0 || cols[i] < 0) return fail(CT_ERR_ARG, "ct_token_gradients_group: negative size");
+    if (rows[i] > 0 && cols[i] > 0 && (!out[i] || (T > 0 && (!left[i] || !right[i]))))
+      return fail(CT_ERR_ARG, "ct_token_gradients_group: null pointer in problem %d", i);
+  }
+  bool grouped = T > 0 && group_on_tensor_cores(count, left, ld_left, right, ld_right, out, rows, cols, T, dtype, path);
+  for (int i = 0; grouped && i < count; ++i) grouped = rows[i] > 0 && cols[i] > 0;
+  if (!grouped) {   // one by one: odd shapes, fp32 operands, the SIMT path, a single product
+    for (int i = 0; i < count; ++i) {
+      if (rows[i] == 0 || cols[i] == 0) continue;
+      const int rc = token_contraction(left[i], ld_left[i], right[i], ld_right[i], out[i], rows[i], cols[i], T, add[i],
+                                       dtype, workspace, path, s);
+      if (rc != CT_OK) return rc;
+    }
+    return CT_OK;
+  }
+  const int splits = group_splits(count, rows, cols, T);
+  if (splits > 1 && !workspace)
+    return fail(CT_ERR_ARG, "ct_token_gradients_group: workspace is null but %d slices are needed", splits);
+  GemmArgs problems[kMaxTokenGroup];
+  float* planes[kMaxTokenGroup];
+  float* cursor = static_cast<float*>(workspace);
+  for (int i = 0; i < count; ++i) {
+    GemmArgs& g = problems[i];
+    g = blank(rows[i], cols[i], dtype, out[i], cols[i], CT_F32);
+    g.nseg = 1;
+    g.seg[0] = segment(left[i], 1, ld_left[i], right[i], ld_right[i], 1, T);
+    g.beta = add[i];
+    planes[i] = nullptr;
+    if (splits > 1) {
+      planes[i] = cursor;
+      cursor += static_cast<int64_t>(splits) * rows[i] * cols[i];
+      g.out = planes[i];
+      g.beta = 0;
+      g.split_k = splits;
+    }
+  }
+  int rc = gemm_tcgen05_group(problems, count, s);
+  if (rc != CT_OK) return rc;
+  for (int i = 0; splits > 1 && i < count; ++i) {
+    rc = reduce_partials(planes[i], splits, rows[i], cols[i], cols[i], out[i], cols[i], add[i], s);
+    if (rc != CT_OK) return rc;
+  }
+  return CT_OK;
+}
+
 // ---- parameter gradients without any allocation ----------------------------------------------
 // Slice-partial scratch that lives in the library image itself. Every GPU on which this entry point
 // has been called holds these bytes until the process exits. In HOST code the array's name is only a stand-in for

@@ -118,6 +118,8 @@ int gemm_simt(const GemmArgs& g, cudaStream_t stream);
 // Returns CT_ERR_UNSUPPORTED (without launching) when a TMA rule is not met.
 int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream);
 bool gemm_tcgen05_supported(const GemmArgs& g);
+// Several independent products (at most 6) in ONE launch of the CTA-pair kernel; each must be supported.
+int gemm_tcgen05_group(const GemmArgs* problems, int count, cudaStream_t stream);
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream);
 // Launches one thread that waits `limit_us` on a barrier nothing completes and reports it (gemm_tc.cu).
 int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream);

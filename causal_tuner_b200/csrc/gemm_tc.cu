@@ -50,20 +50,32 @@ namespace {
 // BM rows of A per CTA; a tile is (BM * CTAS) x BN where CTAS is 1, or 2 for a CTA pair that
 // shares one cta_group::2 MMA (each CTA then stages BM rows of A and BN / 2 columns of B).
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
-constexpr int kThreads = 192;
-constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
+constexpr uint32_t A_HALF_BYTES = BM * BK * 2;  // 16 KB: the 128 rows of A behind one MMA
 constexpr uint32_t MN_BOX_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
-constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulators
+constexpr uint32_t TMEM_COLS = 2 * BN;          // all 512 columns: two accumulators, or the two row halves of one
+constexpr uint32_t STORE_STAGING_BYTES = 32 * 1024;   // epilogue staging tiles for the TMA store (all warps together)
+constexpr uint32_t STORE_TILE_BYTES = 32 * 128;       // one warp's tile: 32 rows x 64 bf16 columns, 128-byte swizzle
 
-template <int CTAS, int STAGES_, int KSUB_ = 1>
+// MH = row halves per CTA. MH = 1: a CTA owns 128 rows of a tile and alternates between two accumulators
+// (the epilogue of one tile runs under the main loop of the next). MH = 2: a CTA owns 256 rows - two MMAs
+// per k step share every B tile, which cuts the bytes staged per FLOP by a quarter and doubles the work
+// buffered per ring stage - and the 128 x 512 TMEM holds that one 256 x 256 accumulator, so the epilogue
+// (two warp sets, one per half) is not overlapped and has to be short.
+template <int CTAS, int STAGES_, int KSUB_ = 1, int MH_ = 1>
 struct Shape {
   static constexpr int kStages = STAGES_;
   static constexpr int kSub = KSUB_;                          // 64-wide k-blocks per ring stage
+  static constexpr int kARows = BM * MH_;                     // A rows staged by one CTA
+  static constexpr uint32_t kATileBytes = kARows * BK * 2;    // 16 KB or 32 KB
   static constexpr int kBRows = BN / CTAS;                    // B columns staged by one CTA
   static constexpr uint32_t kBTileBytes = kBRows * BK * 2;    // 32 KB or 16 KB
-  static constexpr uint32_t kSubBytes = A_TILE_BYTES + kBTileBytes;
+  static constexpr uint32_t kSubBytes = kATileBytes + kBTileBytes;
   static constexpr uint32_t kStageBytes = kSub * kSubBytes;
-  static constexpr size_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kAccumulators = MH_ == 1 ? 2 : 1;
+  static constexpr int kEpilogueWarps = 4 * MH_;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+  static constexpr size_t kSmemBytes =
+      kStages * kStageBytes + STORE_STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 constexpr int GROUP_M = 16;                     // tile rasterisation: 16 row tiles share a sweep over columns
                                                 // (CT_B200_GEMM_GROUP_M overrides it for experiments; 16 is
@@ -91,10 +103,39 @@ struct TcParams {
   int out_f32;
   int beta;
   int vec_store;
+  int tma_store;        // epilogue goes through shared memory and cp.async.bulk.tensor stores of `out_map`
+  CUtensorMap out_map;  // bf16 output, boxes of 32 rows x 64 columns (128-byte swizzle) or x 32 columns (64-byte swizzle, MH == 2)
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   int64_t ld_res;
   int* error_flag;
+
+  // One problem per launch: every tile belongs to it.
+  __device__ __forceinline__ int total_tiles() const { return m_tiles * n_tiles * splits; }
+  __device__ __forceinline__ const TcParams& locate(int tile, int& local) const {
+    local = tile;
+    return *this;
+  }
+  __device__ __forceinline__ int* flag() const { return error_flag; }
+};
+
+// Several independent products in one launch: the persistent CTAs walk the concatenated tile lists, so that
+// products with too few tiles to fill the machine on their own (the token-contracted adapter gradients of one
+// operator) share its waves instead of each ending in a partial one.
+constexpr int kMaxGroup = 6;
+struct TcGroup {
+  int count;
+  int first[kMaxGroup + 1];     // first[i] = tiles of the problems before i; first[count] = all tiles
+  TcParams problem[kMaxGroup];
+
+  __device__ __forceinline__ int total_tiles() const { return first[count]; }
+  __device__ __forceinline__ const TcParams& locate(int tile, int& local) const {
+    int i = 0;
+    while (i + 1 < count && tile >= first[i + 1]) ++i;
+    local = tile - first[i];
+    return problem[i];
+  }
+  __device__ __forceinline__ int* flag() const { return problem[0].error_flag; }
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -227,6 +268,43 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(bar), "h"(both)
                : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void bulk_wait_read() {   // at most PENDING groups still READING their shared-memory source
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_load_32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// Wait for the TMEM loads issued so far. The registers travel through the statement as operands so that the
+// compiler cannot move a use of them above the wait.
+__device__ __forceinline__ void tmem_load_wait(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+        "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+        "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
 }
 
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -362,21 +440,86 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, float (&v)[32], c
   }
 }
 
-// One body for both variants. CTAS == 1: every CTA owns a 128 x 256 tile. CTAS == 2: the two CTAs
-// of a cluster own a 256 x 256 tile; each stages its 128 rows of A and its 128 columns of B, the
-// even ("leader") CTA issues one cta_group::2 MMA per k step for both, and both run their own
-// epilogue on their 128 accumulator rows.
-template <int CTAS, int STAGES_, int KSUB_>
-__device__ __forceinline__ void gemm_body(const TcParams& p) {
-  using S = Shape<CTAS, STAGES_, KSUB_>;
+// Epilogue of one COLS-column chunk (64 or 32) of one accumulator row through shared memory: bias, rounding,
+// residual, then 16-byte pieces into this warp's staging tile of 32 rows x (2 * COLS) bytes, in the swizzle a
+// tensor-map store of that width expects - 128-byte rows: piece j of row r sits at piece j ^ (r & 7); 64-byte
+// rows: at piece j ^ ((r >> 1) & 3) - which also keeps the eight lanes of a store phase on different banks.
+template <int COLS>
+__device__ __forceinline__ void stage_chunk(const TcParams& p, float (&v)[COLS], uint32_t tile, int lane, int64_t row,
+                                            int64_t col0) {
+  const bool full = col0 + COLS <= p.N;
+  if (p.bias) {
+    if (full && p.vec_store) {
+      const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+      for (int q = 0; q < COLS / 8; ++q) {
+        const uint4 o = __ldg(b4 + q);
+        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+          v[8 * q + 2 * j] += f.x;
+          v[8 * q + 2 * j + 1] += f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < COLS; ++j)
+        if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+    }
+  }
+  if (p.residual && row < p.M) {
+    const __nv_bfloat16* res = p.residual + row * p.ld_res + col0;
+    if (full && p.vec_store) {
+      const uint4* r4 = reinterpret_cast<const uint4*>(res);
+#pragma unroll
+      for (int q = 0; q < COLS / 8; ++q) {
+        const uint4 o = __ldg(r4 + q);
+        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+          v[8 * q + 2 * j] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j])), f.x);
+          v[8 * q + 2 * j + 1] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[8 * q + 2 * j + 1])), f.y);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < COLS; ++j)
+        if (col0 + j < p.N)
+          v[j] = __fadd_rn(__bfloat162float(__float2bfloat16_rn(v[j])), __bfloat162float(res[j]));
+    }
+  }
+  const uint32_t row_base = tile + static_cast<uint32_t>(lane) * (2u * COLS);
+  const uint32_t twist = COLS == 64 ? (static_cast<uint32_t>(lane) & 7u) : ((static_cast<uint32_t>(lane) >> 1) & 3u);
+#pragma unroll
+  for (int q = 0; q < COLS / 8; ++q) {
+    const uint32_t dst = row_base + ((static_cast<uint32_t>(q) ^ twist) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(v[8 * q], v[8 * q + 1])),
+                 "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])), "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
+                 "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7]))
+                 : "memory");
+  }
+}
+
+// One body for all variants. CTAS == 1: every CTA owns a 128 x 256 tile. CTAS == 2: the two CTAs of a cluster
+// own a (256 * MH) x 256 tile; each stages its 128 * MH rows of A and its 128 columns of B, the even ("leader")
+// CTA issues the cta_group::2 MMAs (one per row half and k step) for both, and both run their own epilogue on
+// their accumulator rows.
+template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params>
+__device__ __forceinline__ void gemm_body(const Params& params) {
+  using S = Shape<CTAS, STAGES_, KSUB_, MH>;
   constexpr int KSUB = KSUB_;
   constexpr uint32_t SUB_BYTES = S::kSubBytes;
+  constexpr uint32_t A_BYTES = S::kATileBytes;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t STAGE_BYTES = S::kStageBytes;
+  constexpr int ACCS = S::kAccumulators;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;                 // 32 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STORE_STAGING_BYTES);
   // bars: [0, STAGES) full, [STAGES, 2*STAGES) empty, then tmem_full[2], tmem_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -398,7 +541,7 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 4 * CTAS);  // one arrival per epilogue warp of every CTA of the tile
+      mbar_init(tmem_empty_bar(a), S::kEpilogueWarps * CTAS);  // one arrival per epilogue warp of every CTA of the tile
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -426,9 +569,11 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
   // global memory is touched only below.
   grid_dependency_wait();
 
-  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+  const int total_tiles = params.total_tiles();
+  int* const error_flag = params.flag();
   const int first_tile = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
-  constexpr int TILE_M = BM * CTAS;
+  constexpr int CTA_ROWS = BM * MH;             // accumulator rows of one CTA
+  constexpr int TILE_M = CTA_ROWS * CTAS;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -440,10 +585,12 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
       bool alive = true;
       const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
       for (int tile = first_tile; tile < total_tiles && alive; tile += tile_step) {
-        const TileCoord tc = tile_coord(tile, p);
+        int local;
+        const TcParams& p = params.locate(tile, local);
+        const TileCoord tc = tile_coord(local, p);
         int kb_begin, kb_end;
         split_range(p, tc.split, kb_begin, kb_end);
-        const int a_row0 = tc.m * TILE_M + static_cast<int>(rank) * BM;
+        const int a_row0 = tc.m * TILE_M + static_cast<int>(rank) * CTA_ROWS;
         const int b_row0 = tc.n * BN + static_cast<int>(rank) * S::kBRows;
         int seg_first = 0;
         for (int seg = 0; seg < p.nseg && alive; ++seg) {
@@ -456,7 +603,7 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
           const CUtensorMap* map_b = &sg.b;
           const bool a_mn = sg.a_mn != 0, b_mn = sg.b_mn != 0;
           for (int kb = lo; kb < hi; kb += KSUB) {
-            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.error_flag, 1))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, error_flag, 1))) {
               alive = false;
               break;
             }
@@ -473,12 +620,12 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
               for (int sub = 0; sub < KSUB; ++sub) {
                 if (sub >= subs) break;
                 const int k0 = (kb + sub) * BK;
-                const uint32_t a_dst = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES, b_dst = a_dst + A_TILE_BYTES;
+                const uint32_t a_dst = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES, b_dst = a_dst + A_BYTES;
                 if (!a_mn) {
-                  load(a_dst, map_a, k0, a_row0);
+                  load(a_dst, map_a, k0, a_row0);      // one box of CTA_ROWS rows
                 } else {
 #pragma unroll
-                  for (int j = 0; j < BM / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
+                  for (int j = 0; j < CTA_ROWS / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
                 }
                 if (!b_mn) {
                   load(b_dst, map_b, k0, b_row0);
@@ -502,7 +649,7 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
     // ------------------------------ MMA issuer (leader CTA only) ---------------
     // One thread feeds the tensor core, so the loop is kept to a handful of instructions per MMA:
     // everything that depends only on the segment (instruction descriptor, descriptor high words,
-    // per-k-step increments) is hoisted, and a k-block costs one barrier test, four MMAs, one commit.
+    // per-k-step increments) is hoisted, and a k-block costs one barrier test, 4 * MH MMAs, one commit.
     // The whole warp walks the loop so that control flow stays uniform; lane 0 issues.
     if (leader) {
       int stage = 0;
@@ -511,15 +658,17 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
       bool alive = true;
       const uint32_t desc_hi = desc_high(1024);
       for (int tile = first_tile; tile < total_tiles && alive; tile += tile_step, ++local_tile) {
-        const TileCoord tc = tile_coord(tile, p);
+        int local;
+        const TcParams& p = params.locate(tile, local);
+        const TileCoord tc = tile_coord(local, p);
         int kb_begin, kb_end;
         split_range(p, tc.split, kb_begin, kb_end);
-        const int acc = local_tile & 1;
-        const uint32_t acc_phase = (local_tile >> 1) & 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.error_flag, 2)))
+        const int acc = ACCS == 2 ? (local_tile & 1) : 0;
+        const uint32_t acc_phase = (local_tile / ACCS) & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, error_flag, 2)))
           break;
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + acc * BN;      // MH == 2: row half h accumulates at column h * BN
         uint32_t accumulate = 0;
         int seg_first = 0;
         for (int seg = 0; seg < p.nseg && alive; ++seg) {
@@ -528,16 +677,16 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
           const int hi = min(kb_end, seg_first + sg.k_blocks) - seg_first;
           seg_first += sg.k_blocks;
           if (lo >= hi) continue;
-          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn, TILE_M);
+          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn, BM * CTAS);
           // K-major: 8-row groups 1024 B apart, 32 B per 16-element k step inside the swizzle atom.
           // MN-major: 64-wide column groups one box (8 KB) apart, 8-k groups 1024 B apart,
           //           16 k rows (2 KB) per k step.
           const uint32_t a_lo0 = desc_low(smem_base, sg.a_mn ? MN_BOX_BYTES : 16u);
-          const uint32_t b_lo0 = desc_low(smem_base + A_TILE_BYTES, sg.b_mn ? MN_BOX_BYTES : 16u);
+          const uint32_t b_lo0 = desc_low(smem_base + A_BYTES, sg.b_mn ? MN_BOX_BYTES : 16u);
           const uint32_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
           const uint32_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
           for (int kb = lo; kb < hi; kb += KSUB) {
-            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.error_flag, 3))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, error_flag, 3))) {
               alive = false;
               break;
             }
@@ -551,12 +700,17 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
                 const uint32_t b_lo = b_lo0 + stage * (STAGE_BYTES >> 4) + sub * (SUB_BYTES >> 4);
 #pragma unroll
                 for (int j = 0; j < BK / UMMA_K; ++j) {
-                  if constexpr (CTAS == 1)
-                    umma_bf16(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
-                              (accumulate | sub | j) ? 1u : 0u);
-                  else
-                    umma_bf16_pair(tmem_d, a_lo + a_step * j, desc_hi, b_lo + b_step * j, desc_hi, idesc,
-                                   (accumulate | sub | j) ? 1u : 0u);
+#pragma unroll
+                  for (int h = 0; h < MH; ++h) {
+                    // the 128 rows of half h are 16 KB further into the A tile in either orientation
+                    const uint32_t a_h = a_lo + h * (A_HALF_BYTES >> 4) + a_step * j;
+                    if constexpr (CTAS == 1)
+                      umma_bf16(tmem_d + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                                (accumulate | sub | j) ? 1u : 0u);
+                    else
+                      umma_bf16_pair(tmem_d + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                                     (accumulate | sub | j) ? 1u : 0u);
+                  }
                 }
               }
               if constexpr (CTAS == 1) umma_commit(empty_bar(stage));
@@ -580,34 +734,105 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
     __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int half = (warp - 2) >> 2;        // MH == 2: warps 2-5 drain row half 0, warps 6-9 row half 1
+    // This warp's two staging tiles for the tensor-map store: 4 KB each (64 columns, MH == 1) or 2 KB each
+    // (32 columns, MH == 2); 32 KB for all warps in both cases.
+    const uint32_t stage_tile0 =
+        smem_u32(staging) + static_cast<uint32_t>(warp - 2) * (STORE_STAGING_BYTES / S::kEpilogueWarps);
+    int stored = 0;                           // chunks this warp has handed to the store engine
     int local_tile = 0;
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++local_tile) {
-      const TileCoord tc = tile_coord(tile, p);
-      const int acc = local_tile & 1;
-      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      int local;
+      const TcParams& p = params.locate(tile, local);
+      const TileCoord tc = tile_coord(local, p);
+      const int acc = ACCS == 2 ? (local_tile & 1) : 0;
+      const uint32_t acc_phase = (local_tile / ACCS) & 1;
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.error_flag, 4) ? 1 : 0;
+      if (lane == 0) ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, error_flag, 4) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tcgen05_fence_after();
-      const int64_t row = static_cast<int64_t>(tc.m) * TILE_M + rank * BM + quarter * 32 + lane;
+      const int row0 = tc.m * TILE_M + static_cast<int>(rank) * CTA_ROWS + half * BM + quarter * 32;
+      const int64_t row = row0 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      char* out_plane = static_cast<char*>(p.out) +
-                        static_cast<int64_t>(tc.split) * p.split_stride * (p.out_f32 ? 4 : 2);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MH == 2 ? half : acc) * BN;
+      if (p.tma_store) {
+        if constexpr (MH == 1) {
+          // 64-column chunks, two 4 KB staging tiles per warp (this epilogue runs under the next tile's main loop)
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t raw[32];
-        __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped the previous stores
-        tmem_load_32(taddr + c * 32, raw);
-        if (!row_ok) continue;
-        float v[32];
+          for (int c = 0; c < BN / 64; ++c) {
+            const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 64;
+            if (col0 >= p.N) break;  // uniform across the warp
+            uint32_t lo[32], hi[32];
+            tmem_load_32_issue(taddr + c * 64, lo);
+            tmem_load_32_issue(taddr + c * 64 + 32, hi);
+            // the staging tile about to be overwritten must have been read by its previous store
+            if (lane == 0) bulk_wait_read<1>();
+            tmem_load_wait(lo);
+            tmem_load_wait(hi);
+            __syncwarp();
+            float v[64];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-        store_chunk(p, v, out_plane, row, col0);
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(lo[j]);
+              v[32 + j] = __uint_as_float(hi[j]);
+            }
+            const uint32_t tile_smem = stage_tile0 + static_cast<uint32_t>(stored & 1) * STORE_TILE_BYTES;
+            stage_chunk<64>(p, v, tile_smem, lane, row, col0);
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {      // rows and columns past the matrix are clipped by the store
+              tma_store_2d(&p.out_map, tile_smem, static_cast<int>(col0), row0);
+              bulk_commit();
+            }
+            ++stored;
+          }
+        } else {
+          // Not overlapped with a main loop, so kept short: 32-column chunks, two 2 KB staging tiles per warp, and
+          // the TMEM load of the next chunk in flight while this one is converted, staged and handed to the store.
+          constexpr int CHUNKS = BN / 32;
+          uint32_t raw[2][32];
+          tmem_load_32_issue(taddr, raw[0]);
+#pragma unroll
+          for (int c = 0; c < CHUNKS; ++c) {
+            const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
+            tmem_load_wait(raw[c & 1]);
+            if (c + 1 < CHUNKS) tmem_load_32_issue(taddr + (c + 1) * 32, raw[(c + 1) & 1]);
+            if (col0 < p.N) {  // uniform across the warp
+              if (lane == 0) bulk_wait_read<1>();
+              __syncwarp();
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
+              const uint32_t tile_smem = stage_tile0 + static_cast<uint32_t>(stored & 1) * (STORE_TILE_BYTES / 2);
+              stage_chunk<32>(p, v, tile_smem, lane, row, col0);
+              fence_async_shared();
+              __syncwarp();
+              if (lane == 0 && row0 < p.M) {
+                tma_store_2d(&p.out_map, tile_smem, static_cast<int>(col0), row0);
+                bulk_commit();
+              }
+              ++stored;
+            }
+          }
+        }
+      } else {
+        char* out_plane = static_cast<char*>(p.out) +
+                          static_cast<int64_t>(tc.split) * p.split_stride * (p.out_f32 ? 4 : 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
+          if (col0 >= p.N) break;  // uniform across the warp
+          uint32_t raw[32];
+          __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped the previous stores
+          tmem_load_32(taddr + c * 32, raw);
+          if (!row_ok) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          store_chunk(p, v, out_plane, row, col0);
+        }
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -616,6 +841,10 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
         else mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
       }
     }
+    // Shared memory must stay valid until the stores have read it, and the stores must be complete before the
+    // kernel's writes count as done.
+    if (lane == 0) bulk_wait_all();
+    __syncwarp();
   }
 
   tcgen05_fence_before();
@@ -631,14 +860,26 @@ __device__ __forceinline__ void gemm_body(const TcParams& p) {
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
-  gemm_body<1, 4, 1>(p);
+__global__ void __launch_bounds__(Shape<1, 4, 1, 1>::kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<1, 4, 1, 1>(p);
 }
 
 template <int STAGES_, int KSUB_>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, STAGES_, KSUB_, 1>::kThreads, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ TcParams p) {
-  gemm_body<2, STAGES_, KSUB_>(p);
+  gemm_body<2, STAGES_, KSUB_, 1>(p);
+}
+
+// Several products per launch (256 x 256 pair tiles, register-store epilogue: fp32 slice planes).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads, 1)
+    gemm_tcgen05_group_kernel(const __grid_constant__ TcGroup group) {
+  gemm_body<2, 3, 2, 1>(group);
+}
+
+// The 512 x 256 tile: two row halves per CTA, four ring stages of one 48 KB k-block, two epilogue warp sets.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 4, 1, 2>::kThreads, 1)
+    gemm_tcgen05_wide_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<2, 4, 1, 2>(p);
 }
 
 // ---- host side ------------------------------------------------------------------
@@ -662,9 +903,10 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 struct MapKey {
   const void* base;
   int64_t inner, outer, ld;
-  int box_rows;
+  int box_rows, box_inner;
   bool operator==(const MapKey& o) const {
-    return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_rows == o.box_rows;
+    return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_rows == o.box_rows &&
+           box_inner == o.box_inner;
   }
 };
 struct MapSlot {
@@ -676,11 +918,14 @@ constexpr int kMapSlots = 4096;
 MapSlot g_map_table[kMapSlots];
 std::mutex g_map_mutex;
 
-int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_rows) {
-  const MapKey key{base, inner, outer, ld, box_rows};
+// `box_inner` = 64 elements (128-byte rows, 128-byte swizzle: every operand tile and the 64-column store tile) or
+// 32 elements (64-byte rows, 64-byte swizzle: the 32-column store tile).
+int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_rows,
+             int box_inner = 64) {
+  const MapKey key{base, inner, outer, ld, box_rows, box_inner};
   uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
   h = (h ^ static_cast<uint64_t>(inner) * 0x9E3779B97F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
-  h = (h ^ static_cast<uint64_t>(outer) * 0x94D049BB133111EBull ^ static_cast<uint64_t>(ld) << 7 ^ static_cast<uint64_t>(box_rows)) * 0x9E3779B97F4A7C15ull;
+  h = (h ^ static_cast<uint64_t>(outer) * 0x94D049BB133111EBull ^ static_cast<uint64_t>(ld) << 7 ^ static_cast<uint64_t>(box_rows) ^ static_cast<uint64_t>(box_inner) << 20) * 0x9E3779B97F4A7C15ull;
   MapSlot& slot = g_map_table[(h >> 32) % kMapSlots];
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -693,11 +938,12 @@ int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, i
   if (!fn) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t elem[2] = {1, 1};
   const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -809,7 +1055,17 @@ int launch_pair(const TcParams& p, unsigned grid, int device, cudaStream_t strea
   const size_t smem = Shape<2, STAGES_, KSUB_>::kSmemBytes;
   const int rc = configure(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, smem, &configured[device]);
   if (rc != CT_OK) return rc;
-  launch_dependent(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, dim3(grid), dim3(kThreads), smem, stream, p);
+  launch_dependent(gemm_tcgen05_pair_kernel<STAGES_, KSUB_>, dim3(grid), dim3(Shape<2, STAGES_, KSUB_>::kThreads), smem,
+                   stream, p);
+  return CT_OK;
+}
+
+int launch_wide(const TcParams& p, unsigned grid, int device, cudaStream_t stream) {
+  static bool configured[64] = {};
+  using S = Shape<2, 4, 1, 2>;
+  const int rc = configure(gemm_tcgen05_wide_kernel, S::kSmemBytes, &configured[device]);
+  if (rc != CT_OK) return rc;
+  launch_dependent(gemm_tcgen05_wide_kernel, dim3(grid), dim3(S::kThreads), S::kSmemBytes, stream, p);
   return CT_OK;
 }
 
@@ -818,19 +1074,62 @@ int launch_single(const TcParams& p, unsigned grid, int device, cudaStream_t str
   const size_t smem = Shape<1, 4, 1>::kSmemBytes;
   const int rc = configure(gemm_tcgen05_kernel, smem, &configured[device]);
   if (rc != CT_OK) return rc;
-  launch_dependent(gemm_tcgen05_kernel, dim3(grid), dim3(kThreads), smem, stream, p);
+  launch_dependent(gemm_tcgen05_kernel, dim3(grid), dim3(Shape<1, 4, 1>::kThreads), smem, stream, p);
   return CT_OK;
 }
 
-int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
-  if (!gemm_tcgen05_supported(g)) return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05: operands break a TMA rule");
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
-    return fail(CT_ERR_CUDA, "gemm_tcgen05: no current device");
-  const int ctas = ctas_for(g);
+// Row halves per CTA and the kind of epilogue, chosen from same-device comparisons of the four combinations on
+// the shapes of a training step (CT_B200_GEMM_MH = 1 / 2 and CT_B200_GEMM_TMA_STORE = 0 / 1 pin them):
+//  * the 512 x 256 tile halves the B tiles staged per FLOP and doubles the work buffered per ring stage. It pays
+//    where B arrives as MN-major 64 x 64 boxes and the contraction is short (the input-gradient products
+//    dy . W with K of a few thousand: 6 to 9 % faster); with K-major B or a long contraction the two tiles are
+//    within run-to-run noise of each other and the 256 x 256 tile with its overlapped epilogue is kept. The
+//    wide tile's epilogue is not overlapped, so it is only used with the tensor-map store, for outputs of at
+//    least 1024 columns (enough tiles to fill the machine) and 512 rows;
+//  * a product whose tiles fit in one wave (the skinny low-rank products) has no next tile to hide its
+//    epilogue behind either: the tensor-map store is 4 to 9 % ahead there;
+//  * where the epilogue runs under the next tile's main loop the register store is kept (the staged store
+//    costs a few per cent there).
+struct Variant {
+  int halves;
+  bool tma_store;
+};
+
+Variant variant_for(const GemmArgs& g, int ctas, bool store_ok) {
+  const int pinned_halves = env_int("CT_B200_GEMM_MH", 0);
+  const int pinned_store = env_int("CT_B200_GEMM_TMA_STORE", -1);
+  bool b_mn = false;
+  int64_t k_total = 0, k_mn = 0;
+  for (int s = 0; s < g.nseg; ++s) {
+    k_total += g.seg[s].k;
+    if (g.seg[s].b_rs != 1) k_mn += g.seg[s].k;
+  }
+  b_mn = 2 * k_mn > k_total;
+  const int64_t pair_tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
+  Variant v;
+  v.halves = 1;
+  if (ctas == 2 && store_ok && g.M >= 4 * BM && g.N >= 4 * BN && b_mn && k_total < 8192) v.halves = 2;
+  if (ctas == 2 && (pinned_halves == 1 || pinned_halves == 2)) v.halves = pinned_halves;
+  v.tma_store = store_ok && (v.halves == 2 || pair_tiles <= 74);
+  if (pinned_store == 0) v.tma_store = false;
+  if (pinned_store == 1) v.tma_store = store_ok;
+  return v;
+}
+
+// Everything of a launch's TcParams that depends on the problem alone.
+int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* out) {
+  TcParams& p = *out;
   int rc = CT_OK;
-  const int tile_m = BM * ctas, b_rows = BN / ctas;
-  TcParams p;
+  p.splits = g.split_k > 1 ? g.split_k : 1;
+  p.out_f32 = g.out_dtype == CT_F32;
+  p.beta = g.beta;
+  const int vec = p.out_f32 ? 4 : 8;
+  p.vec_store = (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && g.ldo % vec == 0 &&
+                (!g.residual || ((reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 && g.ld_res % 8 == 0)) &&
+                (!g.bias || (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
+  p.tma_store = variant.tma_store ? 1 : 0;
+  const int halves = variant.halves;
+  const int tile_m = BM * ctas * halves, b_rows = BN / ctas;
   p.nseg = g.nseg;
   p.k_blocks_total = 0;
   for (int s = 0; s < g.nseg; ++s) {
@@ -841,33 +1140,47 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
     t.a_mn = sg.a_cs == 1 ? 0 : 1;
     t.b_mn = sg.b_rs == 1 ? 0 : 1;
     // K-major: contiguous index is k, rows are m (or n). MN-major: contiguous index is m (or n), rows are k.
-    rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM);
+    rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM * halves);
     if (rc != CT_OK) return rc;
     rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK) : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, b_rows);
     if (rc != CT_OK) return rc;
   }
-  p.splits = g.split_k > 1 ? g.split_k : 1;
+  if (p.tma_store) {
+    rc = make_map(&p.out_map, g.out, g.N, g.M, g.ldo, 32, halves == 2 ? 32 : 64);
+    if (rc != CT_OK) return rc;
+  }
   p.m_tiles = static_cast<int>((g.M + tile_m - 1) / tile_m);
   p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
   {
     const int value = env_int("CT_B200_GEMM_GROUP_M", 0);
-    p.group_m = value > 0 ? value : GROUP_M;
+    p.group_m = value > 0 ? value : (halves == 2 ? GROUP_M / 2 : GROUP_M);   // the same 4096 rows per sweep
   }
   p.M = g.M;
   p.N = g.N;
   p.out = g.out;
   p.ldo = g.ldo;
   p.split_stride = g.M * g.ldo;
-  p.out_f32 = g.out_dtype == CT_F32;
-  p.beta = g.beta;
-  const int vec = p.out_f32 ? 4 : 8;
-  p.vec_store = (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && g.ldo % vec == 0 &&
-                (!g.residual || ((reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 && g.ld_res % 8 == 0));
   p.bias = static_cast<const __nv_bfloat16*>(g.bias);
   p.residual = static_cast<const __nv_bfloat16*>(g.residual);
   p.ld_res = g.ld_res;
   p.error_flag = device_error_flag();
   if (!p.error_flag) return fail(CT_ERR_CUDA, "gemm_tcgen05: no device error flag");
+  return CT_OK;
+}
+
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
+  if (!gemm_tcgen05_supported(g)) return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05: operands break a TMA rule");
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(CT_ERR_CUDA, "gemm_tcgen05: no current device");
+  const int ctas = ctas_for(g);
+  // Tensor-map store: possible for a bf16 result that is written exactly once, rows 16-byte aligned.
+  const bool store_ok = g.out_dtype != CT_F32 && !g.beta && g.split_k <= 1 &&
+                        (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && g.ldo % 8 == 0;
+  const Variant variant = variant_for(g, ctas, store_ok);
+  TcParams p;
+  int rc = fill_params(g, ctas, variant, &p);
+  if (rc != CT_OK) return rc;
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.splits;
   int sms = sm_count();
   if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05: cannot read the SM count");
@@ -875,7 +1188,9 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * ctas);
   const bool timed = timing_enabled();
   if (timed) timing_begin(stream);
-  if (ctas == 2) {
+  if (ctas == 2 && variant.halves == 2) {
+    rc = launch_wide(p, grid, device, stream);
+  } else if (ctas == 2) {
     // Default: 3 stages of two 64-wide k-blocks (one barrier round per 8 MMAs). CT_B200_GEMM_KSUB=1
     // selects 6 stages of one k-block (one round per 4 MMAs) for comparison runs.
     const int ksub = env_int("CT_B200_GEMM_KSUB", 2);
@@ -892,6 +1207,48 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   }
   count_launch(true);
   return check_launch("gemm_tcgen05");
+}
+
+// `count` independent products (2 .. kMaxGroup) in one launch of the CTA-pair kernel. Every problem must pass
+// gemm_tcgen05_supported; outputs go through the register-store epilogue (fp32 slice planes, beta).
+int gemm_tcgen05_group(const GemmArgs* problems, int count, cudaStream_t stream) {
+  if (count < 1 || count > kMaxGroup) return fail(CT_ERR_ARG, "gemm_tcgen05_group: %d problems (1 .. %d)", count, kMaxGroup);
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(CT_ERR_CUDA, "gemm_tcgen05_group: no current device");
+  static TcGroup staging_area[64];          // 13 KB each: too large for the stack of a host thread to take lightly
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  TcGroup& group = staging_area[device];
+  group.count = count;
+  group.first[0] = 0;
+  double flops = 0;
+  const Variant plain{1, false};
+  for (int i = 0; i < count; ++i) {
+    if (!gemm_tcgen05_supported(problems[i]))
+      return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_group: problem %d breaks a TMA rule", i);
+    const int rc = fill_params(problems[i], 2, plain, &group.problem[i]);
+    if (rc != CT_OK) return rc;
+    const TcParams& p = group.problem[i];
+    group.first[i + 1] = group.first[i] + p.m_tiles * p.n_tiles * p.splits;
+    double k_total = 0;
+    for (int s = 0; s < problems[i].nseg; ++s) k_total += static_cast<double>(problems[i].seg[s].k);
+    flops += 2.0 * static_cast<double>(problems[i].M) * static_cast<double>(problems[i].N) * k_total;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05_group: cannot read the SM count");
+  const int64_t tiles = group.first[count], slots = sms / 2;
+  const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * 2);
+  static bool configured[64] = {};
+  using S = Shape<2, 3, 2, 1>;
+  const int rc = configure(gemm_tcgen05_group_kernel, S::kSmemBytes, &configured[device]);
+  if (rc != CT_OK) return rc;
+  const bool timed = timing_enabled();
+  if (timed) timing_begin(stream);
+  launch_dependent(gemm_tcgen05_group_kernel, dim3(grid), dim3(S::kThreads), S::kSmemBytes, stream, group);
+  if (timed) timing_end(stream, flops, problems[0].M, problems[0].N, -count);   // k = -count marks a grouped launch
+  count_launch(true);
+  return check_launch("gemm_tcgen05_group");
 }
 
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {

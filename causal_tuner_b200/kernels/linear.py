@@ -351,6 +351,45 @@ def token_gradient(left, right, out, *, add=False):
                                          _lib.pointer(workspace), _lib.gemm_path, _lib.stream_of(left)))
 
 
+def token_gradients(problems, *, add=False):
+    """Several `token_gradient` products over the same tokens in one launch: `problems` is a list of
+    (left, right, out); every out_i (+)= left_i.T @ right_i in fp32 with the fixed slice order of the group
+    (ct_token_gradients_group). The adapter gradients of one operator - its stacked dA and each projection's
+    dB - have too few output tiles to fill the machine one by one; together they share its waves."""
+    import ctypes
+    problems = [(l, r, o) for l, r, o in problems if o.numel()]
+    if not problems:
+        return
+    if len(problems) == 1 or len(problems) > 6:
+        for left, right, out in problems:
+            token_gradient(left, right, out, add=add)
+        return
+    prepared = []
+    for left, right, out in problems:
+        _lib.require_cuda(left, right, out)
+        if out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError("token_gradients writes contiguous fp32 matrices")
+        left, right = _readable(left), _readable(right)
+        if right.shape[0] != left.shape[0] or out.shape != (left.shape[1], right.shape[1]):
+            raise ValueError("token_gradients shape mismatch")
+        if left.dtype != right.dtype or left.shape[0] != problems[0][0].shape[0] or left.dtype != problems[0][0].dtype:
+            raise ValueError("token_gradients contracts operands of one dtype over one token count")
+        prepared.append((left, right, out))
+    count, tokens = len(prepared), prepared[0][0].shape[0]
+    library, code = _lib.load(), _lib.code_of(prepared[0][0].dtype)
+    longs = lambda values: (ctypes.c_int64 * count)(*values)
+    pointers = lambda tensors: (ctypes.c_void_p * count)(*[t.data_ptr() for t in tensors])
+    rows, cols = longs([o.shape[0] for _, _, o in prepared]), longs([o.shape[1] for _, _, o in prepared])
+    need = library.ct_token_gradients_group_workspace(count, rows, cols, tokens, code, _lib.gemm_path)
+    workspace = torch.empty(need, device=prepared[0][2].device, dtype=torch.uint8) if need else None
+    with _lib.on_device(prepared[0][2]):
+        _lib.check(library.ct_token_gradients_group(
+            count, pointers([l for l, _, _ in prepared]), longs([_leading(l) for l, _, _ in prepared]),
+            pointers([r for _, r, _ in prepared]), longs([_leading(r) for _, r, _ in prepared]),
+            pointers([o for _, _, o in prepared]), rows, cols, tokens, (ctypes.c_int * count)(*([int(bool(add))] * count)),
+            code, _lib.pointer(workspace), _lib.gemm_path, _lib.stream_of(prepared[0][2])))
+
+
 def parameter_gradients(x, dy, da, db, low, xa, *, add):
     """da (+)= low.T @ x and db (+)= dy.T @ xa in fp32 (kernels/linear.py:42-44), summed in a fixed order."""
     _lib.require_cuda(x, dy, da, db, low, xa)
@@ -361,6 +400,9 @@ def parameter_gradients(x, dy, da, db, low, xa, *, add):
         parameter_gradients(x, dy, da32, db32, low, xa, add=add)
         da.copy_(da32)
         db.copy_(db32)
+        return
+    if x.dtype == torch.bfloat16 and _lib.gemm_path != _lib.PATH_SIMT and x.shape[0]:
+        token_gradients([(low, x, da), (dy, xa, db)], add=add)      # both products in one launch
         return
     x, dy, low, xa = _readable(x), _readable(dy), _readable(low), _readable(xa)
     rows, inner = x.shape
@@ -525,12 +567,17 @@ class _LoRAGroup(torch.autograd.Function):
                 xa_all = torch.empty((rows, total), device=x.device, dtype=dtype)
                 matmul(flat, a_all.T, out=xa_all)
             da_all = torch.empty((total, flat.shape[1]), device=x.device, dtype=torch.float32)
-            token_gradient(low_all, flat, da_all)
+            contractions, db_all = [(low_all, flat, da_all)], []
             for index, (matrix, a16, b16, signal, low) in enumerate(prepared):
+                b = parameters[4 * index + 2]
+                span = slice(offsets[index], offsets[index] + parameters[4 * index + 1].shape[0])
+                db_all.append(torch.empty(b.shape, device=x.device, dtype=torch.float32))
+                contractions.append((signal, xa_all[:, span], db_all[-1]))
+            token_gradients(contractions)        # the stacked dA and every dB in one launch
+            for index in range(len(prepared)):
                 a, b = parameters[4 * index + 1], parameters[4 * index + 2]
                 span = slice(offsets[index], offsets[index] + a.shape[0])
-                da, db = da_all[span], torch.empty(b.shape, device=x.device, dtype=torch.float32)
-                token_gradient(signal, xa_all[:, span], db)
+                da, db = da_all[span], db_all[index]
                 results.extend((None, da if a.dtype == torch.float32 else da.to(a.dtype),
                                 db if b.dtype == torch.float32 else db.to(b.dtype), None))
             del prepared

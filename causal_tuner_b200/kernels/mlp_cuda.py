@@ -12,7 +12,7 @@ import torch
 from .. import _lib
 from .linear import (_policy, apply_projection, cast, materialize, materialize_ahead, forward_linear, input_gradient,
                      input_gradient_with, input_gradient_group, parameter_gradients, projection_parameters, matmul,
-                     stack_adapters, token_gradient)
+                     stack_adapters, token_gradient, token_gradients)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -212,7 +212,6 @@ class _TiledLoRAMLP(torch.autograd.Function):
                 xa_low = saved[4][start:stop]
             else:
                 xa_low = matmul(hidden, adapters[2][0].T, out=xa_down[:count])
-            parameter_gradients(hidden, dy, da_down, db[2], low[2], xa_low, add=start > 0)
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
                 pending.wait()
@@ -221,9 +220,10 @@ class _TiledLoRAMLP(torch.autograd.Function):
             else:
                 for index, signal in enumerate((gate, up)):
                     matmul(signal, adapters[index][1], out=low[index])
-            token_gradient(low_both[:count], part, da_both, add=start > 0)
-            for index, signal in enumerate((gate, up)):
-                token_gradient(signal, xa[index], db[index], add=start > 0)
+            # All five adapter-gradient products of the tile in one launch: d(a_down), d(b_down), the stacked
+            # d(a_gate; a_up), d(b_gate), d(b_up). Apart they leave the machine between 22 % and 76 % occupied.
+            token_gradients([(low[2], hidden, da_down), (dy, xa_low, db[2]), (low_both[:count], part, da_both),
+                             (gate, xa[0], db[0]), (up, xa[1], db[1])], add=start > 0)
         da = [da_both[:ranks[0]], da_both[ranks[0]:], da_down]
         like = lambda value, parameter: value if parameter.dtype == torch.float32 else value.to(parameter.dtype)
         result = [value for i in range(3)

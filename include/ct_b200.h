@@ -213,6 +213,23 @@ CT_API int ct_accumulate(const void* left, int64_t ld_left, const void* right, i
                          float* out, int64_t rows, int64_t cols, int64_t T, int add, int dtype,
                          void* workspace, int path, void* stream);
 
+/* ---- several token-contracted accumulations in one launch -------------------------
+ * `count` independent products out_i[rows_i, cols_i] = (add_i ? out_i : 0) + left_i^T @ right_i over the same T
+ * tokens - the dA and dB of the projections of one operator (kernels/linear.py:42-44 called once per
+ * projection at kernels/linear.py:126 and kernels/mlp_cuda.py:135-141). Same arithmetic as `count` calls of
+ * ct_accumulate; with 2 to 6 products whose operands meet the tensor-core rules they run as ONE persistent
+ * launch that walks the concatenated tile lists, so that products with fewer tiles than the machine has
+ * CTA pairs share its waves instead of each ending in a partial one. One slice count for the whole group
+ * (a function of the shapes alone; fp32 partial planes summed in slice order), so results are reproducible.
+ * The pointer tables, `ld_*`, `rows`, `cols` and `add` are HOST arrays of length `count`; `workspace` holds
+ * ct_token_gradients_group_workspace(...) bytes (NULL when that is 0). */
+CT_API int64_t ct_token_gradients_group_workspace(int count, const int64_t* rows, const int64_t* cols,
+                                                  int64_t T, int dtype, int path);
+CT_API int ct_token_gradients_group(int count, const void* const* left, const int64_t* ld_left,
+                                    const void* const* right, const int64_t* ld_right, float* const* out,
+                                    const int64_t* rows, const int64_t* cols, int64_t T, const int* add,
+                                    int dtype, void* workspace, int path, void* stream);
+
 /* ---- LoRA parameter gradients for callers that must not allocate ---------------
  * No counterpart in the reference (its gradients go through torch's caching
  * allocator, kernels/linear.py:102). Same arithmetic, same fixed summation order

@@ -37,5 +37,6 @@ def pytest_configure(config):
     config._ct_aliased = install()
 
 
-def pytest_report_header(config):
-    return f"causal_tuner.kernels modules served by causal_tuner_b200: {', '.join(config._ct_aliased)}"
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    terminalreporter.write_line(
+        f"causal_tuner.kernels modules served by causal_tuner_b200: {', '.join(config._ct_aliased)}")

@@ -9,16 +9,25 @@ from causal_tuner_b200.kernels import linear
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gpu_guard")]
 
-# name -> (GEMM path, CTAs per tile pinned through CT_B200_GEMM_CTAS)
-PATHS = {"simt": (_lib.PATH_SIMT, None), "tcgen05": (_lib.PATH_TCGEN05, "1"), "tcgen05_pair": (_lib.PATH_TCGEN05, "2")}
+# name -> (GEMM path, CTAs per tile (CT_B200_GEMM_CTAS), row halves per CTA (CT_B200_GEMM_MH), tensor-map store
+# epilogue (CT_B200_GEMM_TMA_STORE)); None leaves the library's own choice
+PATHS = {"simt": (_lib.PATH_SIMT, None, None, None),
+         "tcgen05": (_lib.PATH_TCGEN05, "1", None, None),
+         "tcgen05_pair": (_lib.PATH_TCGEN05, "2", "1", None),
+         "tcgen05_pair_register_store": (_lib.PATH_TCGEN05, "2", "1", "0"),
+         "tcgen05_wide": (_lib.PATH_TCGEN05, "2", "2", None),
+         "tcgen05_wide_register_store": (_lib.PATH_TCGEN05, "2", "2", "0")}
 
 
 @pytest.fixture(params=list(PATHS))
 def path(request, monkeypatch):
-    choice, ctas = PATHS[request.param]
+    choice, ctas, halves, tma_store = PATHS[request.param]
     monkeypatch.setattr(_lib, "gemm_path", choice)
-    if ctas is not None:
-        monkeypatch.setenv("CT_B200_GEMM_CTAS", ctas)
+    for name, value in (("CT_B200_GEMM_CTAS", ctas), ("CT_B200_GEMM_MH", halves), ("CT_B200_GEMM_TMA_STORE", tma_store)):
+        if value is not None:
+            monkeypatch.setenv(name, value)
+        else:
+            monkeypatch.delenv(name, raising=False)
     return request.param
 
 
@@ -35,7 +44,7 @@ def operand(rows, cols, major, dtype=torch.bfloat16):
 
 
 # (M, N, K): one exact tile; ragged in every dimension; more tiles than SMs; a long contraction
-SHAPES = [(128, 256, 64), (304, 520, 200), (2048, 4096, 128), (96, 72, 2048), (1, 8, 8)]
+SHAPES = [(128, 256, 64), (304, 520, 200), (2048, 4096, 128), (96, 72, 2048), (1, 8, 8), (1096, 328, 520)]
 
 
 @pytest.mark.parametrize("a_major,b_major", [("K", "K"), ("K", "MN"), ("MN", "K"), ("MN", "MN")])
@@ -225,6 +234,38 @@ def test_token_gradient_of_stacked_low_matrices(path, tokens, rows, cols):
     assert relative(part, expected[:third]) < 1e-5
     with pytest.raises(ValueError):
         linear.token_gradient(left, right, torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("tokens,shapes", [(4096, [(768, 512), (512, 256), (128, 256), (128, 256)]),      # one slice each
+                                           (2048, [(256, 512), (512, 256)]),                              # sliced
+                                           (304, [(24, 520), (520, 24), (16, 8)]),                        # ragged
+                                           (8192, [(512, 1024), (1024, 256), (1024, 256), (256, 1024), (1024, 256)])])
+def test_grouped_token_gradients_equal_the_separate_products(path, tokens, shapes):
+    """ct_token_gradients_group: several left^T @ right products over the same tokens in one launch (the stacked
+    dA and every dB of an operator). Each result within 1e-5 of an fp32 product and of the one-by-one route,
+    bit-identical when repeated (one slice count per group, planes summed in slice order), beta honoured."""
+    problems = []
+    for rows, cols in shapes:
+        left = torch.randn(tokens, rows, device="cuda").bfloat16()
+        right = torch.randn(tokens, cols, device="cuda").bfloat16()
+        problems.append((left, right, torch.full((rows, cols), float("nan"), device="cuda")))
+    launches = _lib.tcgen05_launch_count()
+    linear.token_gradients(problems)
+    used = _lib.tcgen05_launch_count() - launches
+    if path.startswith("tcgen05") and tokens != 304:
+        assert used == 1                       # one persistent launch for the whole group
+    expected = [left.float().T @ right.float() for left, right, _ in problems]
+    for (left, right, out), reference in zip(problems, expected):
+        assert relative(out, reference) < 1e-5
+        alone = torch.empty_like(out)
+        linear.token_gradient(left, right, alone)
+        assert relative(out, alone) < 1e-5
+    again = [(left, right, torch.empty_like(out)) for left, right, out in problems]
+    linear.token_gradients(again)
+    assert all(torch.equal(a[2], b[2]) for a, b in zip(problems, again))
+    linear.token_gradients(problems, add=True)
+    for (_, _, out), reference in zip(problems, expected):
+        assert relative(out, 2 * reference) < 1e-5
 
 
 @pytest.mark.parametrize("rows,inner,outer,rank", [(300, 256, 520, 16), (1024, 512, 768, 256)])

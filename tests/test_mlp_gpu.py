@@ -346,4 +346,6 @@ def test_keeping_low_rank_inputs_changes_what_is_retained_not_a_value():
     assert torch.equal(results[0][0], results[1][0])
     assert all(torch.equal(a, b) for a, b in zip(results[0][1], results[1][1]))
     assert results[0][2] == module.cache_bytes(14)
-    assert results[1][2] == module.cache_bytes(14) + 14 * 8 * 2      # plus the down projection's [rows, rank] bf16
+    # plus the down projection's [rows, rank] low-rank input and the six adapters in the compute dtype (bf16)
+    adapters = sum(p.numel() for name, p in module.named_parameters() if "lora_" in name)
+    assert results[1][2] == module.cache_bytes(14) + 14 * 8 * 2 + adapters * 2

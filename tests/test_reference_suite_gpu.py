@@ -55,7 +55,7 @@ def test_reference_operator_tests_pass_on_this_library():
     print(tail)
     assert "causal_tuner.kernels modules served by causal_tuner_b200: linear, mlp_cuda, nf4_cuda, core_cuda, loss, loss_cuda" \
         in result.stdout, tail
-    summary = result.stdout.strip().splitlines()[-1]
+    summary = [line for line in result.stdout.strip().splitlines() if " passed" in line or " failed" in line][-1]
     counts = {word: int(number) for number, word in re.findall(r"(\d+) (passed|failed|error|errors|skipped|deselected)", summary)}
     assert result.returncode == 0 and not counts.get("failed") and not counts.get("error") and not counts.get("errors"), tail
     assert counts.get("passed", 0) >= EXPECTED_PASSED, summary
