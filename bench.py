@@ -650,29 +650,51 @@ def run_shapes(args):
                        "ours_tflops": flop / best[0] / 1e6, "cublas_tflops": flop / best[1] / 1e6,
                        "rel_diff": ((ours_out.float() - library_out.float()).norm() / library_out.float().norm()).item()}
         del left, right, ours_out, library_out
-    print(json.dumps({"workload": "shapes (GEMMs of one step7b layer, ours vs torch.matmul on the same GPU)", "shapes": table}),
-          flush=True)
+    # Where should the NF4 decode run? The gate/up base product x . dequant(W)^T (K = 4096, N = 14336) with the
+    # decode as its own kernel into a dense scratch followed by the GEMM (what the operators do), against the
+    # decode inside the GEMM's producer stage (ct_matmul_nf4), which repeats it for every 256-row tile of x.
+    from causal_tuner_b200.kernels.nf4_cuda import dequantize_nf4
+    from causal_tuner_b200.quant import quantize_nf4
+    packed, state = quantize_nf4((torch.randn(OUTER, INNER, device=device) * .02).bfloat16(), blocksize=64, nested=False)
+    placement = {}
+    for tokens in (256, 512, 1024, 4096, 16384):
+        x = make(tokens, INNER)
+        out_once, out_fused = (torch.empty(tokens, OUTER, device=device, dtype=torch.bfloat16) for _ in range(2))
+        once = lambda: linear.matmul(x, dequantize_nf4(packed, state, torch.bfloat16).T, out=out_once)
+        fused = lambda: linear.matmul_nf4(x, packed, state, out=out_fused)
+        count = max(20, int(6e4 / (2 * tokens * OUTER * INNER / 1.3e15 * 1e6 + 30)))
+        best = [min(burst(f, count) for _ in range(2)) for f in (once, fused)]
+        placement[str(tokens)] = {"decode_then_gemm_us": best[0], "decode_inside_gemm_us": best[1],
+                                  "identical": bool(torch.equal(out_once, out_fused))}
+        del x, out_once, out_fused
+    print(json.dumps({"workload": "shapes (GEMMs of one step7b layer, ours vs torch.matmul on the same GPU)", "shapes": table,
+                      "nf4_decode_placement": placement}), flush=True)
 
 
-# DRAM traffic of the tcgen05 GEMM kernels, from the ncu capture summarised in
-# profiles/step7b_one_layer_gemm_dram_traffic.md: one decoder layer of this workload (16384 tokens, forward +
-# backward, MLP activations kept), `dram__bytes_read.sum + dram__bytes_write.sum` summed over that layer's
-# GEMM launches. Every layer launches the same GEMMs on the same shapes, so a step is `layers` times this.
-LAYER_GEMM_DRAM_BYTES = {"step7b": None, "step1b": None}
-LAYER_GEMM_LAUNCHES = {"step7b": None, "step1b": None}
+# DRAM traffic of the tcgen05 GEMM kernels (profiles/step7b_gemm_dram_traffic_ncu.md): `dram__bytes_read.sum +
+# dram__bytes_write.sum` summed over the GEMM launches of one update of this workload cut to ONE and to TWO decoder
+# layers (16384 tokens, forward + backward, MLP activations kept, the lm_head's GEMMs included). The difference
+# is one layer, the rest is the head; every layer launches the same GEMMs, so a step is layers x layer + head.
+# `operands` is the least those launches could move: every operand read once and every result written once.
+GEMM_DRAM_TRAFFIC = {"step7b": {"layer_bytes": 19.94e9, "head_bytes": 12.09e9, "layer_launches": 25, "head_launches": 12,
+                                "operands_bytes_per_step": 348e9}}
 
 
 def gemm_traffic(workload, config, launches_per_step):
-    """`traffic` (DRAM bytes per GEMM launch, averaged over the launches of a step) and the operand bytes the
-    same launches need at least, for the roofline record; None while no capture of this workload is on file."""
-    per_layer = LAYER_GEMM_DRAM_BYTES.get(workload)
-    if not per_layer or not launches_per_step:
+    """`traffic`: DRAM bytes per GEMM launch, averaged over the launches of a step, for the roofline record; None
+    for a workload of which no capture is on file."""
+    capture = GEMM_DRAM_TRAFFIC.get(workload)
+    if not capture or not launches_per_step:
         return {"traffic": None}
     layers = config["num_hidden_layers"]
-    return {"traffic": per_layer * layers / launches_per_step,
-            "traffic_note": (f"ncu dram__bytes_read.sum + dram__bytes_write.sum over the GEMM launches of ONE decoder layer "
-                             f"(forward + backward, this workload's token count) x {layers} layers / GEMM launches per step; "
-                             f"the head's two GEMMs per loss tile are not in the capture")}
+    step_bytes = layers * capture["layer_bytes"] + capture["head_bytes"]
+    launches = layers * capture["layer_launches"] + capture["head_launches"]
+    return {"traffic": step_bytes / launches, "traffic_per_step": step_bytes,
+            "operand_bytes_per_step": capture["operands_bytes_per_step"],
+            "traffic_note": (f"ncu dram__bytes_read.sum + dram__bytes_write.sum over the GEMM launches of this workload with 1 "
+                             f"and with 2 decoder layers; step = {layers} x (difference) + head = {launches} launches "
+                             f"(this run: {launches_per_step:.0f}); operand bytes = every operand read once, every result "
+                             f"written once")}
 
 
 def run_step(args):

@@ -260,6 +260,17 @@ extern "C" int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* 
   return gemm_dispatch(g, path, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int ct_matmul_nf4(const void* x, int64_t ldx, const uint8_t* packed, const float* absmax, const float* code,
+                             void* out, int64_t ld_out, int64_t T, int64_t K, int64_t N, int blocksize, int dtype,
+                             void* stream) {
+  if (T < 0 || K < 0 || N < 0) return fail(CT_ERR_ARG, "ct_matmul_nf4: negative size");
+  if (T == 0 || N == 0) return CT_OK;
+  if (!x || !packed || !absmax || !code || !out) return fail(CT_ERR_ARG, "ct_matmul_nf4: null pointer");
+  if (dtype != CT_BF16 || blocksize != 64)
+    return fail(CT_ERR_UNSUPPORTED, "ct_matmul_nf4: bf16 activations and 64-element blocks with fp32 absmax only");
+  return gemm_tcgen05_nf4(x, ldx, packed, absmax, code, out, ld_out, T, K, N, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* a, const void* b,
                                  const void* bias, const void* residual, int64_t ld_res, void* out, int64_t ld_out,
                                  void* xa, int64_t ld_xa, int64_t T, int64_t K, int64_t N, int64_t r, int dtype,

@@ -121,6 +121,11 @@ bool gemm_tcgen05_supported(const GemmArgs& g);
 // Several independent products (at most 6) in ONE launch of the CTA-pair kernel; each must be supported.
 int gemm_tcgen05_group(const GemmArgs* problems, int count, cudaStream_t stream);
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream);
+// out[T, N] = x[T, K] . dequant(W)^T with the NF4 decode of W[N, K] inside the tcgen05 kernel (bf16, blocks of 64).
+bool gemm_tcgen05_nf4_supported(const void* x, int64_t ldx, const void* packed, const void* absmax, const void* code,
+                                const void* out, int64_t ldo, int64_t T, int64_t K, int64_t N);
+int gemm_tcgen05_nf4(const void* x, int64_t ldx, const uint8_t* packed, const float* absmax, const float* code,
+                     void* out, int64_t ldo, int64_t T, int64_t K, int64_t N, cudaStream_t stream);
 // Launches one thread that waits `limit_us` on a barrier nothing completes and reports it (gemm_tc.cu).
 int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream);
 

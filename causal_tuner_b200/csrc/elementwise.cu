@@ -3,6 +3,7 @@
 // RoPE, the residual add and the ordered reduction of split-contraction
 // partial sums. All are grid-stride loops over 16-byte vectors where the
 // buffers allow it.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -13,15 +14,22 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// Grid of a grid-stride kernel: exactly as many CTAs as are resident at once (SM count x CTAs per SM at this
-// kernel's register use), never more than the work. Every CTA then carries the same share of the work from
-// the first cycle to the last; a larger grid would run its surplus CTAs as a second, mostly empty wave.
+// Grid of an elementwise kernel: one CTA per kThreads * per_thread work items, i.e. every thread makes one pass
+// (the kernels are grid-stride loops, so any grid is correct). Measured on B200 against a persistent grid of
+// exactly the resident CTAs: the SwiGLU forward runs 21 % faster (205 vs 260 us at 16384 x 14336) and its
+// in-place backward 14 % (416 vs 481 us) - the hardware's block scheduler keeps more loads in flight than a
+// loop whose next iteration waits for this one's stores. CT_B200_ELEMENTWISE_PERSISTENT=1 restores the
+// persistent grid for comparison runs.
 template <typename Kernel>
-unsigned grid_for(Kernel kernel, int64_t work_items) {
-  static std::mutex mutex;
-  static std::unordered_map<const void*, int> resident;      // kernel -> resident CTAs on the current device type
-  int64_t cap = 0;
-  {
+unsigned grid_for(Kernel kernel, int64_t work_items, int per_thread = 1) {
+  static const bool persistent = [] {
+    const char* text = getenv("CT_B200_ELEMENTWISE_PERSISTENT");
+    return text && text[0] == '1';
+  }();
+  int64_t blocks = (work_items + static_cast<int64_t>(kThreads) * per_thread - 1) / (static_cast<int64_t>(kThreads) * per_thread);
+  if (persistent) {
+    static std::mutex mutex;
+    static std::unordered_map<const void*, int> resident;      // kernel -> resident CTAs on the current device type
     std::lock_guard<std::mutex> lock(mutex);
     const void* key = reinterpret_cast<const void*>(kernel);
     auto found = resident.find(key);
@@ -37,10 +45,9 @@ unsigned grid_for(Kernel kernel, int64_t work_items) {
       }
       found = resident.emplace(key, sms * per_sm).first;
     }
-    cap = found->second;
+    if (blocks > found->second) blocks = found->second;
   }
-  int64_t blocks = (work_items + kThreads - 1) / kThreads;
-  if (blocks > cap) blocks = cap;
+  if (blocks > (1LL << 30)) blocks = 1LL << 30;
   if (blocks < 1) blocks = 1;
   return static_cast<unsigned>(blocks);
 }
@@ -415,12 +422,13 @@ extern "C" int ct_swiglu(const void* gate, const void* up, const void* grad, voi
   if (dtype == CT_BF16) {
     const bool vec = n % 8 == 0 && aligned16(gate) && aligned16(up) && (!grad || aligned16(grad)) &&
                      (!reconstruct || aligned16(out)) && (!grad || (aligned16(dg) && aligned16(du)));
-    if (vec)
-      (grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>)<<<
-          grid_for(grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>, n / 8), kThreads, 0, s>>>(
+    if (vec) {
+      const unsigned blocks =
+          grid_for(grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>, n / 8, kSwigluUnroll);
+      (grad ? swiglu_bf16_vec_kernel<true> : swiglu_bf16_vec_kernel<false>)<<<blocks, kThreads, 0, s>>>(
           static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<const uint4*>(grad),
           static_cast<uint4*>(out), static_cast<uint4*>(dg), static_cast<uint4*>(du), n / 8, reconstruct);
-    else
+    } else
       swiglu_kernel<__nv_bfloat16><<<grid_for(swiglu_kernel<__nv_bfloat16>, n), kThreads, 0, s>>>(
           static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
           static_cast<const __nv_bfloat16*>(grad), static_cast<__nv_bfloat16*>(out),

@@ -109,6 +109,12 @@ struct TcParams {
   const __nv_bfloat16* residual;
   int64_t ld_res;
   int* error_flag;
+  // In-kernel NF4 decode of the B operand (gemm_tcgen05_nf4_kernel only): W[N, nf4_k] as packed codes, row-major,
+  // two per byte, with one fp32 absmax per 64 elements and the 16-entry code table.
+  const uint8_t* nf4_packed;
+  const float* nf4_absmax;
+  const float* nf4_code;
+  int64_t nf4_k;
 
   // One problem per launch: every tile belongs to it.
   __device__ __forceinline__ int total_tiles() const { return m_tiles * n_tiles * splits; }
@@ -117,6 +123,7 @@ struct TcParams {
     return *this;
   }
   __device__ __forceinline__ int* flag() const { return error_flag; }
+  __device__ __forceinline__ const TcParams& problem_for_decode() const { return *this; }
 };
 
 // Several independent products in one launch: the persistent CTAs walk the concatenated tile lists, so that
@@ -136,6 +143,7 @@ struct TcGroup {
     return problem[i];
   }
   __device__ __forceinline__ int* flag() const { return problem[0].error_flag; }
+  __device__ __forceinline__ const TcParams& problem_for_decode() const { return problem[0]; }
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -155,6 +163,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// The same test with acquire semantics at cluster scope: for a barrier whose arrivals publish shared-memory
+// writes made by threads of the peer CTA.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -506,7 +527,7 @@ __device__ __forceinline__ void stage_chunk(const TcParams& p, float (&v)[COLS],
 // own a (256 * MH) x 256 tile; each stages its 128 * MH rows of A and its 128 columns of B, the even ("leader")
 // CTA issues the cta_group::2 MMAs (one per row half and k step) for both, and both run their own epilogue on
 // their accumulator rows.
-template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params>
+template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params, bool DECODE = false>
 __device__ __forceinline__ void gemm_body(const Params& params) {
   using S = Shape<CTAS, STAGES_, KSUB_, MH>;
   constexpr int KSUB = KSUB_;
@@ -536,7 +557,8 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      // DECODE: besides the producer's expect-tx arrival, one arrival per decode warp of every CTA of the tile
+      mbar_init(full_bar(s), DECODE ? 1 + 4 * CTAS : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -611,7 +633,7 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
               const int subs = min(KSUB, hi - kb);   // a stage holds up to KSUB 64-wide k-blocks
               // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
               const uint32_t bar = lead_full0 + 8u * stage;
-              if (leader) mbar_expect_tx(full_bar(stage), CTAS * subs * SUB_BYTES);
+              if (leader) mbar_expect_tx(full_bar(stage), CTAS * subs * (DECODE ? A_BYTES : SUB_BYTES));
               auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
                 if constexpr (CTAS == 1) tma_load_2d(dst, map, bar, x, y);
                 else tma_load_2d_pair(dst, map, bar, x, y);
@@ -627,7 +649,9 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
 #pragma unroll
                   for (int j = 0; j < CTA_ROWS / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
                 }
-                if (!b_mn) {
+                if constexpr (DECODE) {
+                  // the B tile of this k-block is written by the decode warps
+                } else if (!b_mn) {
                   load(b_dst, map_b, k0, b_row0);
                 } else {
 #pragma unroll
@@ -690,6 +714,11 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
               alive = false;
               break;
             }
+            if constexpr (DECODE) {
+              // the B tiles were written by ordinary stores of both CTAs' decode warps (released at cluster scope)
+              while (!mbar_try_wait_cluster(full_bar(stage), phase)) {
+              }
+            }
             tcgen05_fence_after();
             const int subs = min(KSUB, hi - kb);
             if (lane == 0) {
@@ -729,6 +758,90 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           else umma_commit_pair(tmem_full_bar(acc));
         }
         __syncwarp();
+      }
+    }
+    __syncwarp();
+  } else if (DECODE && warp >= 6) {
+    // ------------------------------ NF4 decode warps --------------------------
+    // Thread d of the 128 owns row d of this CTA's 128 B rows: per 64-wide k-block it turns 32 packed bytes and
+    // one absmax into 64 bf16 values (code[nibble] * absmax in fp32, rounded once: the arithmetic of the
+    // stand-alone decode) and writes them as the K-major 128-byte-swizzled row the tensor core expects. The
+    // packed bytes of the NEXT stage are requested before this stage is decoded, so the loads' latency hides
+    // behind the arithmetic. One problem, one contraction segment, no slices: stage g of this CTA pair is
+    // k-blocks (g % per_tile) * KSUB .. of its (g / per_tile)-th tile.
+    const TcParams& p = params.problem_for_decode();
+    const int d = static_cast<int>(threadIdx.x) - 192;
+    float* lut = reinterpret_cast<float*>(staging);          // entry i of lane l at word 32 * i + l: no bank conflicts
+    for (int i = d; i < 16 * 32; i += 128) lut[i] = __ldg(p.nf4_code + (i >> 5));
+    asm volatile("bar.sync 1, 128;" ::: "memory");            // the four decode warps only
+    const float* mine = lut + lane;
+    const int per_tile = (p.k_blocks_total + KSUB - 1) / KSUB;
+    const int my_tiles = first_tile < total_tiles ? (total_tiles - first_tile + tile_step - 1) / tile_step : 0;
+    const int total_stages = my_tiles * per_tile;
+    uint4 word[2][KSUB][2];
+    float scale[2][KSUB];
+    auto fetch = [&](int g, int slot) {
+      const int tile = first_tile + (g / per_tile) * tile_step;
+      const int kb = (g % per_tile) * KSUB;
+      const TileCoord tc = tile_coord(tile, p);
+      const int64_t n = static_cast<int64_t>(tc.n) * BN + static_cast<int64_t>(rank) * S::kBRows + d;
+#pragma unroll
+      for (int sub = 0; sub < KSUB; ++sub) {
+        const bool live = n < p.N && kb + sub < p.k_blocks_total;
+        const int64_t element = n * p.nf4_k + static_cast<int64_t>(kb + sub) * BK;
+        const uint4* source = reinterpret_cast<const uint4*>(p.nf4_packed + element / 2);
+        word[slot][sub][0] = live ? __ldg(source) : make_uint4(0, 0, 0, 0);
+        word[slot][sub][1] = live ? __ldg(source + 1) : make_uint4(0, 0, 0, 0);
+        scale[slot][sub] = live ? __ldg(p.nf4_absmax + element / 64) : 0.f;
+      }
+    };
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+    if (total_stages > 0) fetch(0, 0);
+#pragma unroll 1
+    for (int g = 0; g < total_stages; g += 2) {
+#pragma unroll
+      for (int slot = 0; slot < 2; ++slot) {       // two stages per trip so that the register slots are static
+        const int current = g + slot;
+        if (current >= total_stages) break;
+        if (current + 1 < total_stages) fetch(current + 1, slot ^ 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, error_flag, 1))) {
+          g = total_stages;
+          break;
+        }
+        const int kb = (current % per_tile) * KSUB;
+#pragma unroll
+        for (int sub = 0; sub < KSUB; ++sub) {
+          if (kb + sub >= p.k_blocks_total) break;
+          const uint32_t row_base = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES + A_BYTES + static_cast<uint32_t>(d) * 128u;
+          const uint32_t words[8] = {word[slot][sub][0].x, word[slot][sub][0].y, word[slot][sub][0].z, word[slot][sub][0].w,
+                                     word[slot][sub][1].x, word[slot][sub][1].y, word[slot][sub][1].z, word[slot][sub][1].w};
+          const float s8 = scale[slot][sub];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const uint32_t byte = (words[j] >> (8 * b)) & 255u;
+              packed[b] = pack_bf16(__fmul_rn(mine[(byte >> 4) * 32], s8), __fmul_rn(mine[(byte & 15u) * 32], s8));
+            }
+            const uint32_t dst = row_base + ((static_cast<uint32_t>(j) ^ (static_cast<uint32_t>(d) & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
+                         "r"(packed[2]), "r"(packed[3])
+                         : "memory");
+          }
+        }
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 1) mbar_arrive(full_bar(stage));
+          else mbar_arrive_cluster(lead_full0 + 8u * stage);
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
     __syncwarp();
@@ -874,6 +987,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, STAGES_, KS
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads, 1)
     gemm_tcgen05_group_kernel(const __grid_constant__ TcGroup group) {
   gemm_body<2, 3, 2, 1>(group);
+}
+
+// y = x . dequant(W)^T with the NF4 decode inside the kernel: four more warps per CTA write the B tiles.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads + 128, 1)
+    gemm_tcgen05_nf4_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<2, 3, 2, 1, TcParams, true>(p);
 }
 
 // The 512 x 256 tile: two row halves per CTA, four ring stages of one 48 KB k-block, two epilogue warp sets.
@@ -1165,6 +1284,10 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
   p.ld_res = g.ld_res;
   p.error_flag = device_error_flag();
   if (!p.error_flag) return fail(CT_ERR_CUDA, "gemm_tcgen05: no device error flag");
+  p.nf4_packed = nullptr;
+  p.nf4_absmax = nullptr;
+  p.nf4_code = nullptr;
+  p.nf4_k = 0;
   return CT_OK;
 }
 
@@ -1249,6 +1372,56 @@ int gemm_tcgen05_group(const GemmArgs* problems, int count, cudaStream_t stream)
   if (timed) timing_end(stream, flops, problems[0].M, problems[0].N, -count);   // k = -count marks a grouped launch
   count_launch(true);
   return check_launch("gemm_tcgen05_group");
+}
+
+// out[T, N] (bf16) = x[T, K] . dequant(W)^T with W[N, K] given as packed NF4 codes (two per byte, row-major), one
+// fp32 absmax per 64 elements and the 16-entry code table: the decode runs inside the GEMM (four extra warps per
+// CTA write the B tiles), so the dense weight never exists in memory. K must be a multiple of 64.
+bool gemm_tcgen05_nf4_supported(const void* x, int64_t ldx, const void* packed, const void* absmax, const void* code,
+                                const void* out, int64_t ldo, int64_t T, int64_t K, int64_t N) {
+  if (T <= 0 || N <= 0 || K <= 0 || K % BK != 0) return false;
+  if (T > (1LL << 31) - 2 * BM || N > (1LL << 31) - BN || K > (1LL << 31) - BK) return false;
+  if (!x || !packed || !absmax || !code || !out) return false;
+  if (!operand_ok(x, ldx, 1) || ldx < K) return false;
+  if ((reinterpret_cast<uintptr_t>(packed) & 15) != 0 || (reinterpret_cast<uintptr_t>(absmax) & 3) != 0) return false;
+  return ldo >= N;
+}
+
+int gemm_tcgen05_nf4(const void* x, int64_t ldx, const uint8_t* packed, const float* absmax, const float* code,
+                     void* out, int64_t ldo, int64_t T, int64_t K, int64_t N, cudaStream_t stream) {
+  if (!gemm_tcgen05_nf4_supported(x, ldx, packed, absmax, code, out, ldo, T, K, N))
+    return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_nf4: needs bf16 x with 16-byte aligned rows, K a multiple of 64, 16-byte aligned codes");
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(CT_ERR_CUDA, "gemm_tcgen05_nf4: no current device");
+  GemmArgs g;
+  g.M = T; g.N = N; g.nseg = 1; g.in_dtype = CT_BF16;
+  g.seg[0].a = x; g.seg[0].a_rs = ldx; g.seg[0].a_cs = 1;
+  g.seg[0].b = x; g.seg[0].b_rs = 1; g.seg[0].b_cs = ldx; g.seg[0].k = K;     // B is never loaded: any valid map will do
+  g.out = out; g.ldo = ldo; g.out_dtype = CT_BF16; g.beta = 0; g.bias = nullptr; g.residual = nullptr; g.ld_res = 0;
+  g.split_k = 1;
+  TcParams p;
+  const Variant plain{1, false};
+  int rc = fill_params(g, 2, plain, &p);
+  if (rc != CT_OK) return rc;
+  p.nf4_packed = packed;
+  p.nf4_absmax = absmax;
+  p.nf4_code = code;
+  p.nf4_k = K;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(CT_ERR_CUDA, "gemm_tcgen05_nf4: cannot read the SM count");
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles, slots = sms / 2;
+  const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * 2);
+  static bool configured[64] = {};
+  using S = Shape<2, 3, 2, 1>;
+  rc = configure(gemm_tcgen05_nf4_kernel, S::kSmemBytes, &configured[device]);
+  if (rc != CT_OK) return rc;
+  const bool timed = timing_enabled();
+  if (timed) timing_begin(stream);
+  launch_dependent(gemm_tcgen05_nf4_kernel, dim3(grid), dim3(S::kThreads + 128), S::kSmemBytes, stream, p);
+  if (timed) timing_end(stream, 2.0 * static_cast<double>(T) * static_cast<double>(N) * static_cast<double>(K), T, N, K);
+  count_launch(true);
+  return check_launch("gemm_tcgen05_nf4");
 }
 
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {

@@ -140,6 +140,29 @@ def matmul(left, right, *, out, add=False):
     return out
 
 
+def matmul_nf4(x, weight, state, *, out):
+    """out = x @ dequantize_nf4(weight, state).T with the decode inside the GEMM (ct_matmul_nf4): the dense
+    weight is never written. Bit-identical to decoding first. bf16, 64-element blocks, fp32 absmax; raises
+    NotImplementedError otherwise. Every 256-row tile of x repeats the decode, so decoding once
+    (`materialize`) is faster from a few hundred tokens up - which is what the operators do."""
+    _lib.require_cuda(x, weight, out)
+    if state.quant_type != "nf4" or bool(state.nested) or state.absmax.dtype != torch.float32:
+        raise NotImplementedError("matmul_nf4 takes plain NF4 with fp32 absmax")
+    if state.dtype not in (torch.bfloat16, torch.float32) or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise NotImplementedError("matmul_nf4 computes in bf16 (quant state bf16 or fp32)")
+    x = _readable(x)
+    _writable(out, "out")
+    outer, inner = state.shape
+    if x.shape[1] != inner or out.shape != (x.shape[0], outer):
+        raise ValueError("matmul_nf4 shape mismatch")
+    code = state.code if state.code.dtype == torch.float32 else state.code.float()
+    with _lib.on_device(x):
+        _lib.check(_lib.load().ct_matmul_nf4(x.data_ptr(), _leading(x), weight.data_ptr(), state.absmax.data_ptr(),
+                                            code.data_ptr(), out.data_ptr(), _leading(out), x.shape[0], inner, outer,
+                                            int(state.blocksize), _lib.code_of(x.dtype), _lib.stream_of(x)))
+    return out
+
+
 # ---- the reference's primitives -----------------------------------------------------------
 
 def materialize(weight, state, dtype):

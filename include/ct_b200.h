@@ -135,6 +135,21 @@ CT_API int ct_matmul(const void* A, int64_t a_rs, int64_t a_cs, const void* B, i
               int64_t b_cs, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
               int in_dtype, int out_dtype, int add, int path, void* stream);
 
+/* ---- base product with the NF4 decode inside the GEMM -------------------------------
+ * Replaces `materialize` + the base product of kernels/linear.py:29 (`dequantize_nf4`, kernels/nf4_cuda.py:32-43,
+ * then torch.mm) for callers that do not want the dense weight to exist:
+ *   out[T, N] = round(x[T, K] @ W^T),  W[n, k] = round(code[nibble(n, k)] * absmax[(n * K + k) / 64])
+ * with the decode arithmetic of ct_nf4_decode (fp32 product rounded once to bf16; bit-identical values).
+ * Four extra warps per CTA turn 128-bit loads of packed codes into the swizzled shared-memory B tiles that the
+ * tcgen05 MMAs read; x tiles arrive by TMA. The result is bit-identical to ct_nf4_decode followed by ct_matmul.
+ * Every row tile of x decodes the weight again, so this form pays for small T only (a few hundred tokens);
+ * the training path decodes once per call instead (see ct_nf4_decode). bf16, `blocksize` 64, fp32 absmax
+ * (not nested), K a multiple of 64, rows of x and the packed codes 16-byte aligned; anything else returns
+ * CT_ERR_UNSUPPORTED and the caller decodes first. */
+CT_API int ct_matmul_nf4(const void* x, int64_t ldx, const uint8_t* packed, const float* absmax,
+                         const float* code, void* out, int64_t ld_out, int64_t T, int64_t K, int64_t N,
+                         int blocksize, int dtype, void* stream);
+
 /* ---- fused projection forward --------------------------------------------
  * Replaces kernels/linear.py:27-33 (forward_linear) plus the in-place residual
  * add of kernels/linear.py:90-91.

@@ -268,6 +268,30 @@ def test_grouped_token_gradients_equal_the_separate_products(path, tokens, shape
         assert relative(out, 2 * reference) < 1e-5
 
 
+@pytest.mark.parametrize("rows,inner,outer", [(512, 4096, 1024), (300, 256, 520), (2051, 1024, 776), (64, 64, 8)])
+def test_decode_inside_the_gemm_is_bit_identical_to_decode_then_gemm(rows, inner, outer):
+    """ct_matmul_nf4: the NF4 decode as a stage of the tcgen05 kernel (decode warps fill the swizzled B tiles).
+    Same decoded values, same MMA sequence per tile -> the very bits of ct_nf4_decode followed by ct_matmul."""
+    from causal_tuner_b200.kernels.nf4_cuda import dequantize_nf4
+    from causal_tuner_b200.quant import quantize_nf4
+    torch.manual_seed(rows)
+    weight = (torch.randn(outer, inner, device="cuda") * .05).bfloat16()
+    packed, state = quantize_nf4(weight, blocksize=64, nested=False)
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    dense = dequantize_nf4(packed, state, torch.bfloat16)
+    expected = torch.empty(rows, outer, device="cuda", dtype=torch.bfloat16)
+    linear.matmul(x, dense.T, out=expected)
+    actual = torch.full((rows, outer), float("nan"), device="cuda", dtype=torch.bfloat16)
+    before = _lib.tcgen05_launch_count()
+    linear.matmul_nf4(x, packed, state, out=actual)
+    assert _lib.tcgen05_launch_count() == before + 1
+    assert torch.equal(actual, expected)
+    assert relative(actual, x.float() @ dense.float().T) < 4e-3
+    nested_packed, nested_state = quantize_nf4(weight, blocksize=64, nested=True)
+    with pytest.raises(NotImplementedError):
+        linear.matmul_nf4(x, nested_packed, nested_state, out=actual)
+
+
 @pytest.mark.parametrize("rows,inner,outer,rank", [(300, 256, 520, 16), (1024, 512, 768, 256)])
 def test_projection_pieces_equal_the_fused_calls(path, rows, inner, outer, rank):
     x = torch.randn(rows, inner, device="cuda").bfloat16()
