@@ -271,6 +271,59 @@ extern "C" int ct_matmul_nf4(const void* x, int64_t ldx, const uint8_t* packed, 
   return gemm_tcgen05_nf4(x, ldx, packed, absmax, code, out, ld_out, T, K, N, static_cast<cudaStream_t>(stream));
 }
 
+namespace {
+int gated(const char* what, const void* x, int64_t ldx, const void* w_pair, int64_t ldw, const void* xa_gate,
+          const void* xa_up, int64_t ld_xa, const void* b_gate, const void* b_up, const void* dh, void* h, void* gate,
+          void* up, int64_t ld_out, int64_t T, int64_t K, int64_t N, int64_t r_gate, int64_t r_up, int dtype,
+          void* stream) {
+  if (T < 0 || K <= 0 || N < 0 || r_gate <= 0 || r_up <= 0) return fail(CT_ERR_ARG, "%s: sizes", what);
+  if (T == 0 || N == 0) return CT_OK;
+  if (!x || !w_pair || !xa_gate || !xa_up || !b_gate || !b_up || !h) return fail(CT_ERR_ARG, "%s: null pointer", what);
+  if (dtype != CT_BF16) return fail(CT_ERR_UNSUPPORTED, "%s: bf16 only", what);
+  GatedArgs a;
+  a.x = x; a.ldx = ldx; a.w_pair = w_pair; a.ldw = ldw;
+  a.xa_gate = xa_gate; a.xa_up = xa_up; a.ld_xa = ld_xa; a.b_gate = b_gate; a.b_up = b_up;
+  a.T = T; a.K = K; a.N = N; a.r_gate = r_gate; a.r_up = r_up;
+  a.h = h; a.gate = gate; a.up = up; a.dh = dh; a.ld_out = ld_out;
+  return gemm_tcgen05_gated(a, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int ct_gated_forward(const void* x, int64_t ldx, const void* w_pair, int64_t ldw, const void* xa_gate,
+                                const void* xa_up, int64_t ld_xa, const void* b_gate, const void* b_up, void* h,
+                                void* gate, void* up, int64_t ld_out, int64_t T, int64_t K, int64_t N, int64_t r_gate,
+                                int64_t r_up, int dtype, void* stream) {
+  return gated("ct_gated_forward", x, ldx, w_pair, ldw, xa_gate, xa_up, ld_xa, b_gate, b_up, nullptr, h, gate, up,
+               ld_out, T, K, N, r_gate, r_up, dtype, stream);
+}
+
+extern "C" int ct_gated_backward(const void* x, int64_t ldx, const void* w_pair, int64_t ldw, const void* xa_gate,
+                                 const void* xa_up, int64_t ld_xa, const void* b_gate, const void* b_up, const void* dh,
+                                 void* h, void* d_gate, void* d_up, int64_t ld_out, int64_t T, int64_t K, int64_t N,
+                                 int64_t r_gate, int64_t r_up, int dtype, void* stream) {
+  if (T > 0 && N > 0 && (!dh || !d_gate || !d_up)) return fail(CT_ERR_ARG, "ct_gated_backward: null pointer");
+  return gated("ct_gated_backward", x, ldx, w_pair, ldw, xa_gate, xa_up, ld_xa, b_gate, b_up, dh, h, d_gate, d_up,
+               ld_out, T, K, N, r_gate, r_up, dtype, stream);
+}
+
+extern "C" int ct_gated_input_gradient(const void* d_gate, const void* d_up, int64_t ld_signal, const void* w_pair,
+                                       int64_t ldw, const void* low_gate, const void* low_up, int64_t ld_low,
+                                       const void* a_gate, const void* a_up, void* dx, int64_t ld_dx, int64_t T,
+                                       int64_t K, int64_t N, int64_t r_gate, int64_t r_up, int add, int dtype,
+                                       void* stream) {
+  if (T < 0 || K < 0 || N <= 0 || r_gate <= 0 || r_up <= 0) return fail(CT_ERR_ARG, "ct_gated_input_gradient: sizes");
+  if (T == 0 || K == 0) return CT_OK;
+  if (!d_gate || !d_up || !w_pair || !low_gate || !low_up || !a_gate || !a_up || !dx)
+    return fail(CT_ERR_ARG, "ct_gated_input_gradient: null pointer");
+  if (dtype != CT_BF16) return fail(CT_ERR_UNSUPPORTED, "ct_gated_input_gradient: bf16 only");
+  GatedGradientArgs a;
+  a.dg = d_gate; a.du = d_up; a.ld_signal = ld_signal; a.w_pair = w_pair; a.ldw = ldw;
+  a.low_gate = low_gate; a.low_up = low_up; a.ld_low = ld_low; a.a_gate = a_gate; a.a_up = a_up;
+  a.T = T; a.K = K; a.N = N; a.r_gate = r_gate; a.r_up = r_up;
+  a.dx = dx; a.ld_dx = ld_dx; a.add = add;
+  return gemm_tcgen05_gated_input_gradient(a, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* a, const void* b,
                                  const void* bias, const void* residual, int64_t ld_res, void* out, int64_t ld_out,
                                  void* xa, int64_t ld_xa, int64_t T, int64_t K, int64_t N, int64_t r, int dtype,

@@ -84,6 +84,29 @@ __device__ __forceinline__ float round_dtype(float v, int dtype) {
   return __half2float(__float2half_rn(v));
 }
 
+// ---- SwiGLU, one element (kernels/mlp_cuda.py:10-25 of the reference) -----------------
+// h = round(silu(g)) * u; backward: d_gate = round(grad * u) * sigmoid'(g)-term, d_up = grad * round(silu(g)).
+// Shared by the stand-alone kernel and the GEMM epilogue that applies it to accumulator tiles, which have to
+// agree bit for bit: every product and the one fused multiply-add are spelled out, so the compiler has no
+// contraction of its own to decide.
+template <typename T>
+__device__ __forceinline__ void swiglu_element(float g, float u, float grad, bool backward, bool reconstruct,
+                                               float& h, float& dg, float& du) {
+  // 16-bit activations: the exponential and the reciprocal come from the special-function unit
+  // (relative error about 2^-21, far below the 8 or 11 mantissa bits the results are rounded to);
+  // the kernels are bound by instruction issue, not by HBM, with the full-precision forms.
+  float sig;
+  if constexpr (sizeof(T) == 2) sig = __fdividef(1.0f, __fadd_rn(1.0f, __expf(-g)));
+  else sig = 1.0f / (1.0f + expf(-g));
+  const float activated = round_to<T>(__fmul_rn(g, sig));
+  if (backward) {
+    const float product_grad = round_to<T>(__fmul_rn(grad, u));
+    dg = __fmul_rn(product_grad, __fmul_rn(sig, __fmaf_rn(g, __fsub_rn(1.0f, sig), 1.0f)));
+    du = __fmul_rn(grad, activated);
+  }
+  if (reconstruct) h = __fmul_rn(activated, u);
+}
+
 // ---- GEMM description shared by the SIMT and tcgen05 kernels ------------------
 // D[M, N] = (beta ? D : 0) + sum over segments s of A_s[M, k_s] * B_s[k_s, N] + bias[N]
 // then (optionally)  D = round(D) + residual, rounded again.
@@ -126,6 +149,32 @@ bool gemm_tcgen05_nf4_supported(const void* x, int64_t ldx, const void* packed, 
                                 const void* out, int64_t ldo, int64_t T, int64_t K, int64_t N);
 int gemm_tcgen05_nf4(const void* x, int64_t ldx, const uint8_t* packed, const float* absmax, const float* code,
                      void* out, int64_t ldo, int64_t T, int64_t K, int64_t N, cudaStream_t stream);
+// SwiGLU MLP in the tcgen05 kernel (bf16). `w_pair` is the gate and up weights interleaved in 128-row blocks
+// ([2 N, K]); xa_* are the low-rank inputs x . a^T, b_* the [N, r] adapter outputs.
+struct GatedArgs {
+  const void* x; int64_t ldx;
+  const void* w_pair; int64_t ldw;
+  const void* xa_gate; const void* xa_up; int64_t ld_xa;
+  const void* b_gate; const void* b_up;
+  int64_t T, K, N, r_gate, r_up;
+  void* h;            // [T, N]: silu(gate) * up
+  void* gate;         // forward: gate(x) or null; backward: d_gate
+  void* up;           // forward: up(x) or null; backward: d_up
+  const void* dh;     // null = forward; else the gradient of h (may be the same buffer as h)
+  int64_t ld_out;     // leading dimension of h, gate, up and dh
+};
+bool gemm_tcgen05_gated_supported(const GatedArgs& a);
+int gemm_tcgen05_gated(const GatedArgs& a, cudaStream_t stream);
+struct GatedGradientArgs {
+  const void* dg; const void* du; int64_t ld_signal;
+  const void* w_pair; int64_t ldw;
+  const void* low_gate; const void* low_up; int64_t ld_low;
+  const void* a_gate; const void* a_up;      // [r, K] row-major
+  int64_t T, K, N, r_gate, r_up;
+  void* dx; int64_t ld_dx;
+  int add;
+};
+int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t stream);
 // Launches one thread that waits `limit_us` on a barrier nothing completes and reports it (gemm_tc.cu).
 int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream);
 

@@ -120,25 +120,7 @@ cast_many_kernel(const __grid_constant__ CastBatch batch, int src_dtype, int dst
 }
 
 // ---- SwiGLU ---------------------------------------------------------------------
-// One scalar element of kernels/mlp_cuda.py:10-25.
-template <typename T>
-__device__ __forceinline__ void swiglu_element(float g, float u, float grad, bool backward, bool reconstruct,
-                                               float& h, float& dg, float& du) {
-  // 16-bit activations: the exponential and the reciprocal come from the special-function unit
-  // (relative error about 2^-21, far below the 8 or 11 mantissa bits the results are rounded to);
-  // this kernel is bound by instruction issue, not by HBM, with the full-precision forms.
-  float sig;
-  if constexpr (sizeof(T) == 2) sig = __fdividef(1.0f, 1.0f + __expf(-g));
-  else sig = 1.0f / (1.0f + expf(-g));
-  const float activated = round_to<T>(g * sig);
-  if (backward) {
-    const float product_grad = round_to<T>(grad * u);
-    dg = product_grad * (sig * (1.0f + g * (1.0f - sig)));
-    du = grad * activated;
-  }
-  if (reconstruct) h = activated * u;
-}
-
+// The element arithmetic (swiglu_element) lives in common.cuh: the GEMM epilogue shares it.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const T* gate, const T* up, const T* grad, T* out, T* dg, T* du, int64_t n, int reconstruct) {

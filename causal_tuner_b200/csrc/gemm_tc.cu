@@ -87,6 +87,11 @@ struct TcSegment {
   CUtensorMap a, b;
   int k_blocks;
   int a_mn, b_mn;
+  // Read by the gated kernel only (zero elsewhere).
+  int n_half;       // 1: the segment's B has N / 2 columns and its MMAs (N = 128) add to accumulator columns
+  int d_col;        //    [d_col, d_col + 128) only: the low-rank term of ONE of the two interleaved projections
+  int b_k_block;    // > 0: B is MN-major and its k rows live in a buffer of interleaved 128-row blocks: row k of
+  int b_k_offset;   //    this operand is row k + (k / 128) * 128 + b_k_offset of the buffer
 };
 
 struct TcParams {
@@ -109,6 +114,17 @@ struct TcParams {
   const __nv_bfloat16* residual;
   int64_t ld_res;
   int* error_flag;
+  // Gated epilogue (gemm_tcgen05_gated_kernel only). The accumulator tile holds 128 columns of the gate
+  // projection and the same 128 columns of the up projection side by side (B is the two weights interleaved in
+  // 128-row blocks). gated = 1: h = silu(gate) * up is written (and gate, up when their pointers are given);
+  // gated = 2: with the upstream gradient dh of h, (d_gate, d_up, h) are written - gate and up never reach
+  // memory. All five matrices are [M, N / 2] with leading dimension gated_ld; gated_h may alias gated_dh.
+  int gated;
+  __nv_bfloat16* gated_h;
+  __nv_bfloat16* gated_g;
+  __nv_bfloat16* gated_u;
+  const __nv_bfloat16* gated_dh;
+  int64_t gated_ld;
   // In-kernel NF4 decode of the B operand (gemm_tcgen05_nf4_kernel only): W[N, nf4_k] as packed codes, row-major,
   // two per byte, with one fp32 absmax per 64 elements and the 16-entry code table.
   const uint8_t* nf4_packed;
@@ -217,10 +233,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag, error_flag, code);
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
 
@@ -265,11 +281,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 }
 // TMA load issued by either CTA of a pair; the completion bytes go to `cluster_bar`, which may
 // live in the peer CTA. No multicast: the data lands in the issuing CTA only.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
-                                                 int y) {
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, uint64_t map, uint32_t cluster_bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
       : "memory");
 }
 __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
@@ -352,9 +367,9 @@ __device__ __forceinline__ uint32_t desc_high(uint32_t stride_bytes) {
 }
 
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128 (one CTA) or 256 (CTA pair), N = 256.
-__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, int m) {
+__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, int m, int n = BN) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
-         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
@@ -527,7 +542,7 @@ __device__ __forceinline__ void stage_chunk(const TcParams& p, float (&v)[COLS],
 // own a (256 * MH) x 256 tile; each stages its 128 * MH rows of A and its 128 columns of B, the even ("leader")
 // CTA issues the cta_group::2 MMAs (one per row half and k step) for both, and both run their own epilogue on
 // their accumulator rows.
-template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params, bool DECODE = false>
+template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params, bool DECODE = false, bool GATED = false>
 __device__ __forceinline__ void gemm_body(const Params& params) {
   using S = Shape<CTAS, STAGES_, KSUB_, MH>;
   constexpr int KSUB = KSUB_;
@@ -621,41 +636,66 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           const int hi = min(kb_end, seg_first + sg.k_blocks) - seg_first;
           seg_first += sg.k_blocks;
           if (lo >= hi) continue;
-          const CUtensorMap* map_a = &sg.a;
-          const CUtensorMap* map_b = &sg.b;
-          const bool a_mn = sg.a_mn != 0, b_mn = sg.b_mn != 0;
+          // Everything of the segment the copies need sits in registers before the k loop starts (the empty
+          // statement pins it): a parameter read between a stage's release and its copies would delay them.
+          uint64_t map_a = reinterpret_cast<uint64_t>(&sg.a), map_b = reinterpret_cast<uint64_t>(&sg.b);
+          int a_mn = sg.a_mn, b_mn = sg.b_mn;
+          int b_row = b_row0;
+          uint32_t sub_tx = DECODE ? A_BYTES : SUB_BYTES;     // bytes one CTA receives per k-block
+          int k_block = 0, k_offset = 0;
+          if constexpr (GATED) {
+            if (sg.n_half) {     // half as many B columns: 64 rows of a K-major [N / 2, k] matrix per CTA
+              b_row = tc.n * (BN / 2) + static_cast<int>(rank) * (S::kBRows / 2);
+              sub_tx = A_BYTES + S::kBTileBytes / 2;
+            }
+            k_block = sg.b_k_block;
+            k_offset = sg.b_k_offset;
+          }
+          asm volatile("" : "+l"(map_a), "+l"(map_b), "+r"(a_mn), "+r"(b_mn), "+r"(b_row), "+r"(sub_tx), "+r"(k_block),
+                       "+r"(k_offset));
           for (int kb = lo; kb < hi; kb += KSUB) {
+            // A freed stage has to be on its way again within the time the MMAs of the other stages take, so
+            // everything the copies need is worked out BEFORE the wait (the empty statement pins it there) and
+            // only the expect-tx and the copy instructions themselves follow it.
+            const int subs = min(KSUB, hi - kb);   // a stage holds up to KSUB 64-wide k-blocks
+            // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
+            uint32_t bar = lead_full0 + 8u * stage;
+            uint32_t expected = CTAS * subs * sub_tx;
+            uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+            int k_first = kb * BK;
+            asm volatile("" : "+r"(bar), "+r"(expected), "+r"(a_dst), "+r"(k_first));
             if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, error_flag, 1))) {
               alive = false;
               break;
             }
             if (lane == 0) {
-              const int subs = min(KSUB, hi - kb);   // a stage holds up to KSUB 64-wide k-blocks
-              // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
-              const uint32_t bar = lead_full0 + 8u * stage;
-              if (leader) mbar_expect_tx(full_bar(stage), CTAS * subs * (DECODE ? A_BYTES : SUB_BYTES));
-              auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+              if (leader) mbar_expect_tx(full_bar(stage), expected);
+              auto load = [&](uint32_t dst, uint64_t map, int x, int y) {
                 if constexpr (CTAS == 1) tma_load_2d(dst, map, bar, x, y);
                 else tma_load_2d_pair(dst, map, bar, x, y);
               };
 #pragma unroll
               for (int sub = 0; sub < KSUB; ++sub) {
                 if (sub >= subs) break;
-                const int k0 = (kb + sub) * BK;
-                const uint32_t a_dst = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES, b_dst = a_dst + A_BYTES;
+                const int k0 = k_first + sub * BK;
+                const uint32_t a_sub = a_dst + sub * SUB_BYTES, b_sub = a_sub + A_BYTES;
                 if (!a_mn) {
-                  load(a_dst, map_a, k0, a_row0);      // one box of CTA_ROWS rows
+                  load(a_sub, map_a, k0, a_row0);      // one box of CTA_ROWS rows
                 } else {
 #pragma unroll
-                  for (int j = 0; j < CTA_ROWS / 64; ++j) load(a_dst + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
+                  for (int j = 0; j < CTA_ROWS / 64; ++j) load(a_sub + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
                 }
                 if constexpr (DECODE) {
                   // the B tile of this k-block is written by the decode warps
                 } else if (!b_mn) {
-                  load(b_dst, map_b, k0, b_row0);
+                  load(b_sub, map_b, k0, b_row);
                 } else {
+                  int k_row = k0;
+                  if constexpr (GATED) {      // B's k rows live in a buffer of interleaved 128-row blocks
+                    if (k_block) k_row = k0 + ((k0 >> 7) << 7) + k_offset;
+                  }
 #pragma unroll
-                  for (int j = 0; j < S::kBRows / 64; ++j) load(b_dst + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k0);
+                  for (int j = 0; j < S::kBRows / 64; ++j) load(b_sub + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k_row);
                 }
               }
             }
@@ -701,7 +741,14 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           const int hi = min(kb_end, seg_first + sg.k_blocks) - seg_first;
           seg_first += sg.k_blocks;
           if (lo >= hi) continue;
-          const uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn, BM * CTAS);
+          uint32_t idesc = instr_desc(sg.a_mn, sg.b_mn, BM * CTAS);
+          uint32_t tmem_seg = tmem_d;
+          if constexpr (GATED) {
+            if (sg.n_half) {
+              idesc = instr_desc(sg.a_mn, sg.b_mn, BM * CTAS, BN / 2);
+              tmem_seg = tmem_d + static_cast<uint32_t>(sg.d_col);
+            }
+          }
           // K-major: 8-row groups 1024 B apart, 32 B per 16-element k step inside the swizzle atom.
           // MN-major: 64-wide column groups one box (8 KB) apart, 8-k groups 1024 B apart,
           //           16 k rows (2 KB) per k step.
@@ -734,10 +781,10 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
                     // the 128 rows of half h are 16 KB further into the A tile in either orientation
                     const uint32_t a_h = a_lo + h * (A_HALF_BYTES >> 4) + a_step * j;
                     if constexpr (CTAS == 1)
-                      umma_bf16(tmem_d + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                      umma_bf16(tmem_seg + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
                                 (accumulate | sub | j) ? 1u : 0u);
                     else
-                      umma_bf16_pair(tmem_d + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
+                      umma_bf16_pair(tmem_seg + h * BN, a_h, desc_hi, b_lo + b_step * j, desc_hi, idesc,
                                      (accumulate | sub | j) ? 1u : 0u);
                   }
                 }
@@ -861,16 +908,81 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
       const TileCoord tc = tile_coord(local, p);
       const int acc = ACCS == 2 ? (local_tile & 1) : 0;
       const uint32_t acc_phase = (local_tile / ACCS) & 1;
+      const int row0 = tc.m * TILE_M + static_cast<int>(rank) * CTA_ROWS + half * BM + quarter * 32;
+      const int64_t row = row0 + lane;
+      const bool row_ok = row < p.M;
+      // Gated backward: the upstream gradient of a 32-column chunk is requested one chunk ahead - the first
+      // chunk's before the wait for the accumulator, while the tile's main loop is still running.
+      uint4 upstream_next[GATED ? 4 : 1];
+      if constexpr (GATED) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) upstream_next[q] = make_uint4(0, 0, 0, 0);
+        if (p.gated == 2 && row_ok) {
+          const uint4* source = reinterpret_cast<const uint4*>(p.gated_dh + row * p.gated_ld + static_cast<int64_t>(tc.n) * (BN / 2));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) upstream_next[q] = source[q];
+        }
+      }
       int ok = 1;
       if (lane == 0) ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, error_flag, 4) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tcgen05_fence_after();
-      const int row0 = tc.m * TILE_M + static_cast<int>(rank) * CTA_ROWS + half * BM + quarter * 32;
-      const int64_t row = row0 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MH == 2 ? half : acc) * BN;
-      if (p.tma_store) {
+      if (GATED && p.gated) {
+        if constexpr (GATED) {
+          // Accumulator columns [0, 128) are the gate projection, [128, 256) the up projection of the same 128
+          // output columns. Each is rounded to bf16 as a stored projection output would be; the SwiGLU element
+          // arithmetic is the stand-alone kernel's.
+          const bool backward = p.gated == 2;
+          const int64_t offset = row * p.gated_ld + static_cast<int64_t>(tc.n) * (BN / 2);
+          // The chunk loop stays a loop: unrolled, the epilogue is tens of KB of code that four warps stream
+          // through the instruction cache the producer and MMA warps' short loops live in.
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t gate_raw[32], up_raw[32];
+            __syncwarp();
+            tmem_load_32_issue(taddr + c * 32, gate_raw);
+            tmem_load_32_issue(taddr + BN / 2 + c * 32, up_raw);
+            uint4 upstream[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) upstream[q] = upstream_next[GATED ? q : 0];
+            if (backward && row_ok && c + 1 < BN / 64) {
+              const uint4* source = reinterpret_cast<const uint4*>(p.gated_dh + offset + (c + 1) * 32);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) upstream_next[GATED ? q : 0] = source[q];
+            }
+            tmem_load_wait(gate_raw);
+            tmem_load_wait(up_raw);
+            if (row_ok) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 grad_vector = upstream[q];
+                const uint32_t grad_words[4] = {grad_vector.x, grad_vector.y, grad_vector.z, grad_vector.w};
+                uint32_t h_words[4], g_words[4], u_words[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float g0 = round_to<__nv_bfloat16>(__uint_as_float(gate_raw[8 * q + 2 * j]));
+                  const float g1 = round_to<__nv_bfloat16>(__uint_as_float(gate_raw[8 * q + 2 * j + 1]));
+                  const float u0 = round_to<__nv_bfloat16>(__uint_as_float(up_raw[8 * q + 2 * j]));
+                  const float u1 = round_to<__nv_bfloat16>(__uint_as_float(up_raw[8 * q + 2 * j + 1]));
+                  const float2 grad = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&grad_words[j]));
+                  float h0 = 0.f, h1 = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+                  swiglu_element<__nv_bfloat16>(g0, u0, grad.x, backward, true, h0, a0, b0);
+                  swiglu_element<__nv_bfloat16>(g1, u1, grad.y, backward, true, h1, a1, b1);
+                  h_words[j] = pack_bf16(h0, h1);
+                  g_words[j] = backward ? pack_bf16(a0, a1) : pack_bf16(g0, g1);
+                  u_words[j] = backward ? pack_bf16(b0, b1) : pack_bf16(u0, u1);
+                }
+                const int64_t at = offset + c * 32 + q * 8;
+                *reinterpret_cast<uint4*>(p.gated_h + at) = make_uint4(h_words[0], h_words[1], h_words[2], h_words[3]);
+                if (p.gated_g) *reinterpret_cast<uint4*>(p.gated_g + at) = make_uint4(g_words[0], g_words[1], g_words[2], g_words[3]);
+                if (p.gated_u) *reinterpret_cast<uint4*>(p.gated_u + at) = make_uint4(u_words[0], u_words[1], u_words[2], u_words[3]);
+              }
+            }
+          }
+        }
+      } else if (p.tma_store) {
         if constexpr (MH == 1) {
           // 64-column chunks, two 4 KB staging tiles per warp (this epilogue runs under the next tile's main loop)
 #pragma unroll 1
@@ -993,6 +1105,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::k
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads + 128, 1)
     gemm_tcgen05_nf4_kernel(const __grid_constant__ TcParams p) {
   gemm_body<2, 3, 2, 1, TcParams, true>(p);
+}
+
+// The pair kernel with the extras of a SwiGLU MLP: B operands made of two projections' weights interleaved in
+// 128-row blocks, per-projection low-rank segments that add to half of the accumulator columns, and the SwiGLU
+// forward or backward applied to the accumulator in the epilogue (TcParams::gated).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads, 1)
+    gemm_tcgen05_gated_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<2, 3, 2, 1, TcParams, false, true>(p);
 }
 
 // The 512 x 256 tile: two row halves per CTA, four ring stages of one 48 KB k-block, two epilogue warp sets.
@@ -1258,6 +1378,7 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
     p.k_blocks_total += t.k_blocks;
     t.a_mn = sg.a_cs == 1 ? 0 : 1;
     t.b_mn = sg.b_rs == 1 ? 0 : 1;
+    t.n_half = t.d_col = t.b_k_block = t.b_k_offset = 0;
     // K-major: contiguous index is k, rows are m (or n). MN-major: contiguous index is m (or n), rows are k.
     rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM * halves);
     if (rc != CT_OK) return rc;
@@ -1288,6 +1409,10 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
   p.nf4_absmax = nullptr;
   p.nf4_code = nullptr;
   p.nf4_k = 0;
+  p.gated = 0;
+  p.gated_h = p.gated_g = p.gated_u = nullptr;
+  p.gated_dh = nullptr;
+  p.gated_ld = 0;
   return CT_OK;
 }
 
@@ -1422,6 +1547,125 @@ int gemm_tcgen05_nf4(const void* x, int64_t ldx, const uint8_t* packed, const fl
   if (timed) timing_end(stream, 2.0 * static_cast<double>(T) * static_cast<double>(N) * static_cast<double>(K), T, N, K);
   count_launch(true);
   return check_launch("gemm_tcgen05_nf4");
+}
+
+namespace {
+
+int launch_gated(const TcParams& p, double flops, int64_t M, int64_t N, int64_t K, const char* what,
+                 cudaStream_t stream) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(CT_ERR_CUDA, "%s: no current device", what);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(CT_ERR_CUDA, "%s: cannot read the SM count", what);
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles, slots = sms / 2;
+  const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * 2);
+  static bool configured[64] = {};
+  using S = Shape<2, 3, 2, 1>;
+  const int rc = configure(gemm_tcgen05_gated_kernel, S::kSmemBytes, &configured[device]);
+  if (rc != CT_OK) return rc;
+  const bool timed = timing_enabled();
+  if (timed) timing_begin(stream);
+  launch_dependent(gemm_tcgen05_gated_kernel, dim3(grid), dim3(S::kThreads), S::kSmemBytes, stream, p);
+  if (timed) timing_end(stream, flops, M, N, K);
+  count_launch(true);
+  return check_launch(what);
+}
+
+bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15) == 0; }
+
+}  // namespace
+
+bool gemm_tcgen05_gated_supported(const GatedArgs& a) {
+  if (a.T <= 0 || a.K <= 0 || a.N <= 0 || a.N % (BN / 2) != 0 || a.r_gate <= 0 || a.r_up <= 0) return false;
+  if (a.T > (1LL << 31) - 2 * BM || 2 * a.N > (1LL << 31) - BN || a.K > (1LL << 31) - BK) return false;
+  if (!a.x || !a.w_pair || !a.xa_gate || !a.xa_up || !a.b_gate || !a.b_up || !a.h) return false;
+  if (!operand_ok(a.x, a.ldx, 1) || !operand_ok(a.w_pair, a.ldw, 1) || a.ldx < a.K || a.ldw < a.K) return false;
+  if (!operand_ok(a.xa_gate, a.ld_xa, 1) || !operand_ok(a.xa_up, a.ld_xa, 1)) return false;
+  if (!operand_ok(a.b_gate, a.r_gate, 1) || !operand_ok(a.b_up, a.r_up, 1)) return false;
+  if (a.ld_out < a.N || a.ld_out % 8 != 0) return false;
+  if (!aligned16(a.h) || !aligned16(a.gate) || !aligned16(a.up) || !aligned16(a.dh)) return false;
+  if (a.dh && (!a.gate || !a.up)) return false;
+  return true;
+}
+
+// One launch for gate(x), up(x) and the SwiGLU between them and the down projection. `w_pair` is
+// [2 N, K]: rows [256 t, 256 t + 128) are rows [128 t, 128 t + 128) of the gate weight, the next 128 rows the
+// same rows of the up weight. Forward (dh == null): h = silu(gate) * up, and gate / up themselves where
+// their pointers are given (the cached mode). Backward (dh given): gate and up are recomputed in the
+// accumulator and (d_gate, d_up, h) are written to (gate, up, h); h may be dh.
+int gemm_tcgen05_gated(const GatedArgs& a, cudaStream_t stream) {
+  if (!gemm_tcgen05_gated_supported(a))
+    return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_gated: needs bf16 operands with 16-byte aligned rows and a width that is a multiple of 128");
+  GemmArgs g;
+  g.M = a.T; g.N = 2 * a.N; g.nseg = 3; g.in_dtype = CT_BF16;
+  g.seg[0].a = a.x; g.seg[0].a_rs = a.ldx; g.seg[0].a_cs = 1;
+  g.seg[0].b = a.w_pair; g.seg[0].b_rs = 1; g.seg[0].b_cs = a.ldw; g.seg[0].k = a.K;
+  g.seg[1].a = a.xa_gate; g.seg[1].a_rs = a.ld_xa; g.seg[1].a_cs = 1;
+  g.seg[1].b = a.b_gate; g.seg[1].b_rs = 1; g.seg[1].b_cs = a.r_gate; g.seg[1].k = a.r_gate;
+  g.seg[2].a = a.xa_up; g.seg[2].a_rs = a.ld_xa; g.seg[2].a_cs = 1;
+  g.seg[2].b = a.b_up; g.seg[2].b_rs = 1; g.seg[2].b_cs = a.r_up; g.seg[2].k = a.r_up;
+  g.out = a.h; g.ldo = a.ld_out; g.out_dtype = CT_BF16; g.beta = 0; g.bias = nullptr; g.residual = nullptr;
+  g.ld_res = 0; g.split_k = 1;
+  TcParams p;
+  const Variant plain{1, false};
+  int rc = fill_params(g, 2, plain, &p);
+  if (rc != CT_OK) return rc;
+  // The low-rank segments: B is [N, r], 64 rows of it per CTA, their MMAs cover half of the accumulator.
+  for (int s = 1; s <= 2; ++s) {
+    TcSegment& t = p.seg[s];
+    rc = make_map(&t.b, g.seg[s].b, g.seg[s].k, a.N, g.seg[s].b_cs, BN / 4);
+    if (rc != CT_OK) return rc;
+    t.n_half = 1;
+    t.d_col = s == 1 ? 0 : BN / 2;
+  }
+  p.gated = a.dh ? 2 : 1;
+  p.gated_h = static_cast<__nv_bfloat16*>(a.h);
+  p.gated_g = static_cast<__nv_bfloat16*>(a.gate);
+  p.gated_u = static_cast<__nv_bfloat16*>(a.up);
+  p.gated_dh = static_cast<const __nv_bfloat16*>(a.dh);
+  p.gated_ld = a.ld_out;
+  const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.N) *
+                       (2.0 * static_cast<double>(a.K) + static_cast<double>(a.r_gate + a.r_up));
+  return launch_gated(p, flops, a.T, 2 * a.N, a.K, "gemm_tcgen05_gated", stream);
+}
+
+// dx[T, K] = (add ? dx : 0) + dg . W_gate + low_g . A_gate + du . W_up + low_u . A_up with the two weights read from
+// the interleaved [2 N, K] buffer of gemm_tcgen05_gated (MN-major B: a k-block of 64 weight rows is 64 consecutive
+// rows of the buffer).
+int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t stream) {
+  GemmArgs g;
+  g.M = a.T; g.N = a.K; g.nseg = 4; g.in_dtype = CT_BF16;
+  const void* signal[2] = {a.dg, a.du};
+  const void* low[2] = {a.low_gate, a.low_up};
+  const void* adapter[2] = {a.a_gate, a.a_up};
+  const int64_t rank[2] = {a.r_gate, a.r_up};
+  for (int i = 0; i < 2; ++i) {
+    Segment& base = g.seg[2 * i];
+    base.a = signal[i]; base.a_rs = a.ld_signal; base.a_cs = 1;
+    base.b = a.w_pair; base.b_rs = a.ldw; base.b_cs = 1; base.k = a.N;
+    Segment& lora = g.seg[2 * i + 1];
+    lora.a = low[i]; lora.a_rs = a.ld_low; lora.a_cs = 1;
+    lora.b = adapter[i]; lora.b_rs = a.K; lora.b_cs = 1; lora.k = rank[i];
+  }
+  g.out = a.dx; g.ldo = a.ld_dx; g.out_dtype = CT_BF16; g.beta = a.add; g.bias = nullptr; g.residual = nullptr;
+  g.ld_res = 0; g.split_k = 1;
+  if (a.N % (BN / 2) != 0 || !gemm_tcgen05_supported(g))
+    return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_gated_input_gradient: operands break a TMA rule");
+  TcParams p;
+  const Variant plain{1, false};
+  int rc = fill_params(g, 2, plain, &p);
+  if (rc != CT_OK) return rc;
+  for (int i = 0; i < 2; ++i) {
+    TcSegment& t = p.seg[2 * i];
+    rc = make_map(&t.b, a.w_pair, a.K, 2 * a.N, a.ldw, BK);     // all 2 N rows of the interleaved buffer
+    if (rc != CT_OK) return rc;
+    t.b_k_block = BN / 2;
+    t.b_k_offset = i * (BN / 2);
+  }
+  const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.K) *
+                       (2.0 * static_cast<double>(a.N) + static_cast<double>(a.r_gate + a.r_up));
+  return launch_gated(p, flops, a.T, a.K, 2 * a.N + a.r_gate + a.r_up, "gemm_tcgen05_gated_input_gradient", stream);
 }
 
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {

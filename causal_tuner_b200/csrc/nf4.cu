@@ -38,7 +38,17 @@ struct Nf4Params {
   int vector_ok;  // packed is 4-byte aligned and out 16-byte aligned
   int block_shift;   // log2(blocksize) when it is a power of two, else -1
   int block2_shift;  // the same for blocksize2
+  // Chunked output (chunk > 0): element e is written to out[(e / chunk) * pitch + e % chunk], i.e. runs of
+  // `chunk` elements land `pitch` elements apart - two weights decoded into one buffer of interleaved row blocks.
+  int64_t chunk;
+  int64_t pitch;
 };
+
+__device__ __forceinline__ int64_t place(const Nf4Params& p, int64_t element) {
+  if (p.chunk <= 0) return element;
+  const int64_t run = element / p.chunk;
+  return run * p.pitch + (element - run * p.chunk);
+}
 
 __device__ __forceinline__ int64_t block_of(const Nf4Params& p, int64_t element) {
   return p.block_shift >= 0 ? element >> p.block_shift : element / p.blocksize;
@@ -125,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
         v[2 * b] = round_state<STATE>(__fmul_rn(mine[(byte >> 4) * 32], scale[step]));
         v[2 * b + 1] = round_state<STATE>(__fmul_rn(mine[(byte & 15u) * 32], scale[step]));
       }
-      store_group<OutT>(out + first, v);
+      store_group<OutT>(out + place(p, first), v);
     }
     return;
   }
@@ -145,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
         v[2 * b] = round_state<STATE>(__fmul_rn(mine[(byte >> 4) * 32], scale));
         v[2 * b + 1] = round_state<STATE>(__fmul_rn(mine[(byte & 15u) * 32], scale));
       }
-      store_group<OutT>(out + first, v);
+      store_group<OutT>(out + place(p, first), v);
       continue;
     }
     // Ragged tail, unaligned buffers or block sizes that are not multiples of 8:
@@ -155,8 +165,8 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
       const uint8_t byte = __ldg(p.packed + e / 2);
       const float high = mine[(byte >> 4) * 32], low = mine[(byte & 15) * 32];
       const float scale = block_scale(p, block_of(p, e));
-      out[e] = from_float<OutT>(round_state<STATE>(__fmul_rn(high, scale)));
-      if (e + 1 < p.n) out[e + 1] = from_float<OutT>(round_state<STATE>(__fmul_rn(low, scale)));
+      out[place(p, e)] = from_float<OutT>(round_state<STATE>(__fmul_rn(high, scale)));
+      if (e + 1 < p.n) out[place(p, e + 1)] = from_float<OutT>(round_state<STATE>(__fmul_rn(low, scale)));
     }
   }
 }
@@ -164,11 +174,38 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
 }  // namespace
 }  // namespace ct
 
+namespace ct {
+namespace {
+int decode(const uint8_t* packed, const void* absmax, const float* code, const float* code2, const float* absmax2,
+           const float* offset, void* out, int64_t n, int blocksize, int blocksize2, int nested, int state_dtype,
+           int out_dtype, int64_t chunk, int64_t pitch, void* stream);
+}
+}  // namespace ct
+
 extern "C" int ct_nf4_decode(const uint8_t* packed, const void* absmax, const float* code,
                              const float* code2, const float* absmax2, const float* offset,
                              void* out, int64_t n, int blocksize, int blocksize2, int nested,
                              int state_dtype, int out_dtype, void* stream) {
-  using namespace ct;
+  return ct::decode(packed, absmax, code, code2, absmax2, offset, out, n, blocksize, blocksize2, nested, state_dtype,
+                    out_dtype, 0, 0, stream);
+}
+
+extern "C" int ct_nf4_decode_chunks(const uint8_t* packed, const void* absmax, const float* code,
+                                    const float* code2, const float* absmax2, const float* offset,
+                                    void* out, int64_t n, int blocksize, int blocksize2, int nested,
+                                    int state_dtype, int out_dtype, int64_t chunk, int64_t pitch, void* stream) {
+  if (chunk <= 0 || chunk % 8 != 0 || pitch < chunk || pitch % 8 != 0)
+    return ct::fail(CT_ERR_ARG, "ct_nf4_decode_chunks: chunk=%lld pitch=%lld (multiples of 8, pitch >= chunk)",
+                    (long long)chunk, (long long)pitch);
+  return ct::decode(packed, absmax, code, code2, absmax2, offset, out, n, blocksize, blocksize2, nested, state_dtype,
+                    out_dtype, chunk, pitch, stream);
+}
+
+namespace ct {
+namespace {
+int decode(const uint8_t* packed, const void* absmax, const float* code, const float* code2, const float* absmax2,
+           const float* offset, void* out, int64_t n, int blocksize, int blocksize2, int nested, int state_dtype,
+           int out_dtype, int64_t chunk, int64_t pitch, void* stream) {
   if (n < 0 || blocksize <= 0 || (blocksize & 1)) return fail(CT_ERR_ARG, "ct_nf4_decode: n=%lld blocksize=%d", (long long)n, blocksize);
   if (n == 0) return CT_OK;
   if (!packed || !absmax || !code || !out) return fail(CT_ERR_ARG, "ct_nf4_decode: null pointer");
@@ -184,7 +221,7 @@ extern "C" int ct_nf4_decode(const uint8_t* packed, const void* absmax, const fl
   const int inner2 = blocksize2 > 0 ? blocksize2 : 1;
   Nf4Params p{packed, absmax, code, code2, absmax2, offset, out, n, blocksize, inner2, nested, state_dtype,
               (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
-              log2_of(blocksize), log2_of(inner2)};
+              log2_of(blocksize), log2_of(inner2), chunk, pitch};
   const int64_t per_block = static_cast<int64_t>(kThreads) * kSteps * kGroup;
   const unsigned blocks = static_cast<unsigned>((n + per_block - 1) / per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -203,3 +240,5 @@ extern "C" int ct_nf4_decode(const uint8_t* packed, const void* absmax, const fl
   count_launch(false);
   return check_launch("ct_nf4_decode");
 }
+}  // namespace
+}  // namespace ct

@@ -198,18 +198,46 @@ class _Pending:
             self.done = position
 
 
-def materialize_ahead(pairs, dtype, order=None):
+def materialize_into_pair(weight, state, pair, which):
+    """`materialize(weight, state, pair.dtype)` written into the interleaved buffer `pair` [2 N, K]: rows
+    [128 t, 128 t + 128) of the weight become rows [256 t + 128 * which, ... + 128) (which = 0: gate, 1: up),
+    the layout the gated GEMM of the MLP reads its B operand in."""
+    if state is not None:
+        if weight.is_cuda and weight.dtype == torch.uint8 and weight.is_contiguous() and state.quant_type == "nf4":
+            from .nf4_cuda import dequantize_nf4_blocks
+            return dequantize_nf4_blocks(weight, state, pair, which)
+        raise RuntimeError("only contiguous uint8 NF4 weights on a CUDA device can be decoded")
+    outer, inner = weight.shape
+    pair.view(outer // 128, 2, 128, inner)[:, which].copy_(weight.view(outer // 128, 128, inner))
+    return pair
+
+
+def materialize_ahead(pairs, dtype, order=None, *, interleave=False):
     """`materialize` for several (weight, quant_state) pairs with the NF4 decodes issued on a side
     stream in `order`, so that they run under whatever the caller launches next that does not need the
     dense weights (the low-rank products, which leave the decode most of the HBM bandwidth).
     Returns (matrices, pending); call `pending.wait(i)` before the first launch that reads matrix i.
-    CT_B200_DECODE_AHEAD=0 decodes in stream order instead."""
+    CT_B200_DECODE_AHEAD=0 decodes in stream order instead.
+    interleave=True: pairs 0 and 1 (the gate and up weights of an MLP, equal shapes) share ONE buffer of
+    interleaved 128-row blocks (`materialize_into_pair`); matrices[0] and matrices[1] are that buffer, complete
+    once both have been waited for."""
     order = list(range(len(pairs))) if order is None else list(order)
     device = pairs[0][0].device
-    ahead = (device.type == "cuda" and any(state is not None for _, state in pairs)
+    shared = []
+
+    def produce(index):
+        weight, state = pairs[index]
+        if interleave and index < 2:
+            if not shared:
+                outer, inner = pairs[0][0].shape if pairs[0][1] is None else pairs[0][1].shape
+                shared.append(torch.empty((2 * outer, inner), device=device, dtype=dtype))
+            return materialize_into_pair(weight, state, shared[0], index)
+        return materialize(weight, state, dtype)
+
+    ahead = (device.type == "cuda" and (interleave or any(state is not None for _, state in pairs))
              and os.environ.get("CT_B200_DECODE_AHEAD", "1") != "0")
     if not ahead:
-        return [materialize(weight, state, dtype) for weight, state in pairs], _Pending([], order)
+        return [produce(index) for index in range(len(pairs))], _Pending([], order)
     with torch.cuda.device(device):
         main = torch.cuda.current_stream()
         side = _side_streams.get(device.index)
@@ -219,8 +247,8 @@ def materialize_ahead(pairs, dtype, order=None):
         matrices, events = [None] * len(pairs), []
         with torch.cuda.stream(side):
             for index in order:
-                weight, state = pairs[index]
-                matrices[index] = materialize(weight, state, dtype)
+                weight = pairs[index][0]
+                matrices[index] = produce(index)
                 if matrices[index] is not weight:
                     matrices[index].record_stream(main)   # consumed on `main`: hold the block until that work is done
                 event = torch.cuda.Event()
@@ -316,6 +344,64 @@ def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
             sizes([t.shape[0] for t in weights]), sizes([t.shape[0] for t in a_list]), dx.data_ptr(), _leading(dx),
             pointers(lows), sizes([_leading(t) for t in lows]), rows, inner, int(bool(add)),
             _lib.code_of(dx.dtype), _lib.gemm_path, _lib.stream_of(dx)))
+
+
+def gated_supported(x, width, ranks, dtype):
+    """Whether the MLP's gate / up projections of `x` can run as one gated GEMM (ct_gated_forward): bf16 on the
+    tcgen05 path, widths that are multiples of 128, rows and ranks in multiples of 8 elements."""
+    return (dtype == torch.bfloat16 and x.is_cuda and _lib.gemm_path != _lib.PATH_SIMT and width % 128 == 0
+            and x.shape[-1] % 8 == 0 and all(rank > 0 and rank % 8 == 0 for rank in ranks)
+            and os.environ.get("CT_B200_MLP_FUSED", "1") != "0")
+
+
+def gated_projections(x, pair, xa_gate, xa_up, b_gate, b_up, *, hidden, gate=None, up=None, gradient=None):
+    """gate(x), up(x) and the SwiGLU between them in one launch over the interleaved weights `pair`.
+    Forward (gradient None): hidden = silu(gate) * up; `gate` / `up`, when given, receive the two projections.
+    Backward: `gradient` is d(hidden); (gate, up, hidden) receive (d_gate, d_up, hidden) - the in-place backward
+    of `activation` without gate and up ever being stored. hidden may be the gradient's buffer."""
+    _lib.require_cuda(x, pair, xa_gate, xa_up, b_gate, b_up, hidden, gate, up, gradient)
+    x, xa_gate, xa_up = _readable(x), _readable(xa_gate), _readable(xa_up)
+    b_gate, b_up = b_gate.contiguous(), b_up.contiguous()
+    rows, inner = x.shape
+    width = pair.shape[0] // 2
+    outputs = [t for t in (hidden, gate, up, gradient) if t is not None]
+    for tensor in outputs:
+        if tensor.shape != (rows, width) or tensor.stride(1) != 1 or tensor.stride(0) != outputs[0].stride(0):
+            raise ValueError("gated projections: hidden, gate, up and gradient must be [rows, width] with one leading dimension")
+    if _leading(xa_gate) != _leading(xa_up):
+        raise ValueError("gated projections: the two low-rank inputs must share a leading dimension")
+    library = _lib.load()
+    common = (x.data_ptr(), _leading(x), pair.data_ptr(), _leading(pair), xa_gate.data_ptr(), xa_up.data_ptr(),
+              _leading(xa_gate), b_gate.data_ptr(), b_up.data_ptr())
+    sizes = (_leading(hidden), rows, inner, width, b_gate.shape[1], b_up.shape[1], _lib.code_of(x.dtype),
+             _lib.stream_of(x))
+    with _lib.on_device(x):
+        if gradient is None:
+            _lib.check(library.ct_gated_forward(*common, hidden.data_ptr(), _lib.pointer(gate), _lib.pointer(up), *sizes))
+        else:
+            _lib.check(library.ct_gated_backward(*common, gradient.data_ptr(), hidden.data_ptr(), gate.data_ptr(),
+                                                 up.data_ptr(), *sizes))
+    return hidden
+
+
+def gated_input_gradient(d_gate, d_up, pair, a_gate, a_up, b_gate, b_up, dx, lows, *, add=False):
+    """`input_gradient_group` for the gate and up projections with their base weights read from the interleaved
+    buffer `pair`: low_i = d_i @ b_i, dx = (add ? dx : 0) + sum_i (d_i @ weight_i + low_i @ a_i)."""
+    _lib.require_cuda(d_gate, d_up, pair, dx, *lows)
+    d_gate, d_up = _readable(d_gate), _readable(d_up)
+    a_gate, a_up = a_gate.contiguous(), a_up.contiguous()
+    _writable(dx, "dx")
+    matmul(d_gate, b_gate, out=lows[0])
+    matmul(d_up, b_up, out=lows[1])
+    if _leading(d_gate) != _leading(d_up) or _leading(lows[0]) != _leading(lows[1]):
+        raise ValueError("gated input gradient: the two signals (and the two low-rank gradients) must share a leading dimension")
+    rows, inner = d_gate.shape[0], pair.shape[1]
+    with _lib.on_device(dx):
+        _lib.check(_lib.load().ct_gated_input_gradient(
+            d_gate.data_ptr(), d_up.data_ptr(), _leading(d_gate), pair.data_ptr(), _leading(pair), lows[0].data_ptr(),
+            lows[1].data_ptr(), _leading(lows[0]), a_gate.data_ptr(), a_up.data_ptr(), dx.data_ptr(), _leading(dx),
+            rows, inner, pair.shape[0] // 2, a_gate.shape[0], a_up.shape[0], int(bool(add)),
+            _lib.code_of(dx.dtype), _lib.stream_of(dx)))
 
 
 def stack_adapters(matrices, dtype, others=()):

@@ -10,9 +10,10 @@ and its in-place backward are ct_swiglu.
 import torch
 
 from .. import _lib
-from .linear import (_policy, apply_projection, cast, materialize, materialize_ahead, forward_linear, input_gradient,
-                     input_gradient_with, input_gradient_group, parameter_gradients, projection_parameters, matmul,
-                     stack_adapters, token_gradient, token_gradients)
+from .linear import (_policy, apply_projection, cast, gated_input_gradient, gated_projections, gated_supported,
+                     materialize, materialize_ahead, forward_linear, input_gradient, input_gradient_with,
+                     input_gradient_group, parameter_gradients, projection_parameters, matmul, stack_adapters,
+                     token_gradient, token_gradients)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -65,12 +66,27 @@ def silu_multiply(gate, up):
     return _SiLUMultiply.apply(gate, up)
 
 
-def _prepare(parameters, states, dtype, order=(0, 1, 2), casts=None):
+def _gated(x, parameters, states, dtype):
+    """Whether gate(x), up(x) and the SwiGLU run as ONE tcgen05 launch (`gated_projections`): the two base
+    weights are then decoded into one buffer of interleaved 128-row blocks, a GEMM tile accumulates the same 128
+    columns of both projections, and the activation (forward, or its in-place backward on recomputed tiles) is
+    the tile's epilogue - gate and up never travel through memory unless the caller keeps them."""
+    if (states[0] is None) != (states[1] is None) or parameters[0].device.type != "cuda":
+        return False
+    shapes = [parameters[4 * i].shape if states[i] is None else tuple(states[i].shape) for i in range(2)]
+    if len(shapes[0]) != 2 or shapes[0] != shapes[1]:
+        return False
+    return gated_supported(x, shapes[0][0], [parameters[1].shape[0], parameters[5].shape[0]], dtype)
+
+
+def _prepare(parameters, states, dtype, order=(0, 1, 2), casts=None, gated=False):
     """Base weights decoding on the side stream in `order` (wait on the returned handle before a
     matrix is read), cast adapters, and the gate/up `a` matrices stacked row-wise (their low-rank
     inputs come from one product over x). `casts` = (stacked, b_gate, b_up, a_down, b_down) already in
-    `dtype` (kept by the forward pass) skips the conversion."""
-    matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order)
+    `dtype` (kept by the forward pass) skips the conversion. gated=True: matrices[0] and matrices[1] are one
+    buffer holding both weights in interleaved 128-row blocks (complete after pending.wait(0) and wait(1))."""
+    matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order,
+                                          interleave=gated)
     ranks = [parameters[1].shape[0], parameters[5].shape[0]]
     if casts is not None:
         stacked, others, offsets = casts[0], list(casts[1:]), [0, ranks[0]]
@@ -91,12 +107,13 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
     """
     flat = cast(x.reshape(-1, x.shape[-1]), dtype)
     rows = flat.shape[0]
-    matrices, adapters, stacked, pending = _prepare(parameters, states, dtype)
-    width = matrices[0].shape[0]
+    gated = rows > 0 and _gated(flat, parameters, states, dtype)
+    matrices, adapters, stacked, pending = _prepare(parameters, states, dtype, gated=gated)
+    width = matrices[2].shape[1]
     ranks = [a.shape[0] for a, _ in adapters]
     step = max(1, min(tile, rows))
     held = min(step, rows)
-    workspace = torch.empty((1 if save else 2, held, width), device=x.device, dtype=dtype)
+    workspace = torch.empty((1 if save or gated else 2, held, width), device=x.device, dtype=dtype)
     low = torch.empty((held, stacked.shape[0]), device=x.device, dtype=dtype)
     low_down = torch.empty((held, ranks[2]), device=x.device, dtype=dtype)
     saved = ()
@@ -118,14 +135,20 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
             gate, up = saved[0][start:stop], saved[1][start:stop]
             both = kept[start:stop]
         else:
-            gate, up = workspace[0, :count], workspace[1, :count]
+            gate, up = (None, None) if gated else (workspace[0, :count], workspace[1, :count])
             both = low[:count]
         matmul(part, stacked.T, out=both)           # low-rank inputs of gate and up, reading x once
         pending.wait(0)
-        apply_projection(part, matrices[0], adapters[0][1], both[:, :ranks[0]], out=gate)
-        pending.wait(1)
-        apply_projection(part, matrices[1], adapters[1][1], both[:, ranks[0]:], out=up)
-        hidden = activation(gate, up, out=workspace[0, :count] if save else gate)
+        if gated:
+            pending.wait(1)
+            hidden = gated_projections(part, matrices[0], both[:, :ranks[0]], both[:, ranks[0]:], adapters[0][1],
+                                       adapters[1][1], hidden=workspace[0, :count], gate=gate if save else None,
+                                       up=up if save else None)
+        else:
+            apply_projection(part, matrices[0], adapters[0][1], both[:, :ranks[0]], out=gate)
+            pending.wait(1)
+            apply_projection(part, matrices[1], adapters[1][1], both[:, ranks[0]:], out=up)
+            hidden = activation(gate, up, out=workspace[0, :count] if save else gate)
         pending.wait(2)
         forward_linear(hidden, matrices[2], *adapters[2], out=destination[start:stop],
                        xa=saved[4][start:stop] if len(saved) > 4 else low_down[:count],
@@ -165,9 +188,10 @@ class _TiledLoRAMLP(torch.autograd.Function):
         want_dx = ctx.needs_input_grad[0]
         dx = torch.empty_like(flat) if want_dx else None
         # Cached: the down projection's weight is needed first, gate/up only for the input gradient.
+        gated = rows > 0 and _gated(flat, parameters, ctx.states, dtype)
         matrices, adapters, stacked, pending = _prepare(parameters, ctx.states, dtype,
-                                                        (2, 0, 1) if ctx.cache else (0, 1, 2),
-                                                        casts=saved[5:10] if len(saved) >= 10 else None)
+                                                        (2, 0, 1) if ctx.cache or gated else (0, 1, 2),
+                                                        casts=saved[5:10] if len(saved) >= 10 else None, gated=gated)
         ranks = [a.shape[0] for a, _ in adapters]
         make = torch.empty if rows else torch.zeros
         wide = dict(device=x.device, dtype=torch.float32)
@@ -177,7 +201,7 @@ class _TiledLoRAMLP(torch.autograd.Function):
         db = [make(parameters[4 * i + 2].shape, **wide) for i in range(3)]
         step = max(1, min(ctx.tile, rows))
         held = min(step, rows)
-        width = matrices[0].shape[0]
+        width = matrices[2].shape[1]
         workspace = torch.empty((3, held, width), device=x.device, dtype=dtype)
         xa_both = torch.empty((held, stacked.shape[0]), device=x.device, dtype=dtype)
         xa_down = torch.empty((held, ranks[2]), device=x.device, dtype=dtype)
@@ -194,10 +218,11 @@ class _TiledLoRAMLP(torch.autograd.Function):
             else:
                 matmul(part, stacked.T, out=xa_both[:count])
                 xa = [xa_both[:count, :ranks[0]], xa_both[:count, ranks[0]:]]
-                pending.wait(0)
-                apply_projection(part, matrices[0], adapters[0][1], xa[0], out=gate)
-                pending.wait(1)
-                apply_projection(part, matrices[1], adapters[1][1], xa[1], out=up)
+                if not gated:
+                    pending.wait(0)
+                    apply_projection(part, matrices[0], adapters[0][1], xa[0], out=gate)
+                    pending.wait(1)
+                    apply_projection(part, matrices[1], adapters[1][1], xa[1], out=up)
             matmul(dy, adapters[2][1], out=low[2])      # needs no base weight: runs beside the decodes
             pending.wait(2)
             input_gradient_with(dy, matrices[2], adapters[2][0], low[2], dh)
@@ -206,6 +231,13 @@ class _TiledLoRAMLP(torch.autograd.Function):
                 # tensors stay untouched and survive a repeated backward pass, without a copy.
                 _swiglu(saved[0][start:stop], saved[1][start:stop], dh, dh, gate, up, True)
                 hidden = dh
+            elif gated:
+                # gate and up are recomputed tile by tile in the GEMM's accumulator and leave it as (d_gate, d_up,
+                # hidden): the activations themselves are never written
+                pending.wait(0)
+                pending.wait(1)
+                hidden = gated_projections(part, matrices[0], xa[0], xa[1], adapters[0][1], adapters[1][1],
+                                           hidden=dh, gate=gate, up=up, gradient=dh)
             else:
                 hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
             if len(saved) > 4:
@@ -215,8 +247,12 @@ class _TiledLoRAMLP(torch.autograd.Function):
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
                 pending.wait()
-                input_gradient_group((gate, up), matrices[:2], [adapters[0][0], adapters[1][0]],
-                                     [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
+                if gated:
+                    gated_input_gradient(gate, up, matrices[0], adapters[0][0], adapters[1][0], adapters[0][1],
+                                         adapters[1][1], dx[start:stop], low[:2])
+                else:
+                    input_gradient_group((gate, up), matrices[:2], [adapters[0][0], adapters[1][0]],
+                                         [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
             else:
                 for index, signal in enumerate((gate, up)):
                     matmul(signal, adapters[index][1], out=low[index])

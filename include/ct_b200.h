@@ -94,6 +94,15 @@ CT_API int ct_nf4_decode(const uint8_t* packed, const void* absmax, const float*
                   void* out, int64_t n, int blocksize, int blocksize2, int nested,
                   int state_dtype, int out_dtype, void* stream);
 
+/* The same decode with the output written in runs: element e goes to out[(e / chunk) * pitch + e % chunk].
+ * With chunk = 128 * K and pitch = 256 * K two [N, K] weights decode into one [2 N, K] buffer of interleaved
+ * 128-row blocks (the second with `out` advanced by 128 * K elements): the B operand of ct_gated_forward.
+ * `chunk` and `pitch` are multiples of 8 elements, pitch >= chunk. */
+CT_API int ct_nf4_decode_chunks(const uint8_t* packed, const void* absmax, const float* code,
+                  const float* code2, const float* absmax2, const float* offset,
+                  void* out, int64_t n, int blocksize, int blocksize2, int nested,
+                  int state_dtype, int out_dtype, int64_t chunk, int64_t pitch, void* stream);
+
 /* ---- NF4 encode ---------------------------------------------------------
  * Replaces the bitsandbytes quantiser the reference calls when it installs a frozen base
  * weight (modeling/lora.py:41-56, `Params4bit(..., quant_type="nf4", compress_statistics=True)`).
@@ -291,6 +300,41 @@ CT_API int ct_parameter_gradients_noalloc(const void* x, int64_t ldx, const void
  * element for element (the in-place use of kernels/mlp_cuda.py:133). */
 CT_API int ct_swiglu(const void* gate, const void* up, const void* grad, void* out, void* dg,
               void* du, int64_t n, int dtype, int reconstruct, void* stream);
+
+/* ---- gate / up projections with the SwiGLU inside the GEMM ---------------------------------
+ * Replaces, in one launch each, the gate and up projections plus the activation between them and the down
+ * projection: kernels/mlp_cuda.py:69-73 (forward: two forward_linear calls, then `activation`) and
+ * kernels/mlp_cuda.py:118-133 (backward without cached activations: the same two projections recomputed,
+ * then `activation(gate, up, hidden_grad)` in place).
+ * `w_pair` [2 N, K] holds both base weights, interleaved in 128-row blocks: rows [256 t, 256 t + 128) are
+ * rows [128 t, 128 t + 128) of the gate weight, the next 128 rows the same rows of the up weight
+ * (ct_nf4_decode_chunks writes that layout). A tile of the tcgen05 kernel then accumulates 128 columns of
+ * gate(x) and the same 128 columns of up(x) side by side - base product over `w_pair`, the two low-rank terms
+ * xa_gate @ b_gate^T and xa_up @ b_up^T by MMAs of half the width into their half of the accumulator - and
+ * the epilogue rounds both to bf16 as stored projection outputs would be and applies ct_swiglu's arithmetic:
+ *   ct_gated_forward:  h = round(silu(gate)) * up; `gate` / `up` (NULL allowed) receive the two projections
+ *                      for callers that keep them for the backward pass.
+ *   ct_gated_backward: with `dh` = gradient of h: (d_gate, d_up, h) as ct_swiglu's in-place backward, written
+ *                      to (`d_gate`, `d_up`, `h`); gate and up exist in the accumulator only. `h` may be `dh`.
+ * Results are bit-identical to ct_forward_linear x 2 + ct_swiglu. xa_* are [T, r_*] with leading dimension
+ * ld_xa, b_* are [N, r_*] contiguous, h / gate / up / dh are [T, N] with leading dimension ld_out. bf16 only,
+ * N a multiple of 128, rows 16-byte aligned; anything else returns CT_ERR_UNSUPPORTED (nothing launched).
+ * ct_gated_input_gradient: dx[T, K] = (add ? dx : 0) + d_gate @ W_gate + low_gate @ a_gate + d_up @ W_up +
+ *   low_up @ a_up with the two base weights read from `w_pair` (kernels/mlp_cuda.py:136-138 in one GEMM);
+ *   low_* = d_* @ b_* are inputs. */
+CT_API int ct_gated_forward(const void* x, int64_t ldx, const void* w_pair, int64_t ldw, const void* xa_gate,
+                            const void* xa_up, int64_t ld_xa, const void* b_gate, const void* b_up, void* h,
+                            void* gate, void* up, int64_t ld_out, int64_t T, int64_t K, int64_t N,
+                            int64_t r_gate, int64_t r_up, int dtype, void* stream);
+CT_API int ct_gated_backward(const void* x, int64_t ldx, const void* w_pair, int64_t ldw, const void* xa_gate,
+                             const void* xa_up, int64_t ld_xa, const void* b_gate, const void* b_up,
+                             const void* dh, void* h, void* d_gate, void* d_up, int64_t ld_out, int64_t T,
+                             int64_t K, int64_t N, int64_t r_gate, int64_t r_up, int dtype, void* stream);
+CT_API int ct_gated_input_gradient(const void* d_gate, const void* d_up, int64_t ld_signal, const void* w_pair,
+                                   int64_t ldw, const void* low_gate, const void* low_up, int64_t ld_low,
+                                   const void* a_gate, const void* a_up, void* dx, int64_t ld_dx, int64_t T,
+                                   int64_t K, int64_t N, int64_t r_gate, int64_t r_up, int add, int dtype,
+                                   void* stream);
 
 /* ---- adjacent-pair partial RoPE ---------------------------------------------
  * Replaces kernels/core_cuda.py:146-164 (_rope: forward, or inverse into a

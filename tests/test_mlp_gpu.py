@@ -349,3 +349,119 @@ def test_keeping_low_rank_inputs_changes_what_is_retained_not_a_value():
     # plus the down projection's [rows, rank] low-rank input and the six adapters in the compute dtype (bf16)
     adapters = sum(p.numel() for name, p in module.named_parameters() if "lora_" in name)
     assert results[1][2] == module.cache_bytes(14) + 14 * 8 * 2 + adapters * 2
+
+
+# ---- gate / up projections with the SwiGLU in the GEMM's epilogue ---------------------------------
+
+class MidConfig:
+    hidden_size, intermediate_size = 512, 384
+
+
+def _mid_module(nf4, nested=False, ranks=(16, 24, 8)):
+    module = MLP(MidConfig, Runtime(rank=16), "cuda")
+    for name, rank in zip(("gate_proj", "up_proj", "down_proj"), ranks):
+        original = getattr(module, name)
+        setattr(module, name, Projection(original.weight.shape[1], original.weight.shape[0], rank=rank, device="cuda"))
+    for projection in (module.gate_proj, module.up_proj, module.down_proj):
+        if nf4:
+            projection.install_nf4(projection.weight.detach().clone(), "cuda", nested=nested)
+        torch.nn.init.normal_(projection.lora_B, std=.05)
+    return module
+
+
+@pytest.mark.parametrize("nested", [False, True])
+def test_interleaved_decode_places_both_weights_in_128_row_blocks(nested):
+    from causal_tuner_b200.kernels.linear import materialize, materialize_into_pair
+    module = _mid_module(True, nested)
+    (gate_weight, *_), gate_state = mlp_cuda.projection_parameters(module.gate_proj)
+    (up_weight, *_), up_state = mlp_cuda.projection_parameters(module.up_proj)
+    pair = torch.full((2 * 384, 512), float("nan"), device="cuda", dtype=torch.bfloat16)
+    materialize_into_pair(gate_weight, gate_state, pair, 0)
+    materialize_into_pair(up_weight, up_state, pair, 1)
+    blocks = pair.view(3, 2, 128, 512)
+    assert torch.equal(blocks[:, 0].reshape(384, 512), materialize(gate_weight, gate_state, torch.bfloat16))
+    assert torch.equal(blocks[:, 1].reshape(384, 512), materialize(up_weight, up_state, torch.bfloat16))
+    dense = torch.randn(384, 512, device="cuda")
+    materialize_into_pair(dense, None, pair, 1)
+    assert torch.equal(blocks[:, 1].reshape(384, 512), dense.bfloat16())
+
+
+@pytest.mark.parametrize("rows", [1000, 256, 77])
+def test_gated_launch_is_bit_identical_to_two_projections_and_the_activation(rows):
+    """ct_gated_forward / ct_gated_backward / ct_gated_input_gradient against ct_forward_linear x 2 + ct_swiglu
+    and ct_input_gradient_group on the same operands: every output equal bit for bit, buffers the launch must
+    not touch untouched, the in-place form (hidden over its own gradient) included."""
+    from causal_tuner_b200.kernels import linear
+    torch.manual_seed(rows)
+    inner, width, ranks = 512, 384, (16, 24)
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(rows, inner, **bf)
+    weights = [torch.randn(width, inner, **bf) * .05 for _ in range(2)]
+    a = [torch.randn(rank, inner, **bf) * .05 for rank in ranks]
+    b = [torch.randn(width, rank, **bf) * .2 for rank in ranks]
+    both = torch.empty(rows, sum(ranks), **bf)
+    linear.matmul(x, torch.cat(a).T, out=both)
+    xa = [both[:, :ranks[0]], both[:, ranks[0]:]]
+    pair = torch.empty(2 * width, inner, **bf)
+    for which in range(2):
+        linear.materialize_into_pair(weights[which], None, pair, which)
+    gate, up = torch.empty(rows, width, **bf), torch.empty(rows, width, **bf)
+    for which, out in enumerate((gate, up)):
+        linear.apply_projection(x, weights[which], b[which], xa[which], out=out)
+    hidden = mlp_cuda.activation(gate, up)
+    before = _lib.tcgen05_launch_count()
+    fused = [torch.full((rows + 1, width), 7.0, **bf) for _ in range(3)]        # one guard row each
+    linear.gated_projections(x, pair, xa[0], xa[1], b[0], b[1], hidden=fused[0][:rows], gate=fused[1][:rows],
+                             up=fused[2][:rows])
+    assert _lib.tcgen05_launch_count() == before + 1
+    for actual, expected in zip(fused, (hidden, gate, up)):
+        assert torch.equal(actual[:rows], expected)
+        assert (actual[rows] == 7).all()
+    alone = torch.empty(rows, width, **bf)
+    linear.gated_projections(x, pair, xa[0], xa[1], b[0], b[1], hidden=alone)
+    assert torch.equal(alone, hidden)
+    # backward: (gate, up, d_hidden) -> (d_gate, d_up, hidden) in place, against recomputed accumulators
+    upstream = torch.randn(rows, width, **bf)
+    expected = [gate.clone(), up.clone(), upstream.clone()]
+    mlp_cuda.activation(*expected)
+    buffers = [torch.empty(rows, width, **bf) for _ in range(2)]
+    in_place = upstream.clone()
+    linear.gated_projections(x, pair, xa[0], xa[1], b[0], b[1], hidden=in_place, gate=buffers[0], up=buffers[1],
+                             gradient=in_place)
+    for actual, wanted in zip((*buffers, in_place), expected):
+        assert torch.equal(actual, wanted)
+    # input gradient through the interleaved weights
+    lows = [torch.empty(rows, sum(ranks), **bf) for _ in range(2)]
+    split = lambda t: [t[:, :ranks[0]], t[:, ranks[0]:]]
+    dx = [torch.full((rows, inner), float("nan"), **bf) for _ in range(2)]
+    linear.input_gradient_group(expected[:2], weights, a, b, dx[0], split(lows[0]))
+    linear.gated_input_gradient(expected[0], expected[1], pair, a[0], a[1], b[0], b[1], dx[1], split(lows[1]))
+    assert torch.equal(dx[0], dx[1]) and torch.equal(lows[0], lows[1])
+    linear.input_gradient_group(expected[:2], weights, a, b, dx[0], split(lows[0]), add=True)
+    linear.gated_input_gradient(expected[0], expected[1], pair, a[0], a[1], b[0], b[1], dx[1], split(lows[1]), add=True)
+    assert torch.equal(dx[0], dx[1])
+
+
+@pytest.mark.parametrize("nf4", [False, True])
+@pytest.mark.parametrize("cache", [False, True])
+@pytest.mark.parametrize("tile", [0, 300])
+def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4, cache, tile):
+    """The whole operator with and without the gated launch (CT_B200_MLP_FUSED=0 turns it off): output and every
+    gradient equal bit for bit, with cached activations and with recompute, whole and in row tiles."""
+    torch.manual_seed(5)
+    module = _mid_module(nf4)
+    module.tile = tile
+    x = torch.randn(3, 333, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    signal = torch.randn_like(x)
+    params = (x, *trainable(module))
+    results = {}
+    for fused in ("0", "1"):
+        monkeypatch.setenv("CT_B200_MLP_FUSED", fused)
+        before = _lib.launch_count()
+        y = module(x, residual=x, cache=cache)
+        grads = torch.autograd.grad(y, params, signal)
+        results[fused] = (y, *grads, _lib.launch_count() - before)
+    assert results["1"][-1] < results["0"][-1]           # fewer launches: the path was taken
+    for separate, gated in zip(results["0"][:-1], results["1"][:-1]):
+        assert torch.isfinite(gated).all()
+        assert torch.equal(separate, gated)
