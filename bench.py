@@ -823,7 +823,7 @@ def run_step(args):
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel / gemm_tcgen05_pair_kernel",
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_{pair,wide,gated,group}_kernel (one body, gemm_tc.cu)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
                      "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
                      "launches": kernel_launches, "kernel_ms_per_step": kernel_ms / args.steps,

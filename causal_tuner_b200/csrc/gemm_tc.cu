@@ -343,6 +343,23 @@ __device__ __forceinline__ void tmem_load_wait(uint32_t (&r)[32]) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_load_16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait(uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+      :
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -534,6 +551,50 @@ __device__ __forceinline__ void stage_chunk(const TcParams& p, float (&v)[COLS],
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(v[8 * q], v[8 * q + 1])),
                  "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])), "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
                  "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7]))
+                 : "memory");
+  }
+}
+
+// The same for 32 columns that were rounded to bf16 when the accumulator was drained (16 packed pairs): only the
+// residual is left to add (round(value) + residual, rounded again - the arithmetic of stage_chunk).
+__device__ __forceinline__ void stage_packed(const TcParams& p, const uint32_t* words, uint32_t tile, int lane,
+                                             int64_t row, int64_t col0) {
+  uint32_t w[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) w[j] = words[j];
+  if (p.residual && row < p.M) {
+    const bool full = col0 + 32 <= p.N;
+    const __nv_bfloat16* res = p.residual + row * p.ld_res + col0;
+    if (full && p.vec_store) {
+      const uint4* r4 = reinterpret_cast<const uint4*>(res);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 o = __ldg(r4 + q);
+        const uint32_t r[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r[j]));
+          const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[4 * q + j]));
+          w[4 * q + j] = pack_bf16(__fadd_rn(v.x, f.x), __fadd_rn(v.y, f.y));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+        const float lo = col0 + 2 * j < p.N ? __fadd_rn(v.x, __bfloat162float(res[2 * j])) : v.x;
+        const float hi = col0 + 2 * j + 1 < p.N ? __fadd_rn(v.y, __bfloat162float(res[2 * j + 1])) : v.y;
+        w[j] = pack_bf16(lo, hi);
+      }
+    }
+  }
+  const uint32_t row_base = tile + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t twist = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t dst = row_base + ((static_cast<uint32_t>(q) ^ twist) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                 "r"(w[4 * q + 2]), "r"(w[4 * q + 3])
                  : "memory");
   }
 }
@@ -929,6 +990,7 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MH == 2 ? half : acc) * BN;
+      bool released = false;   // the accumulator has already been handed back to the MMA warp
       if (GATED && p.gated) {
         if constexpr (GATED) {
           // Accumulator columns [0, 128) are the gate projection, [128, 256) the up projection of the same 128
@@ -1014,24 +1076,42 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
             ++stored;
           }
         } else {
-          // Not overlapped with a main loop, so kept short: 32-column chunks, two 2 KB staging tiles per warp, and
-          // the TMEM load of the next chunk in flight while this one is converted, staged and handed to the store.
-          constexpr int CHUNKS = BN / 32;
-          uint32_t raw[2][32];
-          tmem_load_32_issue(taddr, raw[0]);
+          // Not overlapped with a main loop, so the accumulator is handed back as early as possible: the row's 256
+          // columns are read (16 at a time, the next load in flight), given their bias, rounded to bf16 and kept
+          // in 128 registers; the accumulator is released to the MMA warp; only then do residual, staging and
+          // tensor-map stores run - under the next tile's main loop.
+          constexpr int PIECES = BN / 16;
+          uint32_t kept[BN / 2];
+          uint32_t raw[2][16];
+          tmem_load_16_issue(taddr, raw[0]);
 #pragma unroll
-          for (int c = 0; c < CHUNKS; ++c) {
-            const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
+          for (int c = 0; c < PIECES; ++c) {
             tmem_load_wait(raw[c & 1]);
-            if (c + 1 < CHUNKS) tmem_load_32_issue(taddr + (c + 1) * 32, raw[(c + 1) & 1]);
+            if (c + 1 < PIECES) tmem_load_16_issue(taddr + (c + 1) * 16, raw[(c + 1) & 1]);
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
+            if (p.bias) {
+              const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 16;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + col0 + j));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) kept[c * 8 + j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+          }
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
+          released = true;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            const int64_t col0 = static_cast<int64_t>(tc.n) * BN + c * 32;
             if (col0 < p.N) {  // uniform across the warp
               if (lane == 0) bulk_wait_read<1>();
               __syncwarp();
-              float v[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
               const uint32_t tile_smem = stage_tile0 + static_cast<uint32_t>(stored & 1) * (STORE_TILE_BYTES / 2);
-              stage_chunk<32>(p, v, tile_smem, lane, row, col0);
+              stage_packed(p, kept + c * 16, tile_smem, lane, row, col0);
               fence_async_shared();
               __syncwarp();
               if (lane == 0 && row0 < p.M) {
@@ -1059,11 +1139,13 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           store_chunk(p, v, out_plane, row, col0);
         }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CTAS == 1) mbar_arrive(tmem_empty_bar(acc));
-        else mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
+      if (!released) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 1) mbar_arrive(tmem_empty_bar(acc));
+          else mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
+        }
       }
     }
     // Shared memory must stay valid until the stores have read it, and the stores must be complete before the
@@ -1113,6 +1195,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::k
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 3, 2, 1>::kThreads, 1)
     gemm_tcgen05_gated_kernel(const __grid_constant__ TcParams p) {
   gemm_body<2, 3, 2, 1, TcParams, false, true>(p);
+}
+
+// The wide kernel with the gated kernel's operand handling (interleaved weight buffers); plain epilogue.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Shape<2, 4, 1, 2>::kThreads, 1)
+    gemm_tcgen05_gated_wide_kernel(const __grid_constant__ TcParams p) {
+  gemm_body<2, 4, 1, 2, TcParams, false, true>(p);
 }
 
 // The 512 x 256 tile: two row halves per CTA, four ring stages of one 48 KB k-block, two epilogue warp sets.
@@ -1319,12 +1407,14 @@ int launch_single(const TcParams& p, unsigned grid, int device, cudaStream_t str
 
 // Row halves per CTA and the kind of epilogue, chosen from same-device comparisons of the four combinations on
 // the shapes of a training step (CT_B200_GEMM_MH = 1 / 2 and CT_B200_GEMM_TMA_STORE = 0 / 1 pin them):
-//  * the 512 x 256 tile halves the B tiles staged per FLOP and doubles the work buffered per ring stage. It pays
-//    where B arrives as MN-major 64 x 64 boxes and the contraction is short (the input-gradient products
-//    dy . W with K of a few thousand: 6 to 9 % faster); with K-major B or a long contraction the two tiles are
-//    within run-to-run noise of each other and the 256 x 256 tile with its overlapped epilogue is kept. The
-//    wide tile's epilogue is not overlapped, so it is only used with the tensor-map store, for outputs of at
-//    least 1024 columns (enough tiles to fill the machine) and 512 rows;
+//  * the 512 x 256 tile stages a quarter fewer bytes per FLOP (47 instead of 64 bytes per SM and cycle, the latter
+//    being about what an SM can take from L2) and doubles the work buffered per ring stage. Its accumulator
+//    fills the whole TMEM, so its epilogue cannot run under the next main loop; since that epilogue drains the
+//    accumulator into registers first and hands it back before it stores anything, the exposed part is about a
+//    microsecond per tile and the wide tile is ahead on every large product (2 to 4 % on K-major B, 6 to 9 % on
+//    MN-major B; 14 ms of a 600 ms training step against the 256 x 256 tile everywhere). It needs the
+//    tensor-map store (a bf16 result written once), at least 1024 columns (enough tiles to fill the machine)
+//    and rows that fill 512-row tiles (a multiple of 512, or so many that the padding is below 7 %);
 //  * a product whose tiles fit in one wave (the skinny low-rank products) has no next tile to hide its
 //    epilogue behind either: the tensor-map store is 4 to 9 % ahead there;
 //  * where the epilogue runs under the next tile's main loop the register store is kept (the staged store
@@ -1334,20 +1424,18 @@ struct Variant {
   bool tma_store;
 };
 
+bool wide_tile_fits(int64_t M, int64_t N) {
+  const bool rows_fill = M % (4 * BM) == 0 || M >= 15 * 4 * BM;
+  return M >= 4 * BM && N >= 4 * BN && rows_fill;
+}
+
 Variant variant_for(const GemmArgs& g, int ctas, bool store_ok) {
   const int pinned_halves = env_int("CT_B200_GEMM_MH", 0);
   const int pinned_store = env_int("CT_B200_GEMM_TMA_STORE", -1);
-  bool b_mn = false;
-  int64_t k_total = 0, k_mn = 0;
-  for (int s = 0; s < g.nseg; ++s) {
-    k_total += g.seg[s].k;
-    if (g.seg[s].b_rs != 1) k_mn += g.seg[s].k;
-  }
-  b_mn = 2 * k_mn > k_total;
   const int64_t pair_tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   Variant v;
   v.halves = 1;
-  if (ctas == 2 && store_ok && g.M >= 4 * BM && g.N >= 4 * BN && b_mn && k_total < 8192) v.halves = 2;
+  if (ctas == 2 && store_ok && wide_tile_fits(g.M, g.N)) v.halves = 2;
   if (ctas == 2 && (pinned_halves == 1 || pinned_halves == 2)) v.halves = pinned_halves;
   v.tma_store = store_ok && (v.halves == 2 || pair_tiles <= 74);
   if (pinned_store == 0) v.tma_store = false;
@@ -1551,7 +1639,7 @@ int gemm_tcgen05_nf4(const void* x, int64_t ldx, const uint8_t* packed, const fl
 
 namespace {
 
-int launch_gated(const TcParams& p, double flops, int64_t M, int64_t N, int64_t K, const char* what,
+int launch_gated(const TcParams& p, bool wide, double flops, int64_t M, int64_t N, int64_t K, const char* what,
                  cudaStream_t stream) {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
@@ -1560,13 +1648,16 @@ int launch_gated(const TcParams& p, double flops, int64_t M, int64_t N, int64_t 
   if (sms <= 0) return fail(CT_ERR_CUDA, "%s: cannot read the SM count", what);
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles, slots = sms / 2;
   const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * 2);
-  static bool configured[64] = {};
+  static bool configured[2][64] = {};
   using S = Shape<2, 3, 2, 1>;
-  const int rc = configure(gemm_tcgen05_gated_kernel, S::kSmemBytes, &configured[device]);
+  using W = Shape<2, 4, 1, 2>;
+  const int rc = wide ? configure(gemm_tcgen05_gated_wide_kernel, W::kSmemBytes, &configured[1][device])
+                      : configure(gemm_tcgen05_gated_kernel, S::kSmemBytes, &configured[0][device]);
   if (rc != CT_OK) return rc;
   const bool timed = timing_enabled();
   if (timed) timing_begin(stream);
-  launch_dependent(gemm_tcgen05_gated_kernel, dim3(grid), dim3(S::kThreads), S::kSmemBytes, stream, p);
+  if (wide) launch_dependent(gemm_tcgen05_gated_wide_kernel, dim3(grid), dim3(W::kThreads), W::kSmemBytes, stream, p);
+  else launch_dependent(gemm_tcgen05_gated_kernel, dim3(grid), dim3(S::kThreads), S::kSmemBytes, stream, p);
   if (timed) timing_end(stream, flops, M, N, K);
   count_launch(true);
   return check_launch(what);
@@ -1627,7 +1718,7 @@ int gemm_tcgen05_gated(const GatedArgs& a, cudaStream_t stream) {
   p.gated_ld = a.ld_out;
   const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.N) *
                        (2.0 * static_cast<double>(a.K) + static_cast<double>(a.r_gate + a.r_up));
-  return launch_gated(p, flops, a.T, 2 * a.N, a.K, "gemm_tcgen05_gated", stream);
+  return launch_gated(p, false, flops, a.T, 2 * a.N, a.K, "gemm_tcgen05_gated", stream);
 }
 
 // dx[T, K] = (add ? dx : 0) + dg . W_gate + low_g . A_gate + du . W_up + low_u . A_up with the two weights read from
@@ -1653,8 +1744,11 @@ int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t s
   if (a.N % (BN / 2) != 0 || !gemm_tcgen05_supported(g))
     return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_gated_input_gradient: operands break a TMA rule");
   TcParams p;
-  const Variant plain{1, false};
-  int rc = fill_params(g, 2, plain, &p);
+  // The 512 x 256 tile (tensor-map store) where the result is written once and its rows fill such tiles.
+  const bool wide = !a.add && aligned16(a.dx) && a.ld_dx % 8 == 0 && wide_tile_fits(a.T, a.K) &&
+                    env_int("CT_B200_GEMM_MH", 0) != 1;
+  const Variant variant{wide ? 2 : 1, wide};
+  int rc = fill_params(g, 2, variant, &p);
   if (rc != CT_OK) return rc;
   for (int i = 0; i < 2; ++i) {
     TcSegment& t = p.seg[2 * i];
@@ -1665,7 +1759,7 @@ int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t s
   }
   const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.K) *
                        (2.0 * static_cast<double>(a.N) + static_cast<double>(a.r_gate + a.r_up));
-  return launch_gated(p, flops, a.T, a.K, 2 * a.N + a.r_gate + a.r_up, "gemm_tcgen05_gated_input_gradient", stream);
+  return launch_gated(p, wide, flops, a.T, a.K, 2 * a.N + a.r_gate + a.r_up, "gemm_tcgen05_gated_input_gradient", stream);
 }
 
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {

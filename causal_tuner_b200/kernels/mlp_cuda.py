@@ -66,11 +66,20 @@ def silu_multiply(gate, up):
     return _SiLUMultiply.apply(gate, up)
 
 
-def _gated(x, parameters, states, dtype):
+def _gated(x, parameters, states, dtype, keeps):
     """Whether gate(x), up(x) and the SwiGLU run as ONE tcgen05 launch (`gated_projections`): the two base
     weights are then decoded into one buffer of interleaved 128-row blocks, a GEMM tile accumulates the same 128
     columns of both projections, and the activation (forward, or its in-place backward on recomputed tiles) is
-    the tile's epilogue - gate and up never travel through memory unless the caller keeps them."""
+    the tile's epilogue - gate and up never travel through memory unless the caller keeps them.
+
+    An operator that recomputes takes this path in both passes whenever the shapes allow it (neither activation
+    is written or read, and a kernel goes: 16 ms of a 690 ms 7B step that recomputes in every layer). A forward
+    pass that `keeps` gate and up for the backward pass writes them anyway; there two launches of the
+    512 x 256-tile GEMM plus the stand-alone activation are faster than the gated launch, whose tile is
+    256 x 256 (3 ms of a 583 ms step), and are used unless CT_B200_MLP_FUSED_FORWARD=1."""
+    import os
+    if keeps and os.environ.get("CT_B200_MLP_FUSED_FORWARD", "0") != "1":
+        return False
     if (states[0] is None) != (states[1] is None) or parameters[0].device.type != "cuda":
         return False
     shapes = [parameters[4 * i].shape if states[i] is None else tuple(states[i].shape) for i in range(2)]
@@ -107,7 +116,7 @@ def _forward_into(output, x, dtype, tile, states, parameters, residual, *, save=
     """
     flat = cast(x.reshape(-1, x.shape[-1]), dtype)
     rows = flat.shape[0]
-    gated = rows > 0 and _gated(flat, parameters, states, dtype)
+    gated = rows > 0 and _gated(flat, parameters, states, dtype, save)
     matrices, adapters, stacked, pending = _prepare(parameters, states, dtype, gated=gated)
     width = matrices[2].shape[1]
     ranks = [a.shape[0] for a, _ in adapters]
@@ -188,7 +197,7 @@ class _TiledLoRAMLP(torch.autograd.Function):
         want_dx = ctx.needs_input_grad[0]
         dx = torch.empty_like(flat) if want_dx else None
         # Cached: the down projection's weight is needed first, gate/up only for the input gradient.
-        gated = rows > 0 and _gated(flat, parameters, ctx.states, dtype)
+        gated = rows > 0 and not ctx.cache and _gated(flat, parameters, ctx.states, dtype, False)
         matrices, adapters, stacked, pending = _prepare(parameters, ctx.states, dtype,
                                                         (2, 0, 1) if ctx.cache or gated else (0, 1, 2),
                                                         casts=saved[5:10] if len(saved) >= 10 else None, gated=gated)

@@ -446,8 +446,9 @@ def test_gated_launch_is_bit_identical_to_two_projections_and_the_activation(row
 @pytest.mark.parametrize("cache", [False, True])
 @pytest.mark.parametrize("tile", [0, 300])
 def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4, cache, tile):
-    """The whole operator with and without the gated launch (CT_B200_MLP_FUSED=0 turns it off): output and every
-    gradient equal bit for bit, with cached activations and with recompute, whole and in row tiles."""
+    """The whole operator with and without the gated launch (forward pass and the recompute of the backward pass):
+    output and every gradient equal bit for bit, with cached activations and with recompute, whole and in row
+    tiles."""
     torch.manual_seed(5)
     module = _mid_module(nf4)
     module.tile = tile
@@ -456,7 +457,8 @@ def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4,
     params = (x, *trainable(module))
     results = {}
     for fused in ("0", "1"):
-        monkeypatch.setenv("CT_B200_MLP_FUSED", fused)
+        monkeypatch.setenv("CT_B200_MLP_FUSED", fused)              # the recompute of the backward pass
+        monkeypatch.setenv("CT_B200_MLP_FUSED_FORWARD", fused)      # a forward pass that keeps gate and up (off by default)
         before = _lib.launch_count()
         y = module(x, residual=x, cache=cache)
         grads = torch.autograd.grad(y, params, signal)
