@@ -676,7 +676,7 @@ def run_shapes(args):
 # layers (16384 tokens, forward + backward, MLP activations kept, the lm_head's GEMMs included). The difference
 # is one layer, the rest is the head; every layer launches the same GEMMs, so a step is layers x layer + head.
 # `operands` is the least those launches could move: every operand read once and every result written once.
-GEMM_DRAM_TRAFFIC = {"step7b": {"layer_bytes": 19.94e9, "head_bytes": 12.09e9, "layer_launches": 25, "head_launches": 12,
+GEMM_DRAM_TRAFFIC = {"step7b": {"layer_bytes": 19.03e9, "head_bytes": 10.30e9, "layer_launches": 25, "head_launches": 12,
                                 "operands_bytes_per_step": 348e9}}
 
 

@@ -35,6 +35,7 @@ SIGNATURES = {
     "ct_gated_forward": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
     "ct_gated_backward": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
     "ct_gated_input_gradient": (_I, [_P, _P, _L, _P, _L, _P, _P, _L, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _P]),
+    "ct_input_gradient_swiglu": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _P, _L, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P]),
     "ct_forward_linear": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _P]),
     "ct_input_gradient": (_I, [_P, _L, _P, _L, _P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _I, _P]),
     "ct_input_gradient_group": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _I, _P]),

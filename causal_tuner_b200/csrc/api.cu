@@ -324,6 +324,23 @@ extern "C" int ct_gated_input_gradient(const void* d_gate, const void* d_up, int
   return gemm_tcgen05_gated_input_gradient(a, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int ct_input_gradient_swiglu(const void* dy, int64_t ld_dy, const void* w, int64_t ldw, const void* a,
+                                        const void* low, int64_t ld_low, const void* gate, const void* up,
+                                        int64_t ld_saved, void* d_gate, void* d_up, void* hidden, int64_t ld_out,
+                                        int64_t T, int64_t K, int64_t N, int64_t r, int dtype, void* stream) {
+  if (T < 0 || K < 0 || N <= 0 || r < 0) return fail(CT_ERR_ARG, "ct_input_gradient_swiglu: sizes");
+  if (T == 0 || K == 0) return CT_OK;
+  if (!dy || !w || (r > 0 && (!a || !low)) || !gate || !up || !d_gate || !d_up || !hidden)
+    return fail(CT_ERR_ARG, "ct_input_gradient_swiglu: null pointer");
+  if (dtype != CT_BF16) return fail(CT_ERR_UNSUPPORTED, "ct_input_gradient_swiglu: bf16 only");
+  GatedDownArgs args;
+  args.dy = dy; args.ld_dy = ld_dy; args.w = w; args.ldw = ldw; args.a = a; args.low = low; args.ld_low = ld_low;
+  args.gate = gate; args.up = up; args.ld_saved = ld_saved;
+  args.d_gate = d_gate; args.d_up = d_up; args.hidden = hidden; args.ld_out = ld_out;
+  args.T = T; args.K = K; args.N = N; args.r = r;
+  return gemm_tcgen05_gated_down_gradient(args, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* a, const void* b,
                                  const void* bias, const void* residual, int64_t ld_res, void* out, int64_t ld_out,
                                  void* xa, int64_t ld_xa, int64_t T, int64_t K, int64_t N, int64_t r, int dtype,

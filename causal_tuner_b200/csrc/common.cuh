@@ -175,6 +175,16 @@ struct GatedGradientArgs {
   int add;
 };
 int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t stream);
+struct GatedDownArgs {
+  const void* dy; int64_t ld_dy;           // [T, N]: gradient of the following projection's output
+  const void* w; int64_t ldw;              // [N, K]: that projection's base weight (K = width of the SwiGLU)
+  const void* a;                           // [r, K]
+  const void* low; int64_t ld_low;         // [T, r] = dy . b
+  const void* gate; const void* up; int64_t ld_saved;    // [T, K], kept by the forward pass
+  void* d_gate; void* d_up; void* hidden; int64_t ld_out;  // [T, K] outputs
+  int64_t T, K, N, r;
+};
+int gemm_tcgen05_gated_down_gradient(const GatedDownArgs& a, cudaStream_t stream);
 // Launches one thread that waits `limit_us` on a barrier nothing completes and reports it (gemm_tc.cu).
 int bounded_wait_selftest(int64_t limit_us, cudaStream_t stream);
 

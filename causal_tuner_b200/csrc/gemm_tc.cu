@@ -119,12 +119,18 @@ struct TcParams {
   // 128-row blocks). gated = 1: h = silu(gate) * up is written (and gate, up when their pointers are given);
   // gated = 2: with the upstream gradient dh of h, (d_gate, d_up, h) are written - gate and up never reach
   // memory. All five matrices are [M, N / 2] with leading dimension gated_ld; gated_h may alias gated_dh.
+  // gated = 3: the accumulator itself is the gradient of h (the input gradient of the down projection, N columns)
+  // and gate / up are read from memory (gated_src_g / gated_src_u, leading dimension gated_src_ld, kept by the
+  // forward pass): (d_gate, d_up, h) go to (gated_g, gated_u, gated_h) and the gradient of h is never stored.
   int gated;
   __nv_bfloat16* gated_h;
   __nv_bfloat16* gated_g;
   __nv_bfloat16* gated_u;
   const __nv_bfloat16* gated_dh;
   int64_t gated_ld;
+  const __nv_bfloat16* gated_src_g;
+  const __nv_bfloat16* gated_src_u;
+  int64_t gated_src_ld;
   // In-kernel NF4 decode of the B operand (gemm_tcgen05_nf4_kernel only): W[N, nf4_k] as packed codes, row-major,
   // two per byte, with one fp32 absmax per 64 elements and the 16-entry code table.
   const uint8_t* nf4_packed;
@@ -606,6 +612,7 @@ __device__ __forceinline__ void stage_packed(const TcParams& p, const uint32_t* 
 template <int CTAS, int STAGES_, int KSUB_, int MH, typename Params, bool DECODE = false, bool GATED = false>
 __device__ __forceinline__ void gemm_body(const Params& params) {
   using S = Shape<CTAS, STAGES_, KSUB_, MH>;
+  constexpr bool GATED_EPI = GATED && MH == 1;   // the SwiGLU epilogues exist in the 256 x 256-tile form only
   constexpr int KSUB = KSUB_;
   constexpr uint32_t SUB_BYTES = S::kSubBytes;
   constexpr uint32_t A_BYTES = S::kATileBytes;
@@ -974,14 +981,25 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
       const bool row_ok = row < p.M;
       // Gated backward: the upstream gradient of a 32-column chunk is requested one chunk ahead - the first
       // chunk's before the wait for the accumulator, while the tile's main loop is still running.
-      uint4 upstream_next[GATED ? 4 : 1];
-      if constexpr (GATED) {
+      uint4 upstream_next[GATED_EPI ? 4 : 1];
+      uint4 second_next[GATED_EPI ? 4 : 1];     // gated = 3: gate in upstream_next, up here
+      if constexpr (GATED_EPI) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) upstream_next[q] = make_uint4(0, 0, 0, 0);
+        for (int q = 0; q < 4; ++q) upstream_next[q] = second_next[q] = make_uint4(0, 0, 0, 0);
         if (p.gated == 2 && row_ok) {
           const uint4* source = reinterpret_cast<const uint4*>(p.gated_dh + row * p.gated_ld + static_cast<int64_t>(tc.n) * (BN / 2));
 #pragma unroll
           for (int q = 0; q < 4; ++q) upstream_next[q] = source[q];
+        }
+        if (p.gated == 3 && row_ok) {
+          const int64_t first = row * p.gated_src_ld + static_cast<int64_t>(tc.n) * BN;
+          const uint4* gate_source = reinterpret_cast<const uint4*>(p.gated_src_g + first);
+          const uint4* up_source = reinterpret_cast<const uint4*>(p.gated_src_u + first);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            upstream_next[q] = gate_source[q];
+            second_next[q] = up_source[q];
+          }
         }
       }
       int ok = 1;
@@ -991,8 +1009,65 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MH == 2 ? half : acc) * BN;
       bool released = false;   // the accumulator has already been handed back to the MMA warp
-      if (GATED && p.gated) {
-        if constexpr (GATED) {
+      if (GATED_EPI && p.gated == 3) {
+        if constexpr (GATED_EPI) {
+          // The accumulator is the gradient of hidden = silu(gate) * up; it is rounded to bf16 as the stored
+          // gradient would be and meets gate and up (requested from memory one 32-column chunk ahead) in the
+          // in-place backward of the stand-alone kernel. N is a multiple of 32 here.
+          const int64_t tile_col = static_cast<int64_t>(tc.n) * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int64_t col0 = tile_col + c * 32;
+            if (col0 >= p.N) break;  // uniform across the warp
+            uint32_t raw[32];
+            __syncwarp();
+            tmem_load_32_issue(taddr + c * 32, raw);
+            uint4 gate_now[4], up_now[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              gate_now[q] = upstream_next[GATED_EPI ? q : 0];
+              up_now[q] = second_next[GATED_EPI ? q : 0];
+            }
+            if (row_ok && c + 1 < BN / 32 && col0 + 32 < p.N) {
+              const int64_t next = row * p.gated_src_ld + col0 + 32;
+              const uint4* gate_source = reinterpret_cast<const uint4*>(p.gated_src_g + next);
+              const uint4* up_source = reinterpret_cast<const uint4*>(p.gated_src_u + next);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                upstream_next[GATED_EPI ? q : 0] = gate_source[q];
+                second_next[GATED_EPI ? q : 0] = up_source[q];
+              }
+            }
+            tmem_load_wait(raw);
+            if (row_ok) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t gate_words[4] = {gate_now[q].x, gate_now[q].y, gate_now[q].z, gate_now[q].w};
+                const uint32_t up_words[4] = {up_now[q].x, up_now[q].y, up_now[q].z, up_now[q].w};
+                uint32_t h_words[4], g_words[4], u_words[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gate_words[j]));
+                  const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&up_words[j]));
+                  const float grad0 = round_to<__nv_bfloat16>(__uint_as_float(raw[8 * q + 2 * j]));
+                  const float grad1 = round_to<__nv_bfloat16>(__uint_as_float(raw[8 * q + 2 * j + 1]));
+                  float h0 = 0.f, h1 = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+                  swiglu_element<__nv_bfloat16>(g.x, u.x, grad0, true, true, h0, a0, b0);
+                  swiglu_element<__nv_bfloat16>(g.y, u.y, grad1, true, true, h1, a1, b1);
+                  h_words[j] = pack_bf16(h0, h1);
+                  g_words[j] = pack_bf16(a0, a1);
+                  u_words[j] = pack_bf16(b0, b1);
+                }
+                const int64_t at = row * p.gated_ld + col0 + q * 8;
+                *reinterpret_cast<uint4*>(p.gated_h + at) = make_uint4(h_words[0], h_words[1], h_words[2], h_words[3]);
+                *reinterpret_cast<uint4*>(p.gated_g + at) = make_uint4(g_words[0], g_words[1], g_words[2], g_words[3]);
+                *reinterpret_cast<uint4*>(p.gated_u + at) = make_uint4(u_words[0], u_words[1], u_words[2], u_words[3]);
+              }
+            }
+          }
+        }
+      } else if (GATED_EPI && p.gated) {
+        if constexpr (GATED_EPI) {
           // Accumulator columns [0, 128) are the gate projection, [128, 256) the up projection of the same 128
           // output columns. Each is rounded to bf16 as a stored projection output would be; the SwiGLU element
           // arithmetic is the stand-alone kernel's.
@@ -1008,11 +1083,11 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
             tmem_load_32_issue(taddr + BN / 2 + c * 32, up_raw);
             uint4 upstream[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) upstream[q] = upstream_next[GATED ? q : 0];
+            for (int q = 0; q < 4; ++q) upstream[q] = upstream_next[GATED_EPI ? q : 0];
             if (backward && row_ok && c + 1 < BN / 64) {
               const uint4* source = reinterpret_cast<const uint4*>(p.gated_dh + offset + (c + 1) * 32);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) upstream_next[GATED ? q : 0] = source[q];
+              for (int q = 0; q < 4; ++q) upstream_next[GATED_EPI ? q : 0] = source[q];
             }
             tmem_load_wait(gate_raw);
             tmem_load_wait(up_raw);
@@ -1501,6 +1576,8 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
   p.gated_h = p.gated_g = p.gated_u = nullptr;
   p.gated_dh = nullptr;
   p.gated_ld = 0;
+  p.gated_src_g = p.gated_src_u = nullptr;
+  p.gated_src_ld = 0;
   return CT_OK;
 }
 
@@ -1760,6 +1837,41 @@ int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t s
   const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.K) *
                        (2.0 * static_cast<double>(a.N) + static_cast<double>(a.r_gate + a.r_up));
   return launch_gated(p, wide, flops, a.T, a.K, 2 * a.N + a.r_gate + a.r_up, "gemm_tcgen05_gated_input_gradient", stream);
+}
+
+// (d_gate, d_up, hidden) of a SwiGLU from the input gradient of the projection that follows it, in that
+// projection's input-gradient GEMM: the accumulator dh = dy . W + low . A ([T, K], K the MLP width) is not stored;
+// the epilogue reads the kept gate and up and applies the in-place backward to each element.
+int gemm_tcgen05_gated_down_gradient(const GatedDownArgs& a, cudaStream_t stream) {
+  GemmArgs g;
+  g.M = a.T; g.N = a.K; g.nseg = a.r > 0 ? 2 : 1; g.in_dtype = CT_BF16;
+  g.seg[0].a = a.dy; g.seg[0].a_rs = a.ld_dy; g.seg[0].a_cs = 1;
+  g.seg[0].b = a.w; g.seg[0].b_rs = a.ldw; g.seg[0].b_cs = 1; g.seg[0].k = a.N;
+  if (a.r > 0) {
+    g.seg[1].a = a.low; g.seg[1].a_rs = a.ld_low; g.seg[1].a_cs = 1;
+    g.seg[1].b = a.a; g.seg[1].b_rs = a.K; g.seg[1].b_cs = 1; g.seg[1].k = a.r;
+  }
+  g.out = a.hidden; g.ldo = a.ld_out; g.out_dtype = CT_BF16; g.beta = 0; g.bias = nullptr; g.residual = nullptr;
+  g.ld_res = 0; g.split_k = 1;
+  const bool pointers = aligned16(a.gate) && aligned16(a.up) && aligned16(a.d_gate) && aligned16(a.d_up) &&
+                        aligned16(a.hidden) && a.gate && a.up && a.d_gate && a.d_up && a.hidden;
+  if (!pointers || a.K % 32 != 0 || a.ld_out % 8 != 0 || a.ld_saved % 8 != 0 || a.ld_out < a.K || a.ld_saved < a.K ||
+      !gemm_tcgen05_supported(g))
+    return fail(CT_ERR_UNSUPPORTED, "gemm_tcgen05_gated_down_gradient: needs bf16 operands with 16-byte aligned rows and a width that is a multiple of 32");
+  TcParams p;
+  const Variant plain{1, false};
+  const int rc = fill_params(g, 2, plain, &p);
+  if (rc != CT_OK) return rc;
+  p.gated = 3;
+  p.gated_h = static_cast<__nv_bfloat16*>(a.hidden);
+  p.gated_g = static_cast<__nv_bfloat16*>(a.d_gate);
+  p.gated_u = static_cast<__nv_bfloat16*>(a.d_up);
+  p.gated_ld = a.ld_out;
+  p.gated_src_g = static_cast<const __nv_bfloat16*>(a.gate);
+  p.gated_src_u = static_cast<const __nv_bfloat16*>(a.up);
+  p.gated_src_ld = a.ld_saved;
+  const double flops = 2.0 * static_cast<double>(a.T) * static_cast<double>(a.K) * static_cast<double>(a.N + a.r);
+  return launch_gated(p, false, flops, a.T, a.K, a.N + a.r, "gemm_tcgen05_gated_down_gradient", stream);
 }
 
 int gemm_dispatch(const GemmArgs& g, int path, cudaStream_t stream) {

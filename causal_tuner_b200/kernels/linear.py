@@ -404,6 +404,28 @@ def gated_input_gradient(d_gate, d_up, pair, a_gate, a_up, b_gate, b_up, dx, low
             _lib.code_of(dx.dtype), _lib.stream_of(dx)))
 
 
+def input_gradient_swiglu(dy, weight, a, low, gate, up, d_gate, d_up, hidden):
+    """Backward pass of a SwiGLU whose gate and up were kept, inside the input-gradient GEMM of the projection that
+    follows it: dh = dy @ weight + low @ a stays in the accumulator, and (d_gate, d_up, hidden) - the in-place
+    backward of `activation(gate, up, dh)` - are written; gate and up are only read. `low` = dy @ b is an input."""
+    _lib.require_cuda(dy, weight, a, low, gate, up, d_gate, d_up, hidden)
+    dy, weight, low, gate, up = _readable(dy), _readable(weight), _readable(low), _readable(gate), _readable(up)
+    a = a.contiguous()
+    rows, width = dy.shape[0], weight.shape[1]
+    for tensor in (gate, up, d_gate, d_up, hidden):
+        if tensor.shape != (rows, width) or tensor.stride(1) != 1:
+            raise ValueError("input_gradient_swiglu: gate, up and the outputs must be [rows, width] with unit column stride")
+    if _leading(gate) != _leading(up) or len({_leading(t) for t in (d_gate, d_up, hidden)}) != 1:
+        raise ValueError("input_gradient_swiglu: gate / up (and the three outputs) must share a leading dimension")
+    with _lib.on_device(dy):
+        _lib.check(_lib.load().ct_input_gradient_swiglu(
+            dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), low.data_ptr(),
+            _leading(low), gate.data_ptr(), up.data_ptr(), _leading(gate), d_gate.data_ptr(), d_up.data_ptr(),
+            hidden.data_ptr(), _leading(hidden), rows, width, weight.shape[0], a.shape[0], _lib.code_of(dy.dtype),
+            _lib.stream_of(dy)))
+    return hidden
+
+
 def stack_adapters(matrices, dtype, others=()):
     """Row-wise stack of the `a` matrices of projections that share their input, cast to `dtype`,
     and the row offset of each: one product x @ stack.T then yields every projection's low-rank

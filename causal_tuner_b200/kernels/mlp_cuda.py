@@ -11,6 +11,7 @@ import torch
 
 from .. import _lib
 from .linear import (_policy, apply_projection, cast, gated_input_gradient, gated_projections, gated_supported,
+                     input_gradient_swiglu,
                      materialize, materialize_ahead, forward_linear, input_gradient, input_gradient_with,
                      input_gradient_group, parameter_gradients, projection_parameters, matmul, stack_adapters,
                      token_gradient, token_gradients)
@@ -202,6 +203,14 @@ class _TiledLoRAMLP(torch.autograd.Function):
                                                         (2, 0, 1) if ctx.cache or gated else (0, 1, 2),
                                                         casts=saved[5:10] if len(saved) >= 10 else None, gated=gated)
         ranks = [a.shape[0] for a, _ in adapters]
+        # Cached activations: the SwiGLU backward can ride on the down projection's input-gradient GEMM
+        # (`input_gradient_swiglu`, bit-identical). Measured inside a 7B step it gives back in that GEMM - which
+        # then runs on 256 x 256 tiles with a long epilogue instead of 512 x 256 tiles - what the stand-alone kernel
+        # cost (585-589 ms against 585-586 ms), so it is taken only on request (CT_B200_MLP_FUSED_BACKWARD=1).
+        import os
+        joined = (bool(ctx.cache) and rows > 0 and os.environ.get("CT_B200_MLP_FUSED_BACKWARD", "0") == "1"
+                  and matrices[2].shape[1] % 32 == 0 and matrices[2].shape[0] % 8 == 0
+                  and gated_supported(upstream, 0, ranks[2:], dtype))
         make = torch.empty if rows else torch.zeros
         wide = dict(device=x.device, dtype=torch.float32)
         # fp32 accumulators: d(a_gate) and d(a_up) stacked (one product over x yields both), the rest apart
@@ -234,21 +243,28 @@ class _TiledLoRAMLP(torch.autograd.Function):
                     apply_projection(part, matrices[1], adapters[1][1], xa[1], out=up)
             matmul(dy, adapters[2][1], out=low[2])      # needs no base weight: runs beside the decodes
             pending.wait(2)
-            input_gradient_with(dy, matrices[2], adapters[2][0], low[2], dh)
-            if ctx.cache:
-                # Read the saved gate/up, write (d_gate, d_up, hidden) into the tile buffers: the saved
-                # tensors stay untouched and survive a repeated backward pass, without a copy.
-                _swiglu(saved[0][start:stop], saved[1][start:stop], dh, dh, gate, up, True)
-                hidden = dh
-            elif gated:
-                # gate and up are recomputed tile by tile in the GEMM's accumulator and leave it as (d_gate, d_up,
-                # hidden): the activations themselves are never written
-                pending.wait(0)
-                pending.wait(1)
-                hidden = gated_projections(part, matrices[0], xa[0], xa[1], adapters[0][1], adapters[1][1],
-                                           hidden=dh, gate=gate, up=up, gradient=dh)
+            if joined:
+                # the gradient of hidden meets the kept gate and up in the epilogue of the GEMM that computes it:
+                # it is never written, and (d_gate, d_up, hidden) land in the tile buffers; the saved tensors stay
+                # untouched and survive a repeated backward pass
+                hidden = input_gradient_swiglu(dy, matrices[2], adapters[2][0], low[2], saved[0][start:stop],
+                                               saved[1][start:stop], gate, up, dh)
             else:
-                hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
+                input_gradient_with(dy, matrices[2], adapters[2][0], low[2], dh)
+                if ctx.cache:
+                    # Read the saved gate/up, write (d_gate, d_up, hidden) into the tile buffers: the saved
+                    # tensors stay untouched and survive a repeated backward pass, without a copy.
+                    _swiglu(saved[0][start:stop], saved[1][start:stop], dh, dh, gate, up, True)
+                    hidden = dh
+                elif gated:
+                    # gate and up are recomputed tile by tile in the GEMM's accumulator and leave it as (d_gate,
+                    # d_up, hidden): the activations themselves are never written
+                    pending.wait(0)
+                    pending.wait(1)
+                    hidden = gated_projections(part, matrices[0], xa[0], xa[1], adapters[0][1], adapters[1][1],
+                                               hidden=dh, gate=gate, up=up, gradient=dh)
+                else:
+                    hidden = activation(gate, up, dh)  # (gate, up, dh) now hold (d_gate, d_up, hidden)
             if len(saved) > 4:
                 xa_low = saved[4][start:stop]
             else:

@@ -336,6 +336,20 @@ CT_API int ct_gated_input_gradient(const void* d_gate, const void* d_up, int64_t
                                    int64_t K, int64_t N, int64_t r_gate, int64_t r_up, int add, int dtype,
                                    void* stream);
 
+/* ct_input_gradient_swiglu: the backward pass of an MLP that kept gate(x) and up(x) (kernels/mlp_cuda.py:122-133
+ * with cached activations: `input_gradient` of the down projection, then `activation(gate, up, hidden_grad)`),
+ * in one launch. dh = dy @ w + low @ a ([T, K], K = width of the SwiGLU, w [N, K], a [r, K], low = dy @ b [T, r]) is
+ * accumulated in TMEM, rounded to bf16 as the stored gradient would be and never written: the epilogue reads
+ * `gate` and `up` ([T, K], leading dimension ld_saved; requested one 32-column chunk ahead of their use) and writes
+ *   d_gate, d_up, hidden  =  ct_swiglu's in-place backward of (gate, up, dh)
+ * ([T, K], leading dimension ld_out; none may alias gate or up, which stay intact for a repeated backward
+ * pass). Bit-identical to ct_input_gradient followed by ct_swiglu. bf16, K a multiple of 32, rows 16-byte
+ * aligned; anything else returns CT_ERR_UNSUPPORTED (nothing launched). */
+CT_API int ct_input_gradient_swiglu(const void* dy, int64_t ld_dy, const void* w, int64_t ldw, const void* a,
+                                    const void* low, int64_t ld_low, const void* gate, const void* up,
+                                    int64_t ld_saved, void* d_gate, void* d_up, void* hidden, int64_t ld_out,
+                                    int64_t T, int64_t K, int64_t N, int64_t r, int dtype, void* stream);
+
 /* ---- adjacent-pair partial RoPE ---------------------------------------------
  * Replaces kernels/core_cuda.py:146-164 (_rope: forward, or inverse into a
  * private tile, kernels/core_cuda.py:203-208) and kernels/core_cuda.py:167-199

@@ -459,6 +459,7 @@ def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4,
     for fused in ("0", "1"):
         monkeypatch.setenv("CT_B200_MLP_FUSED", fused)              # the recompute of the backward pass
         monkeypatch.setenv("CT_B200_MLP_FUSED_FORWARD", fused)      # a forward pass that keeps gate and up (off by default)
+        monkeypatch.setenv("CT_B200_MLP_FUSED_BACKWARD", fused)     # SwiGLU backward in the down projection's GEMM (off by default)
         before = _lib.launch_count()
         y = module(x, residual=x, cache=cache)
         grads = torch.autograd.grad(y, params, signal)
@@ -467,3 +468,33 @@ def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4,
     for separate, gated in zip(results["0"][:-1], results["1"][:-1]):
         assert torch.isfinite(gated).all()
         assert torch.equal(separate, gated)
+
+
+@pytest.mark.parametrize("rows", [1000, 256, 77])
+@pytest.mark.parametrize("width", [384, 416])
+def test_swiglu_backward_inside_the_down_projections_input_gradient(rows, width):
+    """ct_input_gradient_swiglu against ct_input_gradient followed by ct_swiglu: (d_gate, d_up, hidden) equal bit for
+    bit, the kept gate and up untouched, nothing written past the rows."""
+    from causal_tuner_b200.kernels import linear
+    torch.manual_seed(rows + width)
+    hidden_size, rank = 512, 24
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(rows, hidden_size, **bf)
+    weight = torch.randn(hidden_size, width, **bf) * .05
+    a, b = torch.randn(rank, width, **bf) * .05, torch.randn(hidden_size, rank, **bf) * .2
+    gate, up = torch.randn(rows, width, **bf), torch.randn(rows, width, **bf)
+    kept = (gate.clone(), up.clone())
+    low = torch.empty(rows, rank, **bf)
+    linear.matmul(dy, b, out=low)
+    dh = torch.empty(rows, width, **bf)
+    linear.input_gradient_with(dy, weight, a, low, dh)
+    expected = [gate.clone(), up.clone(), dh]
+    mlp_cuda.activation(*expected)
+    outputs = [torch.full((rows + 1, width), 7.0, **bf) for _ in range(3)]
+    before = _lib.tcgen05_launch_count()
+    linear.input_gradient_swiglu(dy, weight, a, low, gate, up, outputs[0][:rows], outputs[1][:rows], outputs[2][:rows])
+    assert _lib.tcgen05_launch_count() == before + 1
+    for actual, wanted in zip(outputs, expected):
+        assert torch.equal(actual[:rows], wanted)
+        assert (actual[rows] == 7).all()
+    assert torch.equal(gate, kept[0]) and torch.equal(up, kept[1])
