@@ -614,7 +614,6 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
   using S = Shape<CTAS, STAGES_, KSUB_, MH>;
   constexpr bool GATED_EPI = GATED && MH == 1;   // the SwiGLU epilogues exist in the 256 x 256-tile form only
   constexpr int KSUB = KSUB_;
-  constexpr uint32_t SUB_BYTES = S::kSubBytes;
   constexpr uint32_t A_BYTES = S::kATileBytes;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t STAGE_BYTES = S::kStageBytes;
@@ -709,17 +708,17 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           uint64_t map_a = reinterpret_cast<uint64_t>(&sg.a), map_b = reinterpret_cast<uint64_t>(&sg.b);
           int a_mn = sg.a_mn, b_mn = sg.b_mn;
           int b_row = b_row0;
-          uint32_t sub_tx = DECODE ? A_BYTES : SUB_BYTES;     // bytes one CTA receives per k-block
+          uint32_t b_tx = DECODE ? 0u : S::kBTileBytes;     // bytes of B one CTA receives per k-block
           int k_block = 0, k_offset = 0;
           if constexpr (GATED) {
             if (sg.n_half) {     // half as many B columns: 64 rows of a K-major [N / 2, k] matrix per CTA
               b_row = tc.n * (BN / 2) + static_cast<int>(rank) * (S::kBRows / 2);
-              sub_tx = A_BYTES + S::kBTileBytes / 2;
+              b_tx = S::kBTileBytes / 2;
             }
             k_block = sg.b_k_block;
             k_offset = sg.b_k_offset;
           }
-          asm volatile("" : "+l"(map_a), "+l"(map_b), "+r"(a_mn), "+r"(b_mn), "+r"(b_row), "+r"(sub_tx), "+r"(k_block),
+          asm volatile("" : "+l"(map_a), "+l"(map_b), "+r"(a_mn), "+r"(b_mn), "+r"(b_row), "+r"(b_tx), "+r"(k_block),
                        "+r"(k_offset));
           for (int kb = lo; kb < hi; kb += KSUB) {
             // A freed stage has to be on its way again within the time the MMAs of the other stages take, so
@@ -728,7 +727,8 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
             const int subs = min(KSUB, hi - kb);   // a stage holds up to KSUB 64-wide k-blocks
             // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
             uint32_t bar = lead_full0 + 8u * stage;
-            uint32_t expected = CTAS * subs * sub_tx;
+            // an MN-major operand arrives as boxes of 64 columns x ALL the stage's k rows, whatever `subs` is
+            uint32_t expected = CTAS * ((a_mn ? KSUB : subs) * A_BYTES + (b_mn ? KSUB : subs) * b_tx);
             uint32_t a_dst = smem_base + stage * STAGE_BYTES;
             int k_first = kb * BK;
             asm volatile("" : "+r"(bar), "+r"(expected), "+r"(a_dst), "+r"(k_first));
@@ -742,29 +742,34 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
                 if constexpr (CTAS == 1) tma_load_2d(dst, map, bar, x, y);
                 else tma_load_2d_pair(dst, map, bar, x, y);
               };
+              // A stage is [A: KSUB k-blocks][B: KSUB k-blocks]. A K-major operand takes one copy per k-block
+              // (rows x 64 k, at k-block * tile bytes); an MN-major operand one copy per 64 columns for ALL the
+              // stage's k rows (box j at j * KSUB * 8 KB, k-block s at s * 8 KB inside it): half the copy
+              // instructions of a copy per k-block, and these are what a stage's turn-around waits for.
+              const uint32_t b_dst = a_dst + KSUB * A_BYTES;
+              if (!a_mn) {
 #pragma unroll
-              for (int sub = 0; sub < KSUB; ++sub) {
-                if (sub >= subs) break;
-                const int k0 = k_first + sub * BK;
-                const uint32_t a_sub = a_dst + sub * SUB_BYTES, b_sub = a_sub + A_BYTES;
-                if (!a_mn) {
-                  load(a_sub, map_a, k0, a_row0);      // one box of CTA_ROWS rows
-                } else {
+                for (int sub = 0; sub < KSUB; ++sub)
+                  if (sub < subs) load(a_dst + sub * A_BYTES, map_a, k_first + sub * BK, a_row0);   // CTA_ROWS rows
+              } else {
 #pragma unroll
-                  for (int j = 0; j < CTA_ROWS / 64; ++j) load(a_sub + j * MN_BOX_BYTES, map_a, a_row0 + j * 64, k0);
+                for (int j = 0; j < CTA_ROWS / 64; ++j)
+                  load(a_dst + j * (KSUB * MN_BOX_BYTES), map_a, a_row0 + j * 64, k_first);
+              }
+              if constexpr (DECODE) {
+                // the B tiles of this stage are written by the decode warps
+              } else if (!b_mn) {
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                  if (sub < subs) load(b_dst + sub * S::kBTileBytes, map_b, k_first + sub * BK, b_row);
+              } else {
+                int k_row = k_first;
+                if constexpr (GATED) {      // B's k rows live in a buffer of interleaved 128-row blocks (a stage's
+                  if (k_block) k_row = k_first + ((k_first >> 7) << 7) + k_offset;   // rows never straddle two)
                 }
-                if constexpr (DECODE) {
-                  // the B tile of this k-block is written by the decode warps
-                } else if (!b_mn) {
-                  load(b_sub, map_b, k0, b_row);
-                } else {
-                  int k_row = k0;
-                  if constexpr (GATED) {      // B's k rows live in a buffer of interleaved 128-row blocks
-                    if (k_block) k_row = k0 + ((k0 >> 7) << 7) + k_offset;
-                  }
 #pragma unroll
-                  for (int j = 0; j < S::kBRows / 64; ++j) load(b_sub + j * MN_BOX_BYTES, map_b, b_row0 + j * 64, k_row);
-                }
+                for (int j = 0; j < S::kBRows / 64; ++j)
+                  load(b_dst + j * (KSUB * MN_BOX_BYTES), map_b, b_row0 + j * 64, k_row);
               }
             }
             __syncwarp();
@@ -820,8 +825,11 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
           // K-major: 8-row groups 1024 B apart, 32 B per 16-element k step inside the swizzle atom.
           // MN-major: 64-wide column groups one box (8 KB) apart, 8-k groups 1024 B apart,
           //           16 k rows (2 KB) per k step.
-          const uint32_t a_lo0 = desc_low(smem_base, sg.a_mn ? MN_BOX_BYTES : 16u);
-          const uint32_t b_lo0 = desc_low(smem_base + A_BYTES, sg.b_mn ? MN_BOX_BYTES : 16u);
+          const uint32_t a_lo0 = desc_low(smem_base, sg.a_mn ? KSUB * MN_BOX_BYTES : 16u);
+          const uint32_t b_lo0 = desc_low(smem_base + KSUB * A_BYTES, sg.b_mn ? KSUB * MN_BOX_BYTES : 16u);
+          // k-block s of a stage: K-major tiles follow one another; inside an MN-major box it is 8 KB further
+          const uint32_t a_sub = (sg.a_mn ? MN_BOX_BYTES : A_BYTES) >> 4;
+          const uint32_t b_sub = (sg.b_mn ? MN_BOX_BYTES : S::kBTileBytes) >> 4;
           const uint32_t a_step = sg.a_mn ? (2048u >> 4) : (32u >> 4);
           const uint32_t b_step = sg.b_mn ? (2048u >> 4) : (32u >> 4);
           for (int kb = lo; kb < hi; kb += KSUB) {
@@ -840,8 +848,8 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
 #pragma unroll
               for (int sub = 0; sub < KSUB; ++sub) {
                 if (sub >= subs) break;
-                const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4) + sub * (SUB_BYTES >> 4);
-                const uint32_t b_lo = b_lo0 + stage * (STAGE_BYTES >> 4) + sub * (SUB_BYTES >> 4);
+                const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4) + sub * a_sub;
+                const uint32_t b_lo = b_lo0 + stage * (STAGE_BYTES >> 4) + sub * b_sub;
 #pragma unroll
                 for (int j = 0; j < BK / UMMA_K; ++j) {
 #pragma unroll
@@ -929,7 +937,8 @@ __device__ __forceinline__ void gemm_body(const Params& params) {
 #pragma unroll
         for (int sub = 0; sub < KSUB; ++sub) {
           if (kb + sub >= p.k_blocks_total) break;
-          const uint32_t row_base = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES + A_BYTES + static_cast<uint32_t>(d) * 128u;
+          const uint32_t row_base = smem_base + stage * STAGE_BYTES + KSUB * A_BYTES + sub * S::kBTileBytes +
+                                    static_cast<uint32_t>(d) * 128u;
           const uint32_t words[8] = {word[slot][sub][0].x, word[slot][sub][0].y, word[slot][sub][0].z, word[slot][sub][0].w,
                                      word[slot][sub][1].x, word[slot][sub][1].y, word[slot][sub][1].z, word[slot][sub][1].w};
           const float s8 = scale[slot][sub];
@@ -1532,6 +1541,7 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
   p.tma_store = variant.tma_store ? 1 : 0;
   const int halves = variant.halves;
   const int tile_m = BM * ctas * halves, b_rows = BN / ctas;
+  const int stage_blocks = (ctas == 2 && halves == 1) ? 2 : 1;
   p.nseg = g.nseg;
   p.k_blocks_total = 0;
   for (int s = 0; s < g.nseg; ++s) {
@@ -1543,9 +1553,13 @@ int fill_params(const GemmArgs& g, int ctas, const Variant& variant, TcParams* o
     t.b_mn = sg.b_rs == 1 ? 0 : 1;
     t.n_half = t.d_col = t.b_k_block = t.b_k_offset = 0;
     // K-major: contiguous index is k, rows are m (or n). MN-major: contiguous index is m (or n), rows are k.
-    rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK) : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM * halves);
+    // An MN-major operand is fetched in boxes of 64 columns x all the k rows of a ring stage (two k-blocks in the
+    // 256 x 256 CTA-pair kernels, one elsewhere).
+    rc = t.a_mn ? make_map(&t.a, sg.a, g.M, sg.k, sg.a_cs, BK * stage_blocks)
+                : make_map(&t.a, sg.a, sg.k, g.M, sg.a_rs, BM * halves);
     if (rc != CT_OK) return rc;
-    rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK) : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, b_rows);
+    rc = t.b_mn ? make_map(&t.b, sg.b, g.N, sg.k, sg.b_rs, BK * stage_blocks)
+                : make_map(&t.b, sg.b, sg.k, g.N, sg.b_cs, b_rows);
     if (rc != CT_OK) return rc;
   }
   if (p.tma_store) {
@@ -1604,10 +1618,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t stream) {
   if (ctas == 2 && variant.halves == 2) {
     rc = launch_wide(p, grid, device, stream);
   } else if (ctas == 2) {
-    // Default: 3 stages of two 64-wide k-blocks (one barrier round per 8 MMAs). CT_B200_GEMM_KSUB=1
-    // selects 6 stages of one k-block (one round per 4 MMAs) for comparison runs.
-    const int ksub = env_int("CT_B200_GEMM_KSUB", 2);
-    rc = ksub == 1 ? launch_pair<6, 1>(p, grid, device, stream) : launch_pair<3, 2>(p, grid, device, stream);
+    rc = launch_pair<3, 2>(p, grid, device, stream);   // 3 stages of two 64-wide k-blocks: one barrier round per 8 MMAs
   } else {
     rc = launch_single(p, grid, device, stream);
   }
@@ -1829,7 +1840,7 @@ int gemm_tcgen05_gated_input_gradient(const GatedGradientArgs& a, cudaStream_t s
   if (rc != CT_OK) return rc;
   for (int i = 0; i < 2; ++i) {
     TcSegment& t = p.seg[2 * i];
-    rc = make_map(&t.b, a.w_pair, a.K, 2 * a.N, a.ldw, BK);     // all 2 N rows of the interleaved buffer
+    rc = make_map(&t.b, a.w_pair, a.K, 2 * a.N, a.ldw, wide ? BK : 2 * BK);     // all 2 N rows of the interleaved buffer
     if (rc != CT_OK) return rc;
     t.b_k_block = BN / 2;
     t.b_k_offset = i * (BN / 2);
