@@ -28,6 +28,7 @@ SIGNATURES = {
     "ct_timing_enable": (_I, [_I]),
     "ct_timing_collect": (_I, [_P, _P, _P]),
     "ct_nf4_decode": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
+    "ct_nf4_decode_transposed": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P]),
     "ct_nf4_decode_chunks": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _L, _P]),
     "ct_cast": (_I, [_P, _I, _L, _P, _I, _L, _L, _L, _P]),
     "ct_matmul": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _L, _L, _I, _I, _I, _I, _P]),
@@ -37,8 +38,8 @@ SIGNATURES = {
     "ct_gated_input_gradient": (_I, [_P, _P, _L, _P, _L, _P, _P, _L, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _P]),
     "ct_input_gradient_swiglu": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _P, _L, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P]),
     "ct_forward_linear": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _P]),
-    "ct_input_gradient": (_I, [_P, _L, _P, _L, _P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _I, _P]),
-    "ct_input_gradient_group": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _I, _P]),
+    "ct_input_gradient": (_I, [_P, _L, _P, _L, _L, _P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _I, _I, _I, _P]),
+    "ct_input_gradient_group": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _I, _P]),
     "ct_parameter_gradients_workspace": (_L, [_L, _L, _L, _L, _I, _I]),
     "ct_parameter_gradients": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, _P, _I, _P]),
     "ct_parameter_gradients_noalloc_capacity": (_L, []),

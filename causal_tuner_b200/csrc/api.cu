@@ -366,9 +366,10 @@ extern "C" int ct_forward_linear(const void* x, int64_t ldx, const void* w, int6
   return gemm_dispatch(g, path, s);
 }
 
-extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t ldw, const void* a,
-                                 const void* b, void* dx, int64_t ld_dx, void* low, int64_t ld_low, int64_t T,
-                                 int64_t K, int64_t N, int64_t r, int add, int dtype, int path, void* stream) {
+extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t w_rs, int64_t w_cs,
+                                 const void* a, const void* b, void* dx, int64_t ld_dx, void* low, int64_t ld_low,
+                                 int64_t T, int64_t K, int64_t N, int64_t r, int add, int dtype, int path,
+                                 void* stream) {
   if (T < 0 || K < 0 || N < 0 || r < 0) return fail(CT_ERR_ARG, "ct_input_gradient: negative size");
   if (T == 0) return CT_OK;
   if ((N > 0 && !dy) || (r > 0 && !low) || (w && (!dx || (r > 0 && !a))))
@@ -384,21 +385,22 @@ extern "C" int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, i
   }
   if (!w || K == 0) return CT_OK;
   GemmArgs g = blank(T, K, dtype, dx, ld_dx, dtype);
-  g.seg[g.nseg++] = segment(dy, ld_dy, 1, w, ldw, 1, N);
+  g.seg[g.nseg++] = segment(dy, ld_dy, 1, w, w_rs, w_cs, N);
   if (r > 0) g.seg[g.nseg++] = segment(low, ld_low, 1, a, K, 1, r);
   g.beta = add;
   return gemm_dispatch(g, path, s);
 }
 
 extern "C" int ct_input_gradient_group(int count, const void* const* dy, const int64_t* ld_dy, const void* const* w,
-                                       const int64_t* ldw, const void* const* a, const void* const* b,
+                                       const int64_t* w_rs, const int64_t* w_cs, const void* const* a,
+                                       const void* const* b,
                                        const int64_t* N, const int64_t* r, void* dx, int64_t ld_dx, void* const* low,
                                        const int64_t* ld_low, int64_t T, int64_t K, int add, int dtype, int path,
                                        void* stream) {
   if (count < 1 || 2 * count > kMaxSegments) return fail(CT_ERR_ARG, "ct_input_gradient_group: count %d", count);
   if (T < 0 || K < 0) return fail(CT_ERR_ARG, "ct_input_gradient_group: negative size");
   if (T == 0 || K == 0) return CT_OK;
-  if (!dy || !ld_dy || !w || !ldw || !a || !b || !N || !r || !dx || !low || !ld_low)
+  if (!dy || !ld_dy || !w || !w_rs || !w_cs || !a || !b || !N || !r || !dx || !low || !ld_low)
     return fail(CT_ERR_ARG, "ct_input_gradient_group: null pointer");
   if (!known_dtype(dtype)) return fail(CT_ERR_ARG, "ct_input_gradient_group: dtype %d", dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -413,7 +415,7 @@ extern "C" int ct_input_gradient_group(int count, const void* const* dy, const i
   }
   GemmArgs g = blank(T, K, dtype, dx, ld_dx, dtype);
   for (int i = 0; i < count; ++i) {
-    g.seg[g.nseg++] = segment(dy[i], ld_dy[i], 1, w[i], ldw[i], 1, N[i]);
+    g.seg[g.nseg++] = segment(dy[i], ld_dy[i], 1, w[i], w_rs[i], w_cs[i], N[i]);
     g.seg[g.nseg++] = segment(low[i], ld_low[i], 1, a[i], K, 1, r[i]);
   }
   g.beta = add;

@@ -171,6 +171,51 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const Nf4Params p)
   }
 }
 
+// The same decode with the result written TRANSPOSED: W[rows, cols] (packed row-major) -> out[cols, rows] (bf16,
+// leading dimension ld_out). One CTA takes a 64 x 64 tile: thread t decodes 16 consecutive elements of tile row
+// t / 4 (one 8-byte load of codes, one scale: the 16 lie in one absmax block), parks them in a shared-memory tile
+// indexed [column][row], and after the barrier writes 32 contiguous bytes of a transposed row - four threads
+// cover the 128 bytes a tile contributes to it, so every sector is written whole. rows and cols are multiples of 64.
+// The input gradient dx = dy . W contracts over the rows of W: with this layout W is a K-major operand of that
+// GEMM, which the tensor core reads faster than the MN-major 64 x 64 boxes of the row-major weight.
+constexpr int kTile = 64;
+constexpr int kTilePitch = kTile + 8;   // bf16 elements per tile row: 144 bytes, 16-byte aligned
+
+template <int STATE>
+__global__ void __launch_bounds__(kThreads) nf4_decode_transposed_kernel(const Nf4Params p, int64_t rows, int64_t cols,
+                                                                         int64_t ld_out) {
+  __shared__ float lut[16 * 32];
+  __shared__ __align__(16) __nv_bfloat16 tile[kTile * kTilePitch];
+  lut[threadIdx.x] = __ldg(p.code + (threadIdx.x >> 5));
+  lut[threadIdx.x + kThreads] = __ldg(p.code + ((threadIdx.x + kThreads) >> 5));
+  __syncthreads();
+  const float* mine = lut + (threadIdx.x & 31);
+  const int64_t col0 = static_cast<int64_t>(blockIdx.x) * kTile, row0 = static_cast<int64_t>(blockIdx.y) * kTile;
+  {
+    const int r = threadIdx.x >> 2, quarter = threadIdx.x & 3;
+    const int64_t first = (row0 + r) * cols + col0 + quarter * 16;
+    const uint2 codes = __ldg(reinterpret_cast<const uint2*>(p.packed + first / 2));
+    const float scale = block_scale(p, block_of(p, first));
+    const uint32_t words[2] = {codes.x, codes.y};
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const uint32_t byte = (words[b >> 2] >> (8 * (b & 3))) & 255u;
+      const float high = round_state<STATE>(__fmul_rn(mine[(byte >> 4) * 32], scale));
+      const float low = round_state<STATE>(__fmul_rn(mine[(byte & 15u) * 32], scale));
+      tile[(quarter * 16 + 2 * b) * kTilePitch + r] = __float2bfloat16_rn(high);
+      tile[(quarter * 16 + 2 * b + 1) * kTilePitch + r] = __float2bfloat16_rn(low);
+    }
+  }
+  __syncthreads();
+  {
+    const int c = threadIdx.x >> 2, quarter = threadIdx.x & 3;
+    const uint4* source = reinterpret_cast<const uint4*>(tile + c * kTilePitch + quarter * 16);
+    uint4* target = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (col0 + c) * ld_out + row0 + quarter * 16);
+    target[0] = source[0];
+    target[1] = source[1];
+  }
+}
+
 }  // namespace
 }  // namespace ct
 
@@ -199,6 +244,38 @@ extern "C" int ct_nf4_decode_chunks(const uint8_t* packed, const void* absmax, c
                     (long long)chunk, (long long)pitch);
   return ct::decode(packed, absmax, code, code2, absmax2, offset, out, n, blocksize, blocksize2, nested, state_dtype,
                     out_dtype, chunk, pitch, stream);
+}
+
+extern "C" int ct_nf4_decode_transposed(const uint8_t* packed, const void* absmax, const float* code,
+                                        const float* code2, const float* absmax2, const float* offset, void* out,
+                                        int64_t rows, int64_t cols, int64_t ld_out, int blocksize, int blocksize2,
+                                        int nested, int state_dtype, int out_dtype, void* stream) {
+  using namespace ct;
+  if (rows < 0 || cols < 0 || blocksize <= 0) return fail(CT_ERR_ARG, "ct_nf4_decode_transposed: sizes");
+  if (rows == 0 || cols == 0) return CT_OK;
+  if (!packed || !absmax || !code || !out) return fail(CT_ERR_ARG, "ct_nf4_decode_transposed: null pointer");
+  if (nested && (!code2 || !absmax2 || !offset || blocksize2 <= 0))
+    return fail(CT_ERR_ARG, "ct_nf4_decode_transposed: nested statistics missing");
+  if (out_dtype != CT_BF16 || state_dtype < CT_F32 || state_dtype > CT_F16 || rows % kTile || cols % kTile ||
+      blocksize % 16 || ld_out < rows || ld_out % 8 || (reinterpret_cast<uintptr_t>(packed) & 7) ||
+      (reinterpret_cast<uintptr_t>(out) & 15) || rows / kTile > 65535)
+    return fail(CT_ERR_UNSUPPORTED, "ct_nf4_decode_transposed: bf16 output, rows and columns in multiples of 64, block size a multiple of 16, aligned buffers");
+  auto log2_of = [](int value) {
+    if (value <= 0 || (value & (value - 1))) return -1;
+    int shift = 0;
+    while ((1 << shift) < value) ++shift;
+    return shift;
+  };
+  const int inner2 = blocksize2 > 0 ? blocksize2 : 1;
+  Nf4Params p{packed, absmax, code, code2, absmax2, offset, out, rows * cols, blocksize, inner2, nested, state_dtype,
+              1, log2_of(blocksize), log2_of(inner2), 0, 0};
+  const dim3 grid(static_cast<unsigned>(cols / kTile), static_cast<unsigned>(rows / kTile));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int state = (state_dtype == CT_F32 || state_dtype == out_dtype) ? CT_F32 : state_dtype;
+  if (state == CT_F16) nf4_decode_transposed_kernel<CT_F16><<<grid, kThreads, 0, s>>>(p, rows, cols, ld_out);
+  else nf4_decode_transposed_kernel<CT_F32><<<grid, kThreads, 0, s>>>(p, rows, cols, ld_out);
+  count_launch(false);
+  return check_launch("ct_nf4_decode_transposed");
 }
 
 namespace ct {

@@ -97,6 +97,17 @@ def _readable(tensor):
     return tensor
 
 
+def _weight_operand(weight):
+    """(tensor, row stride, column stride) of a [N, K] weight for the input-gradient products: row-major, or the
+    `.T` view of a weight that was materialised transposed (unit row stride) - passed on as it is."""
+    if weight.dim() != 2:
+        raise ValueError("expected a matrix")
+    if weight.shape[0] > 1 and weight.shape[1] > 1 and weight.stride(0) == 1 and weight.stride(1) >= weight.shape[0]:
+        return weight, 1, weight.stride(1)
+    weight = _readable(weight)
+    return weight, _leading(weight), 1
+
+
 def _writable(tensor, name):
     if tensor.dim() != 2 or (tensor.shape[1] > 1 and tensor.stride(1) != 1):
         raise ValueError(f"{name} must be a matrix with contiguous rows")
@@ -179,6 +190,29 @@ def materialize(weight, state, dtype):
     return cast(weight, dtype)
 
 
+def materialize_for_gradient(weight, state, dtype):
+    """`materialize` for a weight that only the input-gradient product dx = dy @ W will read. With
+    CT_B200_DECODE_TRANSPOSED=1 an NF4 weight is decoded TRANSPOSED where the shapes allow it (same values; returned
+    as the [N, K] view of a [K, N] buffer), which makes W the K-major operand of that GEMM. Timed alone in short
+    bursts that orientation is up to 19 % faster (1555 against 1302 TFLOP/s at 16384 x 14336 x 4352); inside a
+    training step, where the GPU sits at its power cap, the same launches take the same time either way (1461 and
+    1465 us) and the transposed decode is the slower one, so the default is the plain decode."""
+    if decodes_transposed(weight, state, dtype):
+        from .nf4_cuda import dequantize_nf4_transposed
+        return dequantize_nf4_transposed(weight, state, dtype)
+    return materialize(weight, state, dtype)
+
+
+def decodes_transposed(weight, state, dtype):
+    """Whether `materialize_for_gradient` decodes this weight transposed."""
+    if (state is None or not weight.is_cuda or weight.dtype != torch.uint8 or not weight.is_contiguous()
+            or state.quant_type != "nf4" or _lib.gemm_path == _lib.PATH_SIMT
+            or os.environ.get("CT_B200_DECODE_TRANSPOSED", "0") != "1"):
+        return False
+    from .nf4_cuda import transposable
+    return transposable(state, dtype)
+
+
 _side_streams = {}
 
 
@@ -212,7 +246,7 @@ def materialize_into_pair(weight, state, pair, which):
     return pair
 
 
-def materialize_ahead(pairs, dtype, order=None, *, interleave=False):
+def materialize_ahead(pairs, dtype, order=None, *, interleave=False, for_gradient=False):
     """`materialize` for several (weight, quant_state) pairs with the NF4 decodes issued on a side
     stream in `order`, so that they run under whatever the caller launches next that does not need the
     dense weights (the low-rank products, which leave the decode most of the HBM bandwidth).
@@ -220,7 +254,9 @@ def materialize_ahead(pairs, dtype, order=None, *, interleave=False):
     CT_B200_DECODE_AHEAD=0 decodes in stream order instead.
     interleave=True: pairs 0 and 1 (the gate and up weights of an MLP, equal shapes) share ONE buffer of
     interleaved 128-row blocks (`materialize_into_pair`); matrices[0] and matrices[1] are that buffer, complete
-    once both have been waited for."""
+    once both have been waited for.
+    for_gradient: True, or the indices of the matrices that only input-gradient products will read
+    (`materialize_for_gradient`); the interleaved pair is never among them."""
     order = list(range(len(pairs))) if order is None else list(order)
     device = pairs[0][0].device
     shared = []
@@ -232,7 +268,8 @@ def materialize_ahead(pairs, dtype, order=None, *, interleave=False):
                 outer, inner = pairs[0][0].shape if pairs[0][1] is None else pairs[0][1].shape
                 shared.append(torch.empty((2 * outer, inner), device=device, dtype=dtype))
             return materialize_into_pair(weight, state, shared[0], index)
-        return materialize(weight, state, dtype)
+        gradient_only = for_gradient is True or (for_gradient and index in for_gradient)
+        return (materialize_for_gradient if gradient_only else materialize)(weight, state, dtype)
 
     ahead = (device.type == "cuda" and (interleave or any(state is not None for _, state in pairs))
              and os.environ.get("CT_B200_DECODE_AHEAD", "1") != "0")
@@ -292,7 +329,8 @@ def forward_linear(x, weight, a, b, *, out, xa, bias=None, residual=None):
 def input_gradient(dy, weight, a, b, dx, low, *, add=False):
     """low = dy @ b; dx = (add ? dx : 0) + dy @ weight + low @ a (kernels/linear.py:36-39)."""
     _lib.require_cuda(dy, weight, dx, low)
-    dy, weight = _readable(dy), _readable(weight)
+    dy = _readable(dy)
+    weight, w_rs, w_cs = _weight_operand(weight)
     _writable(dx, "dx")
     _writable(low, "low")
     a, b = a.contiguous(), b.contiguous()
@@ -300,7 +338,7 @@ def input_gradient(dy, weight, a, b, dx, low, *, add=False):
     inner, rank = weight.shape[1], a.shape[0]
     with _lib.on_device(dy):
         _lib.check(_lib.load().ct_input_gradient(
-            dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), b.data_ptr(),
+            dy.data_ptr(), _leading(dy), weight.data_ptr(), w_rs, w_cs, a.data_ptr(), b.data_ptr(),
             dx.data_ptr(), _leading(dx), low.data_ptr(), _leading(low), rows, inner, outer, rank, int(bool(add)),
             _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
 
@@ -308,14 +346,15 @@ def input_gradient(dy, weight, a, b, dx, low, *, add=False):
 def input_gradient_with(dy, weight, a, low, dx, *, add=False):
     """`input_gradient` with low = dy @ b already computed: dx = (add ? dx : 0) + dy @ weight + low @ a."""
     _lib.require_cuda(dy, weight, dx, low)
-    dy, weight, low = _readable(dy), _readable(weight), _readable(low)
+    dy, low = _readable(dy), _readable(low)
+    weight, w_rs, w_cs = _weight_operand(weight)
     _writable(dx, "dx")
     a = a.contiguous()
     rows, outer = dy.shape
     inner, rank = weight.shape[1], a.shape[0]
     with _lib.on_device(dy):
         _lib.check(_lib.load().ct_input_gradient(
-            dy.data_ptr(), _leading(dy), weight.data_ptr(), _leading(weight), a.data_ptr(), None,
+            dy.data_ptr(), _leading(dy), weight.data_ptr(), w_rs, w_cs, a.data_ptr(), None,
             dx.data_ptr(), _leading(dx), low.data_ptr(), _leading(low), rows, inner, outer, rank, int(bool(add)),
             _lib.code_of(dy.dtype), _lib.gemm_path, _lib.stream_of(dy)))
 
@@ -329,7 +368,8 @@ def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
     count = len(dys)
     _lib.require_cuda(dx, *dys, *weights, *lows)
     dys = [_readable(t) for t in dys]
-    weights = [_readable(t) for t in weights]
+    operands = [_weight_operand(t) for t in weights]
+    weights = [operand[0] for operand in operands]
     a_list, b_list = [t.contiguous() for t in a_list], [t.contiguous() for t in b_list]
     _writable(dx, "dx")
     for low in lows:
@@ -340,7 +380,8 @@ def input_gradient_group(dys, weights, a_list, b_list, dx, lows, *, add=False):
     with _lib.on_device(dx):
         _lib.check(_lib.load().ct_input_gradient_group(
             count, pointers(dys), sizes([_leading(t) for t in dys]), pointers(weights),
-            sizes([_leading(t) for t in weights]), pointers(a_list), pointers(b_list),
+            sizes([operand[1] for operand in operands]), sizes([operand[2] for operand in operands]),
+            pointers(a_list), pointers(b_list),
             sizes([t.shape[0] for t in weights]), sizes([t.shape[0] for t in a_list]), dx.data_ptr(), _leading(dx),
             pointers(lows), sizes([_leading(t) for t in lows]), rows, inner, int(bool(add)),
             _lib.code_of(dx.dtype), _lib.gemm_path, _lib.stream_of(dx)))
@@ -679,7 +720,8 @@ class _LoRAGroup(torch.autograd.Function):
                                                         [parameters[4 * i + 2] for i in range(len(states))])
             total = a_all.shape[0]
             low_all = torch.empty((rows, total), device=x.device, dtype=dtype)
-            decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype)
+            decoded, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype,
+                                                 for_gradient=True)
             for index, (state, grad) in enumerate(zip(states, grad_outputs)):
                 weight, a, b, _ = parameters[4 * index:4 * index + 4]
                 signal = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
@@ -716,7 +758,7 @@ class _LoRAGroup(torch.autograd.Function):
             return (cast(dx.reshape(x.shape), x.dtype), None, None, None, None, None, None, residual_grad, *results)
         for index, (state, grad) in enumerate(zip(states, grad_outputs)):
             weight, a, b, _ = parameters[4 * index:4 * index + 4]
-            matrix = materialize(weight, state, dtype) if want_dx else None
+            matrix = materialize_for_gradient(weight, state, dtype) if want_dx else None
             a16, b16 = (kept[1], kept[2]) if kept and len(states) == 1 else cast_many((a, b), dtype)
             dy = cast(grad.reshape(-1, grad.shape[-1]), dtype).contiguous()
             make = torch.empty_like if rows else torch.zeros_like

@@ -7,14 +7,15 @@ The three projections run through ``forward_linear`` / ``input_gradient`` /
 and its in-place backward are ct_swiglu.
 """
 
+import os
+
 import torch
 
 from .. import _lib
-from .linear import (_policy, apply_projection, cast, gated_input_gradient, gated_projections, gated_supported,
-                     input_gradient_swiglu,
-                     materialize, materialize_ahead, forward_linear, input_gradient, input_gradient_with,
-                     input_gradient_group, parameter_gradients, projection_parameters, matmul, stack_adapters,
-                     token_gradient, token_gradients)
+from .linear import (_policy, apply_projection, cast, decodes_transposed, gated_input_gradient, gated_projections,
+                     gated_supported, input_gradient_swiglu, materialize, materialize_ahead, forward_linear,
+                     input_gradient, input_gradient_with, input_gradient_group, parameter_gradients,
+                     projection_parameters, matmul, stack_adapters, token_gradient, token_gradients)
 
 
 def _swiglu(gate, up, grad, out, dg, du, reconstruct):
@@ -78,7 +79,6 @@ def _gated(x, parameters, states, dtype, keeps):
     pass that `keeps` gate and up for the backward pass writes them anyway; there two launches of the
     512 x 256-tile GEMM plus the stand-alone activation are faster than the gated launch, whose tile is
     256 x 256 (3 ms of a 583 ms step), and are used unless CT_B200_MLP_FUSED_FORWARD=1."""
-    import os
     if keeps and os.environ.get("CT_B200_MLP_FUSED_FORWARD", "0") != "1":
         return False
     if (states[0] is None) != (states[1] is None) or parameters[0].device.type != "cuda":
@@ -89,14 +89,15 @@ def _gated(x, parameters, states, dtype, keeps):
     return gated_supported(x, shapes[0][0], [parameters[1].shape[0], parameters[5].shape[0]], dtype)
 
 
-def _prepare(parameters, states, dtype, order=(0, 1, 2), casts=None, gated=False):
+def _prepare(parameters, states, dtype, order=(0, 1, 2), casts=None, gated=False, for_gradient=False):
     """Base weights decoding on the side stream in `order` (wait on the returned handle before a
     matrix is read), cast adapters, and the gate/up `a` matrices stacked row-wise (their low-rank
     inputs come from one product over x). `casts` = (stacked, b_gate, b_up, a_down, b_down) already in
     `dtype` (kept by the forward pass) skips the conversion. gated=True: matrices[0] and matrices[1] are one
-    buffer holding both weights in interleaved 128-row blocks (complete after pending.wait(0) and wait(1))."""
+    buffer holding both weights in interleaved 128-row blocks (complete after pending.wait(0) and wait(1)).
+    `for_gradient`: the matrices (True: all; else their indices) that only input-gradient products will read."""
     matrices, pending = materialize_ahead([(parameters[4 * i], state) for i, state in enumerate(states)], dtype, order,
-                                          interleave=gated)
+                                          interleave=gated, for_gradient=for_gradient)
     ranks = [parameters[1].shape[0], parameters[5].shape[0]]
     if casts is not None:
         stacked, others, offsets = casts[0], list(casts[1:]), [0, ranks[0]]
@@ -201,13 +202,21 @@ class _TiledLoRAMLP(torch.autograd.Function):
         gated = rows > 0 and not ctx.cache and _gated(flat, parameters, ctx.states, dtype, False)
         matrices, adapters, stacked, pending = _prepare(parameters, ctx.states, dtype,
                                                         (2, 0, 1) if ctx.cache or gated else (0, 1, 2),
-                                                        casts=saved[5:10] if len(saved) >= 10 else None, gated=gated)
+                                                        casts=saved[5:10] if len(saved) >= 10 else None, gated=gated,
+                                                        for_gradient=(2,) if not ctx.cache else
+                                                        (0, 1) if os.environ.get("CT_B200_MLP_FUSED_BACKWARD", "0") == "1"
+                                                        else True)
+        # The gated recompute reads gate and up from the interleaved buffer; their input gradient is faster from
+        # transposed copies (K-major operands) where those can be decoded - two more decodes on the side stream.
+        gradient_pair = gradient_pending = None
+        if gated and want_dx and all(decodes_transposed(parameters[4 * i], ctx.states[i], dtype) for i in range(2)):
+            gradient_pair, gradient_pending = materialize_ahead(
+                [(parameters[4 * i], ctx.states[i]) for i in range(2)], dtype, for_gradient=True)
         ranks = [a.shape[0] for a, _ in adapters]
         # Cached activations: the SwiGLU backward can ride on the down projection's input-gradient GEMM
         # (`input_gradient_swiglu`, bit-identical). Measured inside a 7B step it gives back in that GEMM - which
         # then runs on 256 x 256 tiles with a long epilogue instead of 512 x 256 tiles - what the stand-alone kernel
         # cost (585-589 ms against 585-586 ms), so it is taken only on request (CT_B200_MLP_FUSED_BACKWARD=1).
-        import os
         joined = (bool(ctx.cache) and rows > 0 and os.environ.get("CT_B200_MLP_FUSED_BACKWARD", "0") == "1"
                   and matrices[2].shape[1] % 32 == 0 and matrices[2].shape[0] % 8 == 0
                   and gated_supported(upstream, 0, ranks[2:], dtype))
@@ -272,7 +281,11 @@ class _TiledLoRAMLP(torch.autograd.Function):
             if want_dx:
                 # gate and up share the input: one GEMM over [d_gate | low_g | d_up | low_u].
                 pending.wait()
-                if gated:
+                if gradient_pair is not None:
+                    gradient_pending.wait()
+                    input_gradient_group((gate, up), gradient_pair, [adapters[0][0], adapters[1][0]],
+                                         [adapters[0][1], adapters[1][1]], dx[start:stop], low[:2])
+                elif gated:
                     gated_input_gradient(gate, up, matrices[0], adapters[0][0], adapters[1][0], adapters[0][1],
                                          adapters[1][1], dx[start:stop], low[:2])
                 else:

@@ -50,6 +50,32 @@ def dequantize_nf4_blocks(weight, state, pair, which):
     return pair
 
 
+def transposable(state, dtype):
+    """Whether `dequantize_nf4_transposed` can produce this weight: bf16, both extents multiples of 64, block size a
+    multiple of 16."""
+    shape = tuple(state.shape)
+    return (dtype == torch.bfloat16 and len(shape) == 2 and shape[0] % 64 == 0 and shape[1] % 64 == 0
+            and 0 < shape[0] // 64 <= 65535 and int(state.blocksize) % 16 == 0)
+
+
+def dequantize_nf4_transposed(weight, state, dtype):
+    """The values of ``dequantize_nf4(weight, state, dtype)`` stored transposed: returns the [N, K] view `.T` of a
+    contiguous [K, N] buffer. The input-gradient product dx = dy @ W contracts over N; with this storage W is the
+    K-major operand of that GEMM (the operators pass the view straight to `input_gradient`)."""
+    _lib.require_cuda(weight)
+    if not transposable(state, dtype):
+        raise ValueError("transposed decode needs bf16 and extents that are multiples of 64")
+    absmax, code, extras, nested, auxiliary = _statistics(weight, state)
+    outer, inner = state.shape
+    output = torch.empty((inner, outer), device=weight.device, dtype=dtype)
+    with _lib.on_device(weight):
+        _lib.check(_lib.load().ct_nf4_decode_transposed(
+            weight.data_ptr(), absmax.data_ptr(), code.data_ptr(), *(_lib.pointer(t) for t in extras),
+            output.data_ptr(), outer, inner, outer, int(state.blocksize), int(auxiliary.blocksize) if nested else 0,
+            int(nested), _lib.code_of(state.dtype), _lib.code_of(dtype), _lib.stream_of(weight)))
+    return output.T
+
+
 def dequantize_nf4(weight, state, dtype):
     """Decode packed NF4 `weight` (uint8, two codes per byte) into a dense `dtype` tensor of `state.shape`.
 

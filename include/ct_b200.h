@@ -103,6 +103,16 @@ CT_API int ct_nf4_decode_chunks(const uint8_t* packed, const void* absmax, const
                   void* out, int64_t n, int blocksize, int blocksize2, int nested,
                   int state_dtype, int out_dtype, int64_t chunk, int64_t pitch, void* stream);
 
+/* The same decode written TRANSPOSED: W[rows, cols] (packed row-major) -> out[cols, rows] (bf16, leading dimension
+ * ld_out), through 64 x 64 shared-memory tiles so that both the packed reads and the transposed writes are whole
+ * sectors. For the backward pass: dx = dy @ W contracts over the rows of W, and with this storage W is the K-major
+ * operand of that GEMM (pass it to ct_input_gradient with strides (1, ld_out)). Same values as ct_nf4_decode.
+ * rows and cols multiples of 64, blocksize a multiple of 16, bf16 output; else CT_ERR_UNSUPPORTED. */
+CT_API int ct_nf4_decode_transposed(const uint8_t* packed, const void* absmax, const float* code,
+                  const float* code2, const float* absmax2, const float* offset, void* out,
+                  int64_t rows, int64_t cols, int64_t ld_out, int blocksize, int blocksize2,
+                  int nested, int state_dtype, int out_dtype, void* stream);
+
 /* ---- NF4 encode ---------------------------------------------------------
  * Replaces the bitsandbytes quantiser the reference calls when it installs a frozen base
  * weight (modeling/lora.py:41-56, `Params4bit(..., quant_type="nf4", compress_statistics=True)`).
@@ -183,11 +193,14 @@ CT_API int ct_forward_linear(const void* x, int64_t ldx, const void* w, int64_t 
  * Replaces kernels/linear.py:36-39 (input_gradient).
  *   low = round(dy @ b)                                        [T, r]
  *   dx  = round((add ? dx : 0) + dy @ w + low @ a)             [T, K]
- * dy[T,N] (ld_dy), w[N,K] (ldw), a[r,K], b[N,r] contiguous. `w` may be NULL:
+ * dy[T,N] (ld_dy), a[r,K], b[N,r] contiguous. Element (n, k) of w[N,K] is at w[n * w_rs + k * w_cs] (element
+ * strides, one of them 1): (ld, 1) for the row-major weight, (1, ld) for a weight that was decoded transposed
+ * (ct_nf4_decode_transposed) - the contraction of this product runs over n, so the transposed storage is the
+ * K-major operand the tensor core reads fastest; the values are the same either way. `w` may be NULL:
  * then only `low` is written (kernels/linear.py:124). `b` may be NULL with r > 0:
  * then `low` is an INPUT that already holds round(dy @ b) (a caller that computed it
  * while the base weight was still being decoded on another stream). */
-CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t ldw,
+CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64_t w_rs, int64_t w_cs,
                       const void* a, const void* b, void* dx, int64_t ld_dx,
                       void* low, int64_t ld_low, int64_t T, int64_t K, int64_t N,
                       int64_t r, int add, int dtype, int path, void* stream);
@@ -199,10 +212,11 @@ CT_API int ct_input_gradient(const void* dy, int64_t ld_dy, const void* w, int64
  *   dx    = round((add ? dx : 0) + sum_i (dy_i @ w_i + low_i @ a_i))      [T, K]
  * in ONE GEMM over the concatenated contraction [dy_0 | low_0 | dy_1 | low_1 | ...], so dx is
  * written (and rounded) once instead of being re-read and re-rounded per projection. Arrays of
- * `count` device pointers / sizes live in HOST memory. dy_i[T, N_i], w_i[N_i, K], a_i[r_i, K],
- * b_i[N_i, r_i] contiguous. */
+ * `count` device pointers / sizes live in HOST memory. dy_i[T, N_i], w_i[N_i, K] with element strides
+ * (w_rs[i], w_cs[i]) as in ct_input_gradient, a_i[r_i, K], b_i[N_i, r_i] contiguous. */
 CT_API int ct_input_gradient_group(int count, const void* const* dy, const int64_t* ld_dy,
-                                   const void* const* w, const int64_t* ldw, const void* const* a,
+                                   const void* const* w, const int64_t* w_rs, const int64_t* w_cs,
+                                   const void* const* a,
                                    const void* const* b, const int64_t* N, const int64_t* r, void* dx,
                                    int64_t ld_dx, void* const* low, const int64_t* ld_low, int64_t T,
                                    int64_t K, int add, int dtype, int path, void* stream);

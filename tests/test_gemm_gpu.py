@@ -212,6 +212,33 @@ def test_grouped_input_gradient_equals_the_sum_of_the_projections(path, shapes):
     assert relative(dx, before.float() + expected) < 6e-3
 
 
+@pytest.mark.parametrize("rows,inner,outers", [(1024, 1024, (1536, 128)), (300, 520, (136,)), (512, 2048, (1024, 1024))])
+def test_input_gradient_from_transposed_weights_is_bit_identical(path, rows, inner, outers):
+    """The `.T` view of a weight stored transposed (what `materialize_for_gradient` returns) gives every
+    input-gradient entry point the very results of the row-major weight: same products, same order."""
+    ranks = [16] * len(outers)
+    dys = [torch.randn(rows, n, device="cuda").bfloat16() for n in outers]
+    weights = [(torch.randn(n, inner, device="cuda") * .05).bfloat16() for n in outers]
+    views = [w.T.contiguous().T for w in weights]
+    assert all(v.stride(0) == 1 and torch.equal(v, w) for v, w in zip(views, weights))
+    a_list = [(torch.randn(r, inner, device="cuda") * .05).bfloat16() for r in ranks]
+    b_list = [(torch.randn(n, r, device="cuda") * .05).bfloat16() for n, r in zip(outers, ranks)]
+    results = []
+    for operands in (weights, views):
+        lows = [torch.empty(rows, r, device="cuda", dtype=torch.bfloat16) for r in ranks]
+        grouped = torch.full((rows, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+        linear.input_gradient_group(dys, operands, a_list, b_list, grouped, lows)
+        single = torch.full((rows, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+        linear.input_gradient(dys[0], operands[0], a_list[0], b_list[0], single, lows[0])
+        given = torch.full((rows, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+        linear.input_gradient_with(dys[0], operands[0], a_list[0], lows[0], given)
+        linear.input_gradient_with(dys[0], operands[0], a_list[0], lows[0], given, add=True)
+        results.append((grouped, single, given))
+    for natural, transposed in zip(*results):
+        assert torch.isfinite(transposed.float()).all()
+        assert torch.equal(natural, transposed)
+
+
 @pytest.mark.parametrize("tokens,rows,cols", [(4096, 768, 512), (300, 24, 520), (1024, 16, 256), (16384, 512, 128)])
 def test_token_gradient_of_stacked_low_matrices(path, tokens, rows, cols):
     # out = left^T @ right over the tokens, fp32, fixed slice order; `left` holds several projections'

@@ -460,6 +460,7 @@ def test_mlp_with_the_gated_launch_equals_the_separate_kernels(monkeypatch, nf4,
         monkeypatch.setenv("CT_B200_MLP_FUSED", fused)              # the recompute of the backward pass
         monkeypatch.setenv("CT_B200_MLP_FUSED_FORWARD", fused)      # a forward pass that keeps gate and up (off by default)
         monkeypatch.setenv("CT_B200_MLP_FUSED_BACKWARD", fused)     # SwiGLU backward in the down projection's GEMM (off by default)
+        monkeypatch.setenv("CT_B200_DECODE_TRANSPOSED", fused)      # weights of input-gradient products decoded transposed
         before = _lib.launch_count()
         y = module(x, residual=x, cache=cache)
         grads = torch.autograd.grad(y, params, signal)

@@ -107,3 +107,30 @@ def test_full_size_weight_properties():
                                state_dtype=torch.bfloat16, out_dtype=torch.bfloat16)
     assert np.array_equal(first.reshape(-1)[sample].float().cpu().numpy(), oracle)
     assert (first.float() - weight.float()).abs().max() <= 0.17 * state.absmax.max()
+
+
+@pytest.mark.parametrize("nested", [False, True])
+@pytest.mark.parametrize("source_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape,blocksize", [((128, 192), 64), ((64, 64), 16), ((256, 128), 128), ((4096, 14336), 64)])
+def test_transposed_decode_holds_the_same_values(monkeypatch, nested, source_dtype, shape, blocksize):
+    """ct_nf4_decode_transposed: the [N, K] view of its [K, N] output equals ct_nf4_decode bit for bit, nothing is
+    written past the buffer, and `materialize_for_gradient` hands out that view (or the plain decode where the
+    shape does not allow the transposed one)."""
+    from causal_tuner_b200.kernels.linear import decodes_transposed, materialize_for_gradient
+    from causal_tuner_b200.kernels.nf4_cuda import dequantize_nf4_transposed
+    monkeypatch.setenv("CT_B200_DECODE_TRANSPOSED", "1")      # off by default: no gain inside a power-capped step
+    values = torch.randn(*shape, device="cuda", dtype=source_dtype)
+    packed, state = quantize_nf4(values, blocksize=blocksize, nested=nested)
+    expected = dequantize_nf4(packed, state, torch.bfloat16)
+    actual = dequantize_nf4_transposed(packed, state, torch.bfloat16)
+    assert actual.shape == expected.shape and actual.stride() == (1, shape[0])
+    assert torch.equal(actual, expected)
+    assert decodes_transposed(packed, state, torch.bfloat16)
+    view = materialize_for_gradient(packed, state, torch.bfloat16)
+    assert view.stride(0) == 1 and torch.equal(view, expected)
+    odd, odd_state = quantize_nf4(torch.randn(72, 96, device="cuda", dtype=source_dtype), blocksize=64, nested=nested)
+    assert not decodes_transposed(odd, odd_state, torch.bfloat16)
+    assert materialize_for_gradient(odd, odd_state, torch.bfloat16).is_contiguous()
+    assert not decodes_transposed(packed, state, torch.float32)
+    monkeypatch.setenv("CT_B200_DECODE_TRANSPOSED", "0")
+    assert materialize_for_gradient(packed, state, torch.bfloat16).is_contiguous()
