@@ -386,14 +386,15 @@ def test_interleaved_decode_places_both_weights_in_128_row_blocks(nested):
     assert torch.equal(blocks[:, 1].reshape(384, 512), dense.bfloat16())
 
 
-@pytest.mark.parametrize("rows", [1000, 256, 77])
-def test_gated_launch_is_bit_identical_to_two_projections_and_the_activation(rows):
+@pytest.mark.parametrize("rows,inner,width", [(1000, 512, 384), (256, 512, 384), (77, 512, 384), (300, 520, 128),
+                                              (513, 72, 256)])
+def test_gated_launch_is_bit_identical_to_two_projections_and_the_activation(rows, inner, width):
     """ct_gated_forward / ct_gated_backward / ct_gated_input_gradient against ct_forward_linear x 2 + ct_swiglu
     and ct_input_gradient_group on the same operands: every output equal bit for bit, buffers the launch must
     not touch untouched, the in-place form (hidden over its own gradient) included."""
     from causal_tuner_b200.kernels import linear
     torch.manual_seed(rows)
-    inner, width, ranks = 512, 384, (16, 24)
+    ranks = (16, 24)
     bf = dict(device="cuda", dtype=torch.bfloat16)
     x = torch.randn(rows, inner, **bf)
     weights = [torch.randn(width, inner, **bf) * .05 for _ in range(2)]
